@@ -1,0 +1,133 @@
+/*
+ * scattermoe_b200 — C ABI of the B200 (sm_100a) kernels behind ScatterMoE's `ParallelLinear` path.
+ *
+ * Conventions (all entry points):
+ *   - every pointer is a DEVICE pointer owned by the caller unless the comment says otherwise; the library
+ *     never allocates, frees or synchronises; work is enqueued on `stream` (a cudaStream_t passed as void*)
+ *     of the CUDA device that is current on the calling thread;
+ *   - strides are in ELEMENTS, sizes in elements/rows; index tensors are int64 like the reference's;
+ *   - return value: SMOE_OK (0) or one of the SMOE_ERR_* codes; `smoe_last_error()` gives the message of the
+ *     last failure on the calling thread. Nothing throws, aborts or traps;
+ *   - `status` (nullable) is a device int32[4] word the tensor-core kernels write if one of their bounded waits
+ *     ran out: status[0] != 0 means "device timeout", status[1..3] say where. The caller reads it when it likes.
+ *
+ * Each declaration cites the interface of the reference project (shawntan/scattermoe) that it replaces.
+ */
+#ifndef SCATTERMOE_B200_H
+#define SCATTERMOE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SMOE_ABI_VERSION 1
+
+enum smoe_status {
+  SMOE_OK = 0,
+  SMOE_ERR_BAD_ARG = 1,       /* shape / pointer / enum value rejected */
+  SMOE_ERR_UNSUPPORTED = 2,   /* valid request this build has no kernel for */
+  SMOE_ERR_CUDA = 3,          /* a CUDA runtime/driver call failed (message has the CUDA error) */
+  SMOE_ERR_WORKSPACE = 4,     /* workspace too small or missing */
+  SMOE_ERR_ARCH = 5           /* current device is not sm_100 */
+};
+
+enum smoe_dtype { SMOE_F32 = 0, SMOE_BF16 = 1, SMOE_F16 = 2 };
+
+/* flags for the GEMM entry points */
+enum smoe_flags {
+  SMOE_FLAG_ALLOW_TF32 = 1,   /* fp32 inputs may use reduced-precision tensor cores (ops.py:7 ALLOW_TF32) */
+  SMOE_FLAG_FORCE_SIMT = 2,   /* take the CUDA-core kernel even where a tensor-core kernel exists */
+  SMOE_FLAG_FORCE_TC = 4      /* fail with SMOE_ERR_UNSUPPORTED instead of taking the CUDA-core kernel */
+};
+
+/* fused epilogues of smoe_scatter2scatter (what sits between / after the two expert linears) */
+enum smoe_epilogue {
+  SMOE_EPI_NONE = 0
+};
+
+int smoe_version(void);
+const char* smoe_last_error(void);
+/* 1 if the last GEMM-shaped call on this thread ran on tcgen05 tensor cores, 0 if on CUDA cores. */
+int smoe_last_path_was_tensor_core(void);
+
+/* ---- routing bookkeeping ----------------------------------------------------------------------------
+ * Replaces flatten_sort_count (scattermoe/parallel_experts.py:14-21): torch.sort + scattermoe::bincount
+ * (:6-12) + cumsum. One stable counting sort: `sorted_expert_idxs[R]` ascending, `sorted_scattered_idxs[R]`
+ * = flat slot index t*k+j of each sorted entry (ascending inside one expert), `expert_offsets[E]` =
+ * inclusive cumulative counts. Ids outside [0, E) are ignored (their output slots are left untouched).
+ * Limits: 0 <= R < 2^31, 1 <= E <= 4096. */
+size_t smoe_sort_count_workspace_bytes(int64_t R, int32_t E);
+int smoe_sort_count(const int64_t* expert_idxs, int64_t R, int32_t E,
+                    int64_t* sorted_expert_idxs, int64_t* sorted_scattered_idxs, int64_t* expert_offsets,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* Inclusive end offsets from the sorted ids alone. The reference's kernels.ops.scatter2scatter
+ * (scattermoe/kernels/ops.py:120) receives no offsets and masks rows per expert inside the kernel
+ * (:81-91); this build's grouped GEMM walks expert segments, so callers that only hold the sorted ids
+ * derive the offsets with this call first. */
+int smoe_offsets_from_sorted(const int64_t* sorted_expert_idxs, int64_t R, int32_t E,
+                             int64_t* expert_offsets, void* stream);
+
+/* ---- grouped GEMM with fused row gather / scatter -----------------------------------------------------
+ * Replaces kernels.ops.scatter2scatter (scattermoe/kernels/ops.py:120-183, kernel :55-118).
+ * For sorted position m in [0, R) with expert e(m):
+ *     Y[out(m), :] = X[in(m), :] @ W[e(m)] (+ bias[e(m), :])
+ *     in(m)  = m if x_grouped else sorted_scattered_idxs[m] / fan_out
+ *     out(m) = m if y_grouped else sorted_scattered_idxs[m]
+ * X is (x_rows, K), W is (E, K, N) with arbitrary element strides (either K or N contiguous for the
+ * tensor-core kernel), Y is (R, N). fp32 accumulation; Y, bias in the dtype of X and W.
+ * `expert_offsets` is REQUIRED (see smoe_offsets_from_sorted). */
+int smoe_scatter2scatter(const void* X, int64_t x_rows, int64_t stride_xm, int64_t stride_xk,
+                         const void* W, int64_t stride_we, int64_t stride_wk, int64_t stride_wn,
+                         const void* bias, int64_t stride_be, int64_t stride_bn,
+                         void* Y, int64_t stride_ym, int64_t stride_yn,
+                         const int64_t* sorted_expert_idxs, const int64_t* sorted_scattered_idxs,
+                         const int64_t* expert_offsets,
+                         int64_t R, int32_t K, int32_t N, int32_t E, int32_t fan_out,
+                         int32_t x_grouped, int32_t y_grouped, int32_t dtype, int32_t flags,
+                         int32_t epilogue, int32_t* status, void* stream);
+
+/* ---- per-expert weight gradient ---------------------------------------------------------------------
+ * Replaces kernels.ops.group_bwd_W (scattermoe/kernels/ops.py:191-239, kernel :247-366).
+ *     DW[e][kk][n] = sum over rows m of expert e of X[xrow(m)][kk] * DY[m][n]
+ *     Db[e][n]     = sum over rows m of expert e of DY[m][n]          (Db nullable)
+ * DY is (R, N) grouped. X is grouped (x_gather_idx == NULL, xrow(m) = m) or, an extension of the
+ * reference, still un-grouped: xrow(m) = x_gather_idx[m] / fan_out, which removes the reference's
+ * group(x) copy (scattermoe/parallel_experts.py:99). DW is addressed through its element strides
+ * (the reference hands out the (E,K,N) permuted view of an (E,N,K) buffer, ops.py:192-193). Every
+ * element of DW and Db is written, experts without rows get zeros: no pre-zeroing is needed. */
+int smoe_group_bwd_w(const void* DY, int64_t stride_dym, int64_t stride_dyn,
+                     const void* X, int64_t x_rows, int64_t stride_xm, int64_t stride_xk,
+                     const int64_t* expert_offsets, const int64_t* x_gather_idx, int32_t fan_out,
+                     void* DW, int64_t stride_dwe, int64_t stride_dwk, int64_t stride_dwn,
+                     void* Db, int64_t stride_dbe, int64_t stride_dbn,
+                     int64_t R, int32_t K, int32_t N, int32_t E, int32_t dtype, int32_t flags,
+                     int32_t* status, void* stream);
+
+/* ---- row gather with optional per-row scale -----------------------------------------------------------
+ * Replaces kernels.ops.group (scattermoe/kernels/ops.py:377-410, kernel :417-457):
+ *     Y[n, :] = A[idx[n] / fan_out, :] * coeff[idx[n]]     (coeff nullable, same dtype as A) */
+int smoe_group(const void* A, int64_t a_rows, int64_t stride_am, int64_t stride_ak,
+               const int64_t* idx, const void* coeff, int32_t fan_out,
+               void* Y, int64_t stride_ym, int64_t stride_yk,
+               int64_t R, int32_t K, int32_t dtype, void* stream);
+
+/* ---- top-k reductions around the GEMMs ----------------------------------------------------------------
+ * smoe_topk_reduce replaces `(gates.unsqueeze(1) @ output.view(T,k,N)).squeeze(1)`
+ * (scattermoe/parallel_experts.py:44-46) and, with gates == NULL, `.view(T,k,K).sum(-2)` (:123):
+ *     out[t, :] = sum_j gates[t, j] * Yx[t*k + j, :]        fp32 accumulation
+ * smoe_gate_grad replaces `(output_expanded @ grad_out.unsqueeze(-1)).squeeze(-1)` (:79):
+ *     d_gates[t, j] = <Yx[t*k + j, :], grad_out[t, :]>     fp32 accumulation */
+int smoe_topk_reduce(const void* Yx, int64_t stride_yxm, const void* gates, int64_t stride_gt, int64_t stride_gk,
+                     void* out, int64_t stride_om, int64_t T, int32_t k, int32_t N, int32_t dtype, void* stream);
+int smoe_gate_grad(const void* Yx, int64_t stride_yxm, const void* grad_out, int64_t stride_gom,
+                   void* d_gates, int64_t stride_dgt, int64_t stride_dgk,
+                   int64_t T, int32_t k, int32_t N, int32_t dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SCATTERMOE_B200_H */

@@ -1,0 +1,130 @@
+// C-ABI entry points of the GEMM-shaped calls: argument validation and the choice between the tcgen05
+// kernels and the CUDA-core kernels. Declarations and the contract are in include/scattermoe_b200.h.
+#include <stdarg.h>
+
+#include <mutex>
+
+#include "smoe_common.cuh"
+
+namespace smoe {
+
+static thread_local char g_last_error[512] = "";
+static thread_local int g_last_path_tc = 0;
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+}
+
+void set_last_path(int tensor_core) { g_last_path_tc = tensor_core; }
+
+int get_device_info(DeviceInfo* out) {
+  static std::mutex mu;
+  static DeviceInfo cache[64];
+  static bool have[64] = {false};
+  int dev = 0;
+  SMOE_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev < 0 || dev >= 64 || !have[dev]) {
+    DeviceInfo d;
+    d.device = dev;
+    SMOE_CUDA(cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    SMOE_CUDA(cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev));
+    SMOE_CUDA(cudaDeviceGetAttribute(&d.cc_minor, cudaDevAttrComputeCapabilityMinor, dev));
+    SMOE_CUDA(cudaDeviceGetAttribute(&d.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    if (dev < 0 || dev >= 64) { *out = d; return SMOE_OK; }
+    cache[dev] = d;
+    have[dev] = true;
+  }
+  *out = cache[dev];
+  return SMOE_OK;
+}
+
+}  // namespace smoe
+
+using namespace smoe;
+
+extern "C" int smoe_version(void) { return SMOE_ABI_VERSION; }
+extern "C" const char* smoe_last_error(void) { return g_last_error; }
+extern "C" int smoe_last_path_was_tensor_core(void) { return g_last_path_tc; }
+
+static int check_dtype(const char* who, int dtype) {
+  if (dtype != SMOE_F32 && dtype != SMOE_BF16 && dtype != SMOE_F16) {
+    set_error("%s: unknown dtype %d", who, dtype);
+    return SMOE_ERR_BAD_ARG;
+  }
+  return SMOE_OK;
+}
+
+extern "C" int smoe_scatter2scatter(const void* X, int64_t x_rows, int64_t stride_xm, int64_t stride_xk,
+                                    const void* W, int64_t stride_we, int64_t stride_wk, int64_t stride_wn,
+                                    const void* bias, int64_t stride_be, int64_t stride_bn, void* Y,
+                                    int64_t stride_ym, int64_t stride_yn, const int64_t* sorted_expert_idxs,
+                                    const int64_t* sorted_scattered_idxs, const int64_t* expert_offsets, int64_t R,
+                                    int32_t K, int32_t N, int32_t E, int32_t fan_out, int32_t x_grouped,
+                                    int32_t y_grouped, int32_t dtype, int32_t flags, int32_t epilogue,
+                                    int32_t* status, void* stream) {
+  if (int rc = check_dtype("scatter2scatter", dtype)) return rc;
+  SMOE_CHECK_ARG(R >= 0 && R < (int64_t(1) << 31), "scatter2scatter: R=%lld out of range [0, 2^31)", (long long)R);
+  SMOE_CHECK_ARG(K >= 0 && N >= 0 && E >= 1 && fan_out >= 1, "scatter2scatter: bad sizes K=%d N=%d E=%d fan_out=%d", K,
+                 N, E, fan_out);
+  // same contract as the reference's assertion `idx.size(0) == X.size(0) * k` (ops.py:124-125)
+  SMOE_CHECK_ARG(x_rows * fan_out == R && (!x_grouped || fan_out == 1),
+                 "scatter2scatter: %lld index entries but X has %lld rows with fan_out %d", (long long)R,
+                 (long long)x_rows, fan_out);
+  SMOE_CHECK_ARG(epilogue == SMOE_EPI_NONE, "scatter2scatter: unknown epilogue %d", epilogue);
+  if (R == 0 || N == 0) return SMOE_OK;
+  SMOE_CHECK_ARG(X && W && Y && sorted_expert_idxs && sorted_scattered_idxs && expert_offsets,
+                 "scatter2scatter: null pointer");
+  S2SArgs a{X, x_rows, stride_xm, stride_xk, W, stride_we, stride_wk, stride_wn, bias, stride_be, stride_bn,
+            Y, stride_ym, stride_yn, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
+            R, K, N, E, fan_out, x_grouped ? 1 : 0, y_grouped ? 1 : 0, dtype, flags, epilogue,
+            status, static_cast<cudaStream_t>(stream)};
+  if (!(flags & SMOE_FLAG_FORCE_SIMT)) {
+    const int rc = launch_s2s_tc(a);
+    if (rc != SMOE_ERR_UNSUPPORTED) {
+      if (rc == SMOE_OK) set_last_path(1);
+      return rc;
+    }
+    if (flags & SMOE_FLAG_FORCE_TC) {
+      set_error("scatter2scatter: no tensor-core kernel for this dtype/alignment (dtype=%d K=%d N=%d)", dtype, K, N);
+      return rc;
+    }
+  }
+  set_last_path(0);
+  return launch_s2s_simt(a);
+}
+
+extern "C" int smoe_group_bwd_w(const void* DY, int64_t stride_dym, int64_t stride_dyn, const void* X,
+                                int64_t x_rows, int64_t stride_xm, int64_t stride_xk,
+                                const int64_t* expert_offsets, const int64_t* x_gather_idx, int32_t fan_out,
+                                void* DW, int64_t stride_dwe, int64_t stride_dwk, int64_t stride_dwn, void* Db,
+                                int64_t stride_dbe, int64_t stride_dbn, int64_t R, int32_t K, int32_t N, int32_t E,
+                                int32_t dtype, int32_t flags, int32_t* status, void* stream) {
+  if (int rc = check_dtype("group_bwd_w", dtype)) return rc;
+  SMOE_CHECK_ARG(R >= 0 && R < (int64_t(1) << 31), "group_bwd_w: R=%lld out of range [0, 2^31)", (long long)R);
+  SMOE_CHECK_ARG(K >= 0 && N >= 0 && E >= 1 && fan_out >= 1, "group_bwd_w: bad sizes K=%d N=%d E=%d fan_out=%d", K, N,
+                 E, fan_out);
+  if (K == 0 || N == 0) return SMOE_OK;
+  SMOE_CHECK_ARG(DW && expert_offsets && (R == 0 || (DY && X)), "group_bwd_w: null pointer");
+  SMOE_CHECK_ARG(x_gather_idx != nullptr || x_rows >= R, "group_bwd_w: grouped X has %lld rows, %lld needed",
+                 (long long)x_rows, (long long)R);
+  WGradArgs a{DY, stride_dym, stride_dyn, X, x_rows, stride_xm, stride_xk, expert_offsets, x_gather_idx, fan_out,
+              DW, stride_dwe, stride_dwk, stride_dwn, Db, stride_dbe, stride_dbn, R, K, N, E, dtype, flags,
+              status, static_cast<cudaStream_t>(stream)};
+  if (!(flags & SMOE_FLAG_FORCE_SIMT)) {
+    const int rc = launch_wgrad_tc(a);
+    if (rc != SMOE_ERR_UNSUPPORTED) {
+      if (rc == SMOE_OK) set_last_path(1);
+      return rc;
+    }
+    if (flags & SMOE_FLAG_FORCE_TC) {
+      set_error("group_bwd_w: no tensor-core kernel for this dtype/alignment (dtype=%d K=%d N=%d)", dtype, K, N);
+      return rc;
+    }
+  }
+  set_last_path(0);
+  return launch_wgrad_simt(a);
+}

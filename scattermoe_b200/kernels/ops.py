@@ -1,0 +1,261 @@
+"""Kernel-level operators, same names and signatures as the reference's scattermoe/kernels/ops.py.
+
+    scatter2scatter  (ops.py:120)   grouped GEMM with fused row gather / scatter
+    group_bwd_W      (ops.py:191)   per-expert weight (and bias) gradient
+    group            (ops.py:377)   row gather with optional per-row scale
+    BLOCK_M, ALLOW_TF32 (ops.py:6-7) module globals read at call time
+
+Every function hands raw device pointers, element strides and the current CUDA stream to the C-ABI library
+(include/scattermoe_b200.h). Outputs are allocated here, as in the reference (ops.py:130, :192-195, :384);
+the library never allocates. Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _lib
+
+BLOCK_M = 128        # rows of the expert-sorted slot list per tensor-core tile (ops.py:6)
+ALLOW_TF32 = True    # fp32 inputs may use reduced-precision tensor cores (ops.py:7); read at call time
+FORCE_PATH = None    # testing hook: None (automatic) | "simt" | "tc"
+
+
+def _flags() -> int:
+    f = _lib.FLAG_ALLOW_TF32 if ALLOW_TF32 else 0
+    if FORCE_PATH == "simt":
+        f |= _lib.FLAG_FORCE_SIMT
+    elif FORCE_PATH == "tc":
+        f |= _lib.FLAG_FORCE_TC
+    return f
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _lib.DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise RuntimeError("scattermoe_b200: unsupported dtype %s (float32, bfloat16, float16)" % t.dtype)
+
+
+def _i64(t: torch.Tensor) -> torch.Tensor:
+    if t.dtype != torch.int64:
+        t = t.to(torch.int64)
+    return t if t.is_contiguous() else t.contiguous()
+
+
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def last_path_was_tensor_core() -> bool:
+    """True if the last GEMM-shaped call made from this thread ran on the tcgen05 kernels."""
+    return bool(_lib.load().smoe_last_path_was_tensor_core())
+
+
+def offsets_from_sorted(sorted_expert_idxs: torch.Tensor, num_experts: int) -> torch.Tensor:
+    """Inclusive per-expert end offsets recomputed from the sorted expert ids."""
+    _lib.require_cuda(sorted_expert_idxs, "sorted_expert_idxs")
+    se = _i64(sorted_expert_idxs)
+    out = torch.empty(num_experts, dtype=torch.int64, device=se.device)
+    with torch.cuda.device(se.device):
+        rc = _lib.load().smoe_offsets_from_sorted(se.data_ptr(), se.numel(), num_experts, out.data_ptr(),
+                                                  _lib.stream_ptr(se.device))
+    _lib.check(rc, "smoe_offsets_from_sorted")
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
+# scatter2scatter
+# --------------------------------------------------------------------------------------------------
+
+def _scatter2scatter_impl(output, W, X, k, sorted_expert_idxs, sorted_scattered_idxs, b, x_grouped, y_grouped,
+                          expert_offsets):
+    _lib.require_cuda(X, "X")
+    if W.dtype != X.dtype or output.dtype != X.dtype or (b is not None and b.dtype != X.dtype):
+        raise RuntimeError("scatter2scatter: X, W, b and the output must share one dtype")
+    se, ss = _i64(sorted_expert_idxs), _i64(sorted_scattered_idxs)
+    E = W.size(0)
+    if expert_offsets is None:
+        expert_offsets = offsets_from_sorted(se, E)
+    off = _i64(expert_offsets)
+    sb = (b.stride(0), b.stride(1)) if b is not None else (0, 0)
+    with torch.cuda.device(X.device):
+        rc = _lib.load().smoe_scatter2scatter(
+            X.data_ptr(), X.size(0), X.stride(0), X.stride(1),
+            W.data_ptr(), W.stride(0), W.stride(1), W.stride(2),
+            _ptr(b), sb[0], sb[1],
+            output.data_ptr(), output.stride(0), output.stride(1),
+            se.data_ptr(), ss.data_ptr(), off.data_ptr(),
+            se.numel(), X.size(1), output.size(1), E, k,
+            int(x_grouped), int(y_grouped), _dtype_code(X), _flags(), 0,
+            _lib.status_word(X.device).data_ptr(), _lib.stream_ptr(X.device))
+    _lib.check(rc, "smoe_scatter2scatter")
+
+
+@torch.library.custom_op("scattermoe_b200::scatter2scatter", mutates_args={"output"})
+def scatter2scatter_compileable(output: torch.Tensor, W: torch.Tensor, X: torch.Tensor, k: int,
+                                sorted_expert_idxs: torch.Tensor, sorted_scattered_idxs: torch.Tensor,
+                                b: Optional[torch.Tensor], x_grouped: bool, y_grouped: bool,
+                                expert_offsets: Optional[torch.Tensor]) -> None:
+    """Traceable form (mirrors scattermoe::scatter2scatter, ops.py:140)."""
+    _scatter2scatter_impl(output, W, X, k, sorted_expert_idxs, sorted_scattered_idxs, b, x_grouped, y_grouped,
+                          expert_offsets)
+
+
+def scatter2scatter(X, W, sorted_expert_idxs, sorted_scattered_idxs, k, b=None, x_grouped=False, y_grouped=False,
+                    out=None, expert_offsets=None):
+    """ops.py:120-137. `expert_offsets` is an optional extra: pass it when already known to save the small
+    kernel that rebuilds it from `sorted_expert_idxs`."""
+    assert sorted_scattered_idxs.size(0) == sorted_expert_idxs.size(0)
+    assert sorted_scattered_idxs.size(0) == X.size(0) * k
+    y_dim = W.size(-1)
+    L_scattered = sorted_expert_idxs.size(0)
+    if out is None:
+        output = torch.empty((L_scattered, y_dim), device=X.device, dtype=X.dtype)
+    else:
+        assert out.size(0) == L_scattered and out.size(1) == y_dim
+        output = out
+    if torch.compiler.is_compiling():
+        scatter2scatter_compileable(output, W, X, k, sorted_expert_idxs, sorted_scattered_idxs, b, x_grouped,
+                                    y_grouped, expert_offsets)
+    else:
+        _scatter2scatter_impl(output, W, X, k, sorted_expert_idxs, sorted_scattered_idxs, b, x_grouped, y_grouped,
+                              expert_offsets)
+    return output
+
+
+# --------------------------------------------------------------------------------------------------
+# group_bwd_W
+# --------------------------------------------------------------------------------------------------
+
+def _group_bwd_w_impl(E, DW, Db, DY, X, expert_offsets, x_gather_idx, fan_out):
+    _lib.require_cuda(DY, "DY")
+    if X.dtype != DY.dtype or DW.dtype != DY.dtype:
+        raise RuntimeError("group_bwd_W: DY, X and DW must share one dtype")
+    off = _i64(expert_offsets)
+    gi = _i64(x_gather_idx) if x_gather_idx is not None else None
+    sdb = (Db.stride(0), Db.stride(1)) if Db is not None else (0, 0)
+    with torch.cuda.device(DY.device):
+        rc = _lib.load().smoe_group_bwd_w(
+            DY.data_ptr(), DY.stride(0), DY.stride(1),
+            X.data_ptr(), X.size(0), X.stride(0), X.stride(1),
+            off.data_ptr(), _ptr(gi), fan_out,
+            DW.data_ptr(), DW.stride(0), DW.stride(1), DW.stride(2),
+            _ptr(Db), sdb[0], sdb[1],
+            DY.size(0), X.size(1), DY.size(1), E, _dtype_code(DY), _flags(),
+            _lib.status_word(DY.device).data_ptr(), _lib.stream_ptr(DY.device))
+    _lib.check(rc, "smoe_group_bwd_w")
+
+
+@torch.library.custom_op("scattermoe_b200::groupXtY", mutates_args={"DW", "Db"})
+def groupXtY_compileable(E: int, DW: torch.Tensor, Db: Optional[torch.Tensor], DY: torch.Tensor, X: torch.Tensor,
+                         expert_offsets: torch.Tensor, x_gather_idx: Optional[torch.Tensor], fan_out: int) -> None:
+    """Traceable form (mirrors scattermoe::groupXtY, ops.py:202; Db is declared as mutated here)."""
+    _group_bwd_w_impl(E, DW, Db, DY, X, expert_offsets, x_gather_idx, fan_out)
+
+
+def group_bwd_W(DY, X, expert_offsets, E, has_bias=False, x_gather_idx=None, fan_out=1):
+    """ops.py:191-199. Returns (DW as the (E,K,N) view of an (E,N,K) buffer, Db or None).
+
+    Extension: with `x_gather_idx` (the sorted slot indices) X may be the un-grouped (T, K) input; row m then
+    reads X[x_gather_idx[m] // fan_out], which makes the reference's `group(x)` copy unnecessary.
+    The kernel writes every element (zeros for experts without rows), so the buffers are not pre-zeroed.
+    """
+    if x_gather_idx is None:
+        assert X.size(0) == DY.size(0)
+    else:
+        assert x_gather_idx.size(0) == DY.size(0) and X.size(0) * fan_out == DY.size(0)
+    DWt = torch.empty((E, DY.size(-1), X.size(-1)), device=DY.device, dtype=DY.dtype)
+    DW = DWt.permute(0, 2, 1)
+    Db = torch.empty((E, DY.size(-1)), device=DY.device, dtype=DY.dtype) if has_bias else None
+    if torch.compiler.is_compiling():
+        groupXtY_compileable(E, DW, Db, DY, X, expert_offsets, x_gather_idx, fan_out)
+    else:
+        _group_bwd_w_impl(E, DW, Db, DY, X, expert_offsets, x_gather_idx, fan_out)
+    return DW, Db
+
+
+# --------------------------------------------------------------------------------------------------
+# group
+# --------------------------------------------------------------------------------------------------
+
+def _group_impl(A, K, N, Y, coeff, has_coeff, fan_out, sorted_expert_idxs):
+    _lib.require_cuda(A, "A")
+    if Y.dtype != A.dtype:
+        raise RuntimeError("group: A and the output must share one dtype")
+    idx = _i64(sorted_expert_idxs)
+    c = None
+    if has_coeff:
+        c = coeff if (coeff.dtype == A.dtype and coeff.is_contiguous()) else coeff.to(A.dtype).contiguous()
+    with torch.cuda.device(A.device):
+        rc = _lib.load().smoe_group(A.data_ptr(), A.size(0), A.stride(0), A.stride(1), idx.data_ptr(), _ptr(c),
+                                    fan_out, Y.data_ptr(), Y.stride(0), Y.stride(1), N, K, _dtype_code(A),
+                                    _lib.stream_ptr(A.device))
+    _lib.check(rc, "smoe_group")
+
+
+@torch.library.custom_op("scattermoe_b200::group", mutates_args={"Y"})
+def group_compileable(A: torch.Tensor, K: int, N: int, Y: torch.Tensor, coeff: Optional[torch.Tensor],
+                      has_coeff: bool, fan_out: int, sorted_expert_idxs: torch.Tensor) -> None:
+    """Traceable form (mirrors scattermoe::group, ops.py:389)."""
+    _group_impl(A, K, N, Y, coeff, has_coeff, fan_out, sorted_expert_idxs)
+
+
+def group(A, sorted_expert_idxs, coeff=None, fan_out=1, out=None):
+    """ops.py:377-386. The index argument keeps the reference's name although every caller passes the
+    sorted slot indices (parallel_experts.py:92, :99)."""
+    N = sorted_expert_idxs.size(0)
+    K = A.size(1)
+    assert A.size(0) * fan_out == N
+    if out is not None:
+        Y = out
+    else:
+        Y = torch.empty((N, K), dtype=A.dtype, device=A.device)
+    if torch.compiler.is_compiling():
+        group_compileable(A, K, N, Y, coeff, coeff is not None, fan_out, sorted_expert_idxs)
+    else:
+        _group_impl(A, K, N, Y, coeff, coeff is not None, fan_out, sorted_expert_idxs)
+    return Y
+
+
+# --------------------------------------------------------------------------------------------------
+# top-k reductions (torch ops in the reference, parallel_experts.py:44-46, :79, :123)
+# --------------------------------------------------------------------------------------------------
+
+def topk_reduce(expanded: torch.Tensor, gates: Optional[torch.Tensor], T: int, k: int) -> torch.Tensor:
+    """out[t] = sum_j gates[t, j] * expanded[t*k + j]  (gates None: plain sum). `expanded` is (T*k, N)."""
+    _lib.require_cuda(expanded, "expanded")
+    assert expanded.size(0) == T * k
+    if expanded.stride(1) != 1:
+        expanded = expanded.contiguous()
+    N = expanded.size(1)
+    out = torch.empty((T, N), dtype=expanded.dtype, device=expanded.device)
+    g = None
+    if gates is not None:
+        assert gates.size(0) == T and gates.size(1) == k
+        g = gates if gates.dtype == expanded.dtype else gates.to(expanded.dtype)
+    sg = (g.stride(0), g.stride(1)) if g is not None else (0, 0)
+    with torch.cuda.device(expanded.device):
+        rc = _lib.load().smoe_topk_reduce(expanded.data_ptr(), expanded.stride(0), _ptr(g), sg[0], sg[1],
+                                          out.data_ptr(), out.stride(0), T, k, N, _dtype_code(expanded),
+                                          _lib.stream_ptr(expanded.device))
+    _lib.check(rc, "smoe_topk_reduce")
+    return out
+
+
+def gate_grad(expanded: torch.Tensor, grad_out: torch.Tensor, T: int, k: int) -> torch.Tensor:
+    """d_gates[t, j] = <expanded[t*k + j], grad_out[t]>, in the dtype of `expanded`."""
+    _lib.require_cuda(expanded, "expanded")
+    assert expanded.size(0) == T * k and grad_out.size(0) == T
+    if expanded.stride(1) != 1:
+        expanded = expanded.contiguous()
+    if grad_out.stride(1) != 1 or grad_out.dtype != expanded.dtype:
+        grad_out = grad_out.to(expanded.dtype).contiguous()
+    dg = torch.empty((T, k), dtype=expanded.dtype, device=expanded.device)
+    with torch.cuda.device(expanded.device):
+        rc = _lib.load().smoe_gate_grad(expanded.data_ptr(), expanded.stride(0), grad_out.data_ptr(),
+                                        grad_out.stride(0), dg.data_ptr(), dg.stride(0), dg.stride(1), T, k,
+                                        expanded.size(1), _dtype_code(expanded), _lib.stream_ptr(expanded.device))
+    _lib.check(rc, "smoe_gate_grad")
+    return dg

@@ -1,0 +1,192 @@
+"""Autograd boundary of the expert linear layer; same surface as the reference's
+scattermoe/parallel_experts.py (flatten_sort_count :14, ParallelLinear :25, parallel_linear :136,
+ParallelExperts :148).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from . import _lib
+from . import kernels
+
+
+def _sort_count_impl(flat: torch.Tensor, num_experts: int):
+    _lib.require_cuda(flat, "expert_idxs")
+    R = flat.numel()
+    dev = flat.device
+    lib = _lib.load()
+    sorted_e = torch.empty(R, dtype=torch.int64, device=dev)
+    sorted_idx = torch.empty(R, dtype=torch.int64, device=dev)
+    offsets = torch.empty(num_experts, dtype=torch.int64, device=dev)
+    ws_bytes = lib.smoe_sort_count_workspace_bytes(R, num_experts)
+    ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.smoe_sort_count(flat.data_ptr(), R, num_experts, sorted_e.data_ptr(), sorted_idx.data_ptr(),
+                                 offsets.data_ptr(), ws.data_ptr(), ws_bytes, _lib.stream_ptr(dev))
+    _lib.check(rc, "smoe_sort_count")
+    return sorted_e, sorted_idx, offsets
+
+
+@torch.library.custom_op("scattermoe_b200::sort_count", mutates_args={})
+def sort_count_compileable(flat_expert_idxs: torch.Tensor, num_experts: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Traceable form; plays the role of the reference's scattermoe::bincount op (parallel_experts.py:6-12)."""
+    return _sort_count_impl(flat_expert_idxs, num_experts)
+
+
+@sort_count_compileable.register_fake
+def _(flat_expert_idxs: torch.Tensor, num_experts: int):
+    R = flat_expert_idxs.numel()
+    dev = flat_expert_idxs.device
+    return (torch.empty(R, dtype=torch.long, device=dev), torch.empty(R, dtype=torch.long, device=dev),
+            torch.empty(num_experts, dtype=torch.long, device=dev))
+
+
+def flatten_sort_count(expert_idxs: torch.Tensor, num_experts: int):
+    """parallel_experts.py:14-21. Returns (sorted_expert_idxs, sorted_scattered_idxs, expert_offsets):
+    expert ids ascending, the flat slot index `t*k+j` of every sorted entry in ascending order inside one
+    expert (the stable order; the reference's torch.sort leaves ties unspecified), and the inclusive
+    cumulative per-expert counts. One counting-sort pass on the device; no host synchronisation and no
+    torch.compile needed."""
+    with torch.no_grad():
+        flat = expert_idxs.flatten()
+        in_dtype = flat.dtype
+        if in_dtype != torch.int64:
+            flat = flat.to(torch.int64)
+        flat = flat.contiguous()
+        if torch.compiler.is_compiling():
+            sorted_e, sorted_idx, offsets = sort_count_compileable(flat, num_experts)
+        else:
+            sorted_e, sorted_idx, offsets = _sort_count_impl(flat, num_experts)
+        if in_dtype != torch.int64:
+            sorted_e = sorted_e.to(in_dtype)
+        return sorted_e, sorted_idx, offsets
+
+
+def _rowmajor(t: torch.Tensor) -> torch.Tensor:
+    return t if t.stride(-1) == 1 else t.contiguous()
+
+
+class ParallelLinear(torch.autograd.Function):
+    """parallel_experts.py:25-134, same argument order and return arity.
+
+    Differences that are not visible in results: the top-k reductions are dedicated kernels instead of
+    batched matmuls (:44-46, :79, :123), the un-grouped input is gathered inside the weight-gradient kernel
+    instead of being copied by `group` (:99), and gradients nobody asked for are not computed.
+    """
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, expert_weights: torch.Tensor, k: int,
+                sorted_expert_idxs: torch.Tensor, sorted_scattered_idxs: torch.Tensor,
+                expert_offsets: torch.Tensor,
+                expert_biases: Optional[torch.Tensor] = None,
+                gates: Optional[torch.Tensor] = None,
+                grouped_in: bool = False, grouped_out: bool = False):
+        x = _rowmajor(x)
+        output = kernels.ops.scatter2scatter(
+            X=x, W=expert_weights, b=expert_biases, k=k,
+            sorted_expert_idxs=sorted_expert_idxs, sorted_scattered_idxs=sorted_scattered_idxs,
+            x_grouped=grouped_in, y_grouped=grouped_out, expert_offsets=expert_offsets)
+        if gates is not None:
+            output_expanded = output.view(gates.size(0), gates.size(1), output.size(-1))
+            output = kernels.ops.topk_reduce(output, gates, gates.size(0), gates.size(1))
+        else:
+            output_expanded = None
+        ctx.save_for_backward(x, expert_weights, expert_biases, sorted_expert_idxs, sorted_scattered_idxs,
+                              expert_offsets, gates, output_expanded)
+        ctx.grouped_in = grouped_in
+        ctx.grouped_out = grouped_out
+        ctx.k = k
+        return output
+
+    @staticmethod
+    def backward(ctx, grad_out: torch.Tensor):
+        (x, expert_weights, expert_biases, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
+         gates, output_expanded) = ctx.saved_tensors
+        k = ctx.k
+        grouped_in = ctx.grouped_in
+        grouped_out = ctx.grouped_out
+        need_x, need_w = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        need_b = expert_biases is not None and ctx.needs_input_grad[6]
+        need_g = gates is not None and ctx.needs_input_grad[7]
+        grad_out = _rowmajor(grad_out)
+        if grad_out.dtype != x.dtype:
+            grad_out = grad_out.to(x.dtype)
+
+        d_gates = None
+        if gates is not None:
+            T, gate_fan = gates.size(0), gates.size(1)
+            expanded_flat = output_expanded.flatten(0, 1)
+            if need_g:
+                d_gates = kernels.ops.gate_grad(expanded_flat, grad_out, T, gate_fan).to(gates.dtype)
+            gates_flat = gates.flatten()
+            grouped_grad_out = expanded_flat   # storage reused below, as the reference does (:82)
+        else:
+            gates_flat = None
+            gate_fan = 1
+            grouped_grad_out = None
+
+        d_input = d_weights = d_biases = None
+        if need_x or need_w or need_b:
+            if grouped_out:
+                grouped_grad_out = grad_out
+            else:
+                grouped_grad_out = kernels.ops.group(grad_out, sorted_scattered_idxs, fan_out=gate_fan,
+                                                     coeff=gates_flat, out=grouped_grad_out)
+            if need_w or need_b:
+                d_weights, d_biases = kernels.ops.group_bwd_W(
+                    DY=grouped_grad_out, X=x, expert_offsets=expert_offsets, E=expert_weights.size(0),
+                    has_bias=expert_biases is not None,
+                    x_gather_idx=None if grouped_in else sorted_scattered_idxs, fan_out=1 if grouped_in else k)
+            if need_x:
+                d_expanded_input = kernels.ops.scatter2scatter(
+                    X=grouped_grad_out, x_grouped=True, W=expert_weights.permute(0, 2, 1),
+                    sorted_expert_idxs=sorted_expert_idxs, sorted_scattered_idxs=sorted_scattered_idxs,
+                    k=1, y_grouped=grouped_in, expert_offsets=expert_offsets)
+                if k == 1:
+                    d_input = d_expanded_input
+                else:
+                    d_input = kernels.ops.topk_reduce(d_expanded_input, None, x.size(0), k)
+        return (d_input, d_weights, None, None, None, None, d_biases, d_gates, None, None)
+
+
+def parallel_linear(inputs, expert_weights, k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
+                    expert_biases=None, gates=None, grouped_in=False, grouped_out=False):
+    """parallel_experts.py:136-146. `expert_weights` is (E, in, out) in any stride order."""
+    return ParallelLinear.apply(inputs, expert_weights, k, sorted_expert_idxs, sorted_scattered_idxs,
+                                expert_offsets, expert_biases, gates, grouped_in, grouped_out)
+
+
+class ParallelExperts(nn.Module):
+    """parallel_experts.py:148-182: weight (E, out, in) ~ N(0, 0.02), optional bias (E, out) zeros; same
+    parameter names and shapes, so reference checkpoints load unchanged."""
+
+    def __init__(self, num_experts, input_size, output_size, bias=False) -> None:
+        super().__init__()
+        self.weight = nn.Parameter(torch.empty(num_experts, output_size, input_size))
+        if bias:
+            self.bias = nn.Parameter(torch.empty(num_experts, output_size))
+        else:
+            self.bias = None
+        self.num_experts = num_experts
+        self.input_size = input_size
+        self.output_size = output_size
+        self.reset_parameters()
+
+    def extra_repr(self):
+        return 'num_experts={}, input_size={}, output_size={}'.format(
+            self.num_experts, self.input_size, self.output_size)
+
+    def reset_parameters(self) -> None:
+        nn.init.normal_(self.weight, std=0.02)
+        if self.bias is not None:
+            nn.init.zeros_(self.bias)
+
+    def forward(self, inputs, k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
+                gates=None, grouped_in=False, grouped_out=False):
+        return parallel_linear(
+            inputs, self.weight.permute(0, 2, 1), k,
+            sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
+            expert_biases=self.bias, gates=gates, grouped_in=grouped_in, grouped_out=grouped_out)

@@ -1,0 +1,115 @@
+"""Hugging Face MoE blocks routed through the B200 grouped-GEMM path.
+
+Mirrors the reference's scattermoe/utils/replace_moe.py: importing this module swaps
+`GptOssExperts.forward` (:21-55) and `GraniteMoeHybridMoE.forward` (:62-93) for versions built on
+`parallel_linear` + `flatten_sort_count`; the swap is logged on first use (:8-17) and a failure to patch is
+logged and swallowed (:56-57, :94-95).
+
+Two differences from the reference text, both needed to run against current transformers releases:
+  * gpt_oss: `routing_weights` may be the dense (T, E) score matrix the reference gathers from (:26) or the
+    already selected (T, k) scores newer routers return; it is gathered only in the first case.
+  * granitemoehybrid: the reference returns `(layer_output, router_logits)` (:93); releases whose own forward
+    returns the tensor alone get the tensor alone, otherwise the caller's residual add breaks.
+Inputs that are not on a CUDA device are handed to the original Hugging Face forward: this package has no
+CPU implementation.
+"""
+import inspect
+import logging
+
+import torch
+from torch.nn import functional as F
+
+from ..parallel_experts import flatten_sort_count, parallel_linear
+
+PATCHED = {}      # class name -> original forward
+
+
+def replace_function(cls, fun_name):
+    """Class-method swap that announces itself the first time the replacement runs (replace_moe.py:8-17)."""
+    def decorator(fun):
+        PATCHED[cls.__name__] = getattr(cls, fun_name)
+
+        def _announce_then_call(*args, **kwargs):
+            logging.info("Replacing `%s.%s` with %s:%s", cls.__name__, fun_name, fun.__code__.co_filename,
+                         fun.__name__)
+            setattr(cls, fun_name, fun)
+            return fun(*args, **kwargs)
+        setattr(cls, fun_name, _announce_then_call)
+        return fun
+    return decorator
+
+
+def gpt_oss_glu(gate_up: torch.Tensor, alpha: float, limit: float) -> torch.Tensor:
+    """Clamped SwiGLU on interleaved gate/up columns (replace_moe.py:39-43)."""
+    gate, up = gate_up[..., ::2], gate_up[..., 1::2]
+    gate = gate.clamp(min=None, max=limit)
+    up = up.clamp(min=-limit, max=limit)
+    return (up + 1) * (gate * torch.sigmoid(gate * alpha))
+
+
+try:
+    from transformers.models.gpt_oss.modeling_gpt_oss import GptOssExperts
+
+    @replace_function(cls=GptOssExperts, fun_name='forward')
+    def gpt_oss_forward(self, hidden_states: torch.Tensor, router_indices=None, routing_weights=None) -> torch.Tensor:
+        if not hidden_states.is_cuda:
+            return PATCHED['GptOssExperts'](self, hidden_states, router_indices=router_indices,
+                                            routing_weights=routing_weights)
+        batch_size = hidden_states.shape[0]
+        tokens = hidden_states.reshape(-1, self.hidden_size)
+        k = router_indices.shape[1]
+        if routing_weights.shape[-1] == self.num_experts:
+            # dense (T, E) scores, the layout the reference expects (k == E is read this way too)
+            selected = torch.gather(routing_weights, dim=1, index=router_indices)
+        else:
+            selected = routing_weights                                                  # already (T, k)
+        routing = flatten_sort_count(router_indices.flatten(), num_experts=self.num_experts)
+        gate_up = parallel_linear(tokens, self.gate_up_proj, k, *routing,
+                                  expert_biases=self.gate_up_proj_bias, grouped_in=False, grouped_out=True)
+        gated = gpt_oss_glu(gate_up, self.alpha, self.limit)
+        out = parallel_linear(gated, self.down_proj, 1, *routing,
+                              expert_biases=self.down_proj_bias, grouped_in=True, grouped_out=False,
+                              gates=selected.to(tokens.dtype))
+        return out.view(batch_size, -1, self.hidden_size)
+except Exception:  # transformers absent or without this model
+    logging.info("Failed to replace GptOssExperts")
+
+
+try:
+    from transformers.models.granitemoehybrid.modeling_granitemoehybrid import GraniteMoeHybridMoE
+
+    def _original_returns_tuple(fn) -> bool:
+        try:
+            src = inspect.getsource(fn)
+        except (OSError, TypeError):
+            return True
+        return any(line.strip().startswith("return") and "," in line for line in src.splitlines())
+
+    GRANITE_RETURNS_ROUTER_LOGITS = _original_returns_tuple(GraniteMoeHybridMoE.forward)
+
+    @replace_function(cls=GraniteMoeHybridMoE, fun_name='forward')
+    def granite_moe_forward(self, layer_input):
+        if not layer_input.is_cuda:
+            return PATCHED['GraniteMoeHybridMoE'](self, layer_input)
+        bsz, length, emb_size = layer_input.size()
+        tokens = layer_input.reshape(-1, emb_size)
+        # top-k routing decision (replace_moe.py:67-71)
+        router_logits = self.router.layer(tokens)
+        probs = F.softmax(router_logits, dim=1, dtype=torch.float)
+        probs, selected_experts = torch.topk(probs, self.router.top_k, dim=-1)
+        probs = probs / probs.sum(dim=-1, keepdim=True)
+        probs = probs.to(tokens.dtype)
+        routing = flatten_sort_count(selected_experts, num_experts=self.router.num_experts)
+        # experts: the FIRST half of the up-projection is the activated one here (replace_moe.py:76-83)
+        gate_half, linear_half = parallel_linear(
+            tokens, self.input_linear.weight.transpose(2, 1), self.router.top_k, *routing,
+            grouped_in=False, grouped_out=True).chunk(2, dim=-1)
+        hidden = self.activation(gate_half) * linear_half
+        layer_output = parallel_linear(hidden, self.output_linear.weight.transpose(2, 1), 1, *routing,
+                                       grouped_in=True, grouped_out=False, gates=probs)
+        layer_output = layer_output.view(bsz, length, emb_size)
+        if GRANITE_RETURNS_ROUTER_LOGITS:
+            return layer_output, router_logits
+        return layer_output
+except Exception:
+    logging.info("Failed to replace GraniteMoeHybridMoE")
