@@ -1,0 +1,420 @@
+"""Benchmark of the MoE-layer hot path: forward + backward tokens/s of one expert-MLP layer.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--config NAME] [--impl ours|reference]
+
+One "step" = routing bookkeeping (flatten_sort_count) + forward + backward (gradients w.r.t. the input, the
+gates and both expert weight tensors) of the layer on one batch of seeded synthetic tokens. Prints ONE JSON
+line. `value` is device-timed with the inputs resident in HBM; `e2e` repeats the measurement with the
+step's inputs copied from pinned host memory and its results copied back inside the timed region.
+
+N > 1 (launched by torch.distributed.run, one rank per GPU): every rank runs the same layer on its own shard
+of tokens (weak scaling, no data-path collective); time is the max over ranks.
+
+`--impl reference` times the reference's CPU path for the same layer (the dense per-expert PyTorch loop the
+reference's own test uses as ground truth) on the host cores, on a bounded sample of the tokens.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LAYERS = {
+    # name: T, d_model, d_ffn, E, top_k, kind, bias
+    "mixtral_8x7b": dict(T=16384, d=4096, F=14336, E=8, k=2, kind="glu_silu", bias=False),
+    "gpt_oss_20b": dict(T=8192, d=2880, F=2880, E=32, k=4, kind="gpt_oss", bias=True),
+    "granite_zipf": dict(T=32768, d=1536, F=512, E=64, k=8, kind="glu_silu", bias=False),
+    "qwen3_moe_ep": dict(T=65536, d=2048, F=768, E=128, k=8, kind="glu_silu", bias=False),
+    "tiny": dict(T=256, d=128, F=256, E=8, k=2, kind="glu_silu", bias=False),
+}
+CPU_SAMPLE_TOKENS = {"mixtral_8x7b": 2048, "gpt_oss_20b": 2048, "granite_zipf": 8192, "qwen3_moe_ep": 8192, "tiny": 256}
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=d["hbm_gbs"], tflops_burst=d["bf16_tflops"], tflops_sustained=d["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm_gbs=6650.0, tflops_burst=1590.0, tflops_sustained=1400.0, source="fallback")
+
+
+def layer_flops(c, tokens):
+    R = tokens * c["k"]
+    n1 = 2 * c["F"]
+    fwd = 2.0 * R * c["d"] * n1 + 2.0 * R * c["F"] * c["d"]
+    return fwd, 3.0 * fwd
+
+
+def make_routing(cfg_name, T, E, k, seed):
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(T, E, generator=g)
+    if cfg_name == "granite_zipf":
+        pop = torch.arange(1, E + 1, dtype=torch.float32) ** -1.2
+        pop = pop / pop.sum()
+        logits = logits + torch.log(pop)[torch.randperm(E, generator=g)]
+    if cfg_name == "gpt_oss_20b":
+        top, idx = torch.topk(logits, k, dim=-1)
+        p = torch.softmax(top, dim=-1)
+    else:
+        p, idx = torch.topk(torch.softmax(logits, dim=-1), k, dim=-1)
+        p = p / p.sum(-1, keepdim=True)
+    return p, idx
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clock and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return None
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1])); mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if not sm:
+            return None
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_layer(name, c, tokens, device, seed):
+    """Parameters and inputs of one rank: weights ~N(0, 0.02), X ~N(0, 1), softmax top-k routing."""
+    import scattermoe_b200 as sm
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+    d, F, E, k = c["d"], c["F"], c["E"], c["k"]
+
+    def rnd(*shape, std):
+        out = torch.empty(shape, dtype=bf, device=device)
+        # generate on the device in slabs: the CPU generator would take minutes for multi-GB tensors
+        gd = torch.Generator(device=device).manual_seed(seed + sum(shape))
+        out.normal_(0.0, std, generator=gd)
+        return out
+
+    layer = {}
+    if c["kind"] == "gpt_oss":
+        layer["w1"] = rnd(E, d, 2 * F, std=0.02).requires_grad_()     # (E, in, out) as gpt-oss stores it
+        layer["w2"] = rnd(E, F, d, std=0.02).requires_grad_()
+        layer["b1"] = rnd(E, 2 * F, std=0.02).requires_grad_()
+        layer["b2"] = rnd(E, d, std=0.02).requires_grad_()
+    else:
+        m = sm.mlp.GLUMLP(d, F, E, k).to(device=device, dtype=bf)
+        with torch.no_grad():
+            m.experts.weight.copy_(rnd(E, 2 * F, d, std=0.02))
+            m.output_experts.weight.copy_(rnd(E, d, F, std=0.02))
+        layer["module"] = m
+    p, idx = make_routing(name, tokens, E, k, seed)
+    host = dict(x=torch.randn(tokens, d, generator=g).to(bf).pin_memory(),
+                p=p.to(bf).pin_memory(), idx=idx.pin_memory(),
+                dy=torch.randn(tokens, d, generator=g).to(bf).pin_memory())
+    return layer, host
+
+
+def run_step(c, layer, x, p, idx, dy):
+    """One forward + backward through the public API. Returns (y, dx)."""
+    import scattermoe_b200 as sm
+    x = x.requires_grad_()
+    p = p.requires_grad_()
+    if c["kind"] == "gpt_oss":
+        from scattermoe_b200.utils.replace_moe import gpt_oss_glu
+        routing = sm.flatten_sort_count(idx, c["E"])
+        up = sm.parallel_linear(x, layer["w1"], c["k"], *routing, expert_biases=layer["b1"], grouped_out=True)
+        h = gpt_oss_glu(up, 1.702, 7.0)
+        y = sm.parallel_linear(h, layer["w2"], 1, *routing, expert_biases=layer["b2"], grouped_in=True, gates=p)
+        leaves = [x, p, layer["w1"], layer["w2"], layer["b1"], layer["b2"]]
+    else:
+        m = layer["module"]
+        y = m(x, p, idx)
+        leaves = [x, p, m.experts.weight, m.output_experts.weight]
+    grads = torch.autograd.grad(y, leaves, dy)
+    return y, grads[0]
+
+
+class KernelTimer:
+    """CUDA-event brackets around the C-ABI GEMM launches (they run on torch's current stream)."""
+
+    def __init__(self):
+        self.records = []   # (kind, flops, start_event, end_event)
+
+    def install(self):
+        from scattermoe_b200.kernels import ops
+        self._s2s, self._wg = ops._scatter2scatter_impl, ops._group_bwd_w_impl
+        timer = self
+
+        def s2s(output, W, X, k, se, ss, b, xg, yg, off):
+            a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            timer._s2s(output, W, X, k, se, ss, b, xg, yg, off)
+            z.record()
+            timer.records.append(("scatter2scatter", 2.0 * se.numel() * X.size(1) * output.size(1), a, z))
+
+        def wg(E, DW, Db, DY, X, off, gi, fan):
+            a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            timer._wg(E, DW, Db, DY, X, off, gi, fan)
+            z.record()
+            timer.records.append(("group_bwd_w", 2.0 * DY.size(0) * X.size(1) * DY.size(1), a, z))
+        ops._scatter2scatter_impl, ops._group_bwd_w_impl = s2s, wg
+
+    def remove(self):
+        from scattermoe_b200.kernels import ops
+        ops._scatter2scatter_impl, ops._group_bwd_w_impl = self._s2s, self._wg
+
+    def summary(self):
+        out = {}
+        for kind, flops, a, z in self.records:
+            d = out.setdefault(kind, dict(launches=0, ms=0.0, flops=0.0))
+            d["launches"] += 1
+            d["ms"] += a.elapsed_time(z)
+            d["flops"] += flops
+        return out
+
+
+def time_reference_triton(name, c, host, device, iters=5, warmup=3):
+    """The reference's own Triton kernels (installed copy under baseline/_ref) on the same layer and GPU."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if c["kind"] == "gpt_oss" or not os.path.isdir(os.path.join(ref_dir, "scattermoe")):
+        return None
+    sys.path.insert(0, ref_dir)
+    try:
+        import scattermoe as ref
+        bf = torch.bfloat16
+        m = ref.mlp.GLUMLP(c["d"], c["F"], c["E"], c["k"]).to(device=device, dtype=bf)
+        x, p, idx, dy = (host[n].to(device) for n in ("x", "p", "idx", "dy"))
+
+        def step():
+            xx, pp = x.detach().requires_grad_(), p.detach().requires_grad_()
+            y = m(xx, pp, idx)
+            torch.autograd.grad(y, [xx, pp, m.experts.weight, m.output_experts.weight], dy)
+        for _ in range(warmup):
+            step()
+        torch.cuda.synchronize()
+        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            step()
+        z.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(z) / iters
+        del m
+        torch.cuda.empty_cache()
+        return {"impl": "reference Triton kernels, same GPU, same inputs", "ms_per_step": ms,
+                "value": x.size(0) / (ms / 1e3), "unit": "tokens/s", "iters": iters}
+    except Exception as e:  # the comparison is informative; it must not break the benchmark line
+        return {"unavailable": "%s: %s" % (type(e).__name__, str(e)[:200])}
+    finally:
+        sys.path.remove(ref_dir)
+
+
+def cpu_reference(name, c, steps, warmup):
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import scattermoe_oracle as oracle
+    tokens = min(CPU_SAMPLE_TOKENS.get(name, 1024), c["T"])
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    b = oracle.DenseLoopBench(name if name in oracle.CONFIGS else "tiny_fp32_gelu", tokens, threads=cores)
+    threads = b.threads
+    times = []
+    for i in range(warmup + steps):
+        t = b.step()
+        if i >= warmup:
+            times.append(t)
+    sec = sum(times) / len(times)
+    return dict(value=tokens / sec, unit="tokens/s", cores=threads, kind="port",
+                sample="%d of %d tokens per step, fp32 dense per-expert loop, forward+backward, %.2f s/step"
+                       % (tokens, c["T"], sec)), sec
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--config", default="mixtral_8x7b", choices=sorted(LAYERS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-triton-ref", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    name, c = args.config, LAYERS[args.config]
+    metric = "moe_layer_fwd_bwd_tokens_per_s"
+    config = {"workload": name, "tokens_per_gpu": c["T"], "d_model": c["d"], "d_ffn": c["F"], "experts": c["E"],
+              "top_k": c["k"], "activation": c["kind"], "bias": c["bias"], "parallelism": "replicated layer, token shards",
+              "l2": "weights and activations exceed L2 (126 MB) every step"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        base, sec = cpu_reference(name, c, max(1, min(args.steps, 3)), min(args.warmup, 1))
+        line = {"impl": "reference", "metric": metric, "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+                "cpu_baseline": base,
+                "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the product has no CPU path); use --impl reference for the CPU baseline")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+    import scattermoe_b200 as sm
+    peaks = load_peaks()
+    layer, host = build_layer(name, c, c["T"], device, seed=rank)
+    dev_in = {n: t.to(device) for n, t in host.items()}
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def resident_step():
+        return run_step(c, layer, dev_in["x"].detach(), dev_in["p"].detach(), dev_in["idx"], dev_in["dy"])
+
+    out_host = dict(y=torch.empty_like(host["x"]).pin_memory(), dx=torch.empty_like(host["x"]).pin_memory())
+
+    def e2e_step():
+        x = host["x"].to(device, non_blocking=True)
+        p = host["p"].to(device, non_blocking=True)
+        idx = host["idx"].to(device, non_blocking=True)
+        dy = host["dy"].to(device, non_blocking=True)
+        y, dx = run_step(c, layer, x, p, idx, dy)
+        out_host["y"].copy_(y, non_blocking=True)
+        out_host["dx"].copy_(dx, non_blocking=True)
+
+    def timed(fn, steps, timer=None):
+        barrier()
+        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        z.record()
+        barrier()
+        ms = a.elapsed_time(z)
+        if dist is not None:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = t.item()
+        return ms
+
+    for _ in range(args.warmup):
+        resident_step()
+    sm.check_device_status(device)
+    timer = KernelTimer()
+    timer.install()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ms_total = timed(resident_step, args.steps)
+    clocks = sampler.stop() if sampler else None
+    timer.remove()
+    ksum = timer.summary()
+    tensor_core = sm.kernels.ops.last_path_was_tensor_core()
+
+    for _ in range(2):
+        e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+    sm.check_device_status(device)
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    ms_step = ms_total / args.steps
+    tokens_all = c["T"] * world
+    value = tokens_all / (ms_step / 1e3)
+    fwd_flops, fb_flops = layer_flops(c, c["T"])
+    h2d = sum(host[n].numel() * host[n].element_size() for n in ("x", "p", "idx", "dy"))
+    d2h = sum(t.numel() * t.element_size() for t in out_host.values())
+    dom = ksum.get("scatter2scatter", dict(launches=0, ms=0.0, flops=0.0))
+    achieved = dom["flops"] / (dom["ms"] / 1e3) / 1e12 if dom["ms"] > 0 else 0.0
+    peak = peaks["tflops_sustained"]
+    roofline = {"bound": "tensor", "kernel": "s2s_tc_kernel (scatter2scatter: 2 forward + 2 input-gradient launches per step)",
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_source": "%s, sustained bf16 (kernel timed inside a long step)" % peaks["source"],
+                "launches": dom["launches"], "avg_launch_ms": dom["ms"] / max(dom["launches"], 1), "traffic": None}
+    wg = ksum.get("group_bwd_w")
+    if wg and wg["ms"] > 0:
+        roofline["group_bwd_w"] = {"achieved": wg["flops"] / (wg["ms"] / 1e3) / 1e12, "launches": wg["launches"],
+                                   "avg_launch_ms": wg["ms"] / wg["launches"],
+                                   "frac": wg["flops"] / (wg["ms"] / 1e3) / 1e12 / peak}
+    line = {"metric": metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
+            "layer_tflops": fb_flops * world / (ms_step / 1e3) / 1e12,
+            "layer_frac_of_bf16_peak": fb_flops / (ms_step / 1e3) / 1e12 / peak,
+            "tensor_core_path": bool(tensor_core),
+            "roofline": roofline,
+            "e2e": {"value": tokens_all / (ms_e2e / args.steps / 1e3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps},
+            # kernels of this library per step: 3 routing (histogram, scan, scatter) + 4 scatter2scatter + 2
+            # group_bwd_w (+ 2 bias-gradient sums with biases) + 2 top-k reductions + gate gradient + group
+            "gpu_launches": (13 + (2 if c["bias"] else 0)) * args.steps,
+            "clocks": clocks}
+    if world == 1 and not args.no_triton_ref:
+        line["reference_gpu"] = time_reference_triton(name, c, host, device)
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"], _ = cpu_reference(name, c, 1, 0)
+    print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

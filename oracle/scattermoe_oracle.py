@@ -289,30 +289,35 @@ def make_routing(cfg_name: str, T: int, E: int, k: int, seed: int = 0):
     return p, idx
 
 
-def time_dense_loop(cfg_name: str, T_sample: int, threads: Optional[int] = None, seed: int = 0,
-                    backward: bool = True) -> Tuple[float, int]:
-    """Time one forward(+backward) of the dense per-expert loop on `T_sample` tokens of a
-    config, on the host cores. Returns (seconds, threads used). Used as the CPU baseline."""
-    import time
-    cfg = CONFIGS[cfg_name]
-    if threads:
-        torch.set_num_threads(threads)
-    d, F, E, k = cfg["d"], cfg["F"], cfg["E"], cfg["k"]
-    n1 = F if cfg["kind"] == "mlp_gelu" else 2 * F
-    g = torch.Generator().manual_seed(seed)
-    dt = torch.float32
-    x = torch.randn(T_sample, d, generator=g, dtype=dt)
-    w1 = torch.randn(E, d, n1, generator=g, dtype=dt) * 0.02
-    w2 = torch.randn(E, F, d, generator=g, dtype=dt) * 0.02
-    b1 = torch.randn(E, n1, generator=g, dtype=dt) * 0.02 if cfg["bias"] else None
-    b2 = torch.randn(E, d, generator=g, dtype=dt) * 0.02 if cfg["bias"] else None
-    p, idx = make_routing(cfg_name, T_sample, E, k, seed)
-    act = {"mlp_gelu": act_gelu, "glu_silu": act_glu_second_half, "gpt_oss": act_gpt_oss}[cfg["kind"]]
-    go = torch.randn(T_sample, d, generator=g, dtype=dt)
-    t0 = time.perf_counter()
-    if backward:
-        moe_mlp_forward_backward(x, p, idx, w1, w2, b1, b2, act, go, compute_dtype=dt)
-    else:
-        with torch.no_grad():
-            dense_moe_mlp(x, p, idx, w1, w2, b1, b2, act, dt)
-    return time.perf_counter() - t0, torch.get_num_threads()
+class DenseLoopBench:
+    """One layer of a benchmark config with fp32 weights, for timing the dense per-expert loop on the host
+    cores (the CPU baseline). Weights and inputs are built once; `step()` runs forward (+ backward)."""
+
+    def __init__(self, cfg_name: str, T_sample: int, threads: Optional[int] = None, seed: int = 0):
+        cfg = CONFIGS[cfg_name]
+        if threads:
+            torch.set_num_threads(threads)
+        self.threads = torch.get_num_threads()
+        d, F, E, k = cfg["d"], cfg["F"], cfg["E"], cfg["k"]
+        n1 = F if cfg["kind"] == "mlp_gelu" else 2 * F
+        g = torch.Generator().manual_seed(seed)
+        dt = torch.float32
+        self.x = torch.randn(T_sample, d, generator=g, dtype=dt)
+        self.w1 = torch.empty(E, d, n1, dtype=dt).normal_(0, 0.02, generator=g)
+        self.w2 = torch.empty(E, F, d, dtype=dt).normal_(0, 0.02, generator=g)
+        self.b1 = torch.randn(E, n1, generator=g, dtype=dt) * 0.02 if cfg["bias"] else None
+        self.b2 = torch.randn(E, d, generator=g, dtype=dt) * 0.02 if cfg["bias"] else None
+        self.p, self.idx = make_routing(cfg_name, T_sample, E, k, seed)
+        self.act = {"mlp_gelu": act_gelu, "glu_silu": act_glu_second_half, "gpt_oss": act_gpt_oss}[cfg["kind"]]
+        self.go = torch.randn(T_sample, d, generator=g, dtype=dt)
+
+    def step(self, backward: bool = True) -> float:
+        import time
+        t0 = time.perf_counter()
+        if backward:
+            moe_mlp_forward_backward(self.x, self.p, self.idx, self.w1, self.w2, self.b1, self.b2, self.act, self.go,
+                                     compute_dtype=torch.float32)
+        else:
+            with torch.no_grad():
+                dense_moe_mlp(self.x, self.p, self.idx, self.w1, self.w2, self.b1, self.b2, self.act, torch.float32)
+        return time.perf_counter() - t0

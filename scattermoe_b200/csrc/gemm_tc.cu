@@ -1,5 +1,840 @@
+// tcgen05 (5th-generation tensor core) grouped GEMM with fused row gather / scatter for sm_100a.
+//
+//   Y[out(m), :] = X[in(m), :] @ W[e(m)] (+ bias[e(m)])      for every position m of the expert-sorted slot list
+//
+// replaces the reference's Triton kernel _scatter2scatter (scattermoe/kernels/ops.py:55-118). Design:
+//   * persistent CTAs (one per SM) walk a tile list derived on the device from the expert offsets; a tile is
+//     128 sorted positions of ONE expert x BN output columns, so no row of another expert is ever multiplied
+//     (the reference instead masks rows and repeats the K loop per expert, ops.py:87-107);
+//   * warp-specialised roles: one warp feeds the expert's weight tiles with TMA (3-D tensor map over
+//     (inner, outer, expert), 128-byte swizzle), four warps gather the token rows with 16-byte cp.async
+//     straight into the same swizzled layout (no padded or grouped copy of X exists), one thread issues
+//     tcgen05.mma (128 x BN x 16, bf16/fp16 in, fp32 accumulators in tensor memory), four warps run the
+//     epilogue (tcgen05.ld -> bias -> convert -> scattered or grouped row stores);
+//   * the accumulator is double-buffered in tensor memory so the epilogue of one tile overlaps the MMAs of
+//     the next; a STAGES-deep shared-memory ring decouples loads from MMAs;
+//   * both weight orientations are native: K-contiguous (nn.Linear storage seen through .permute) and
+//     N-contiguous (gpt-oss storage, and the transposed views used for the input gradient), selected by the
+//     "major" bits of the UMMA descriptors.
+// Every wait is bounded (ptx.cuh): a protocol bug sets the status word and the kernel returns.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "ptx.cuh"
 #include "smoe_common.cuh"
+
 namespace smoe {
-int launch_s2s_tc(const S2SArgs&) { return SMOE_ERR_UNSUPPORTED; }
-int launch_wgrad_tc(const WGradArgs&) { return SMOE_ERR_UNSUPPORTED; }
+namespace tc {
+
+using namespace ptx;
+
+constexpr int BM = 128;            // sorted positions per tile (UMMA M)
+constexpr int BK = 64;             // K elements per pipeline stage: one 128-byte swizzle row of 16-bit data
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 320;   // warp 0 TMA, warp 1 MMA + TMEM, warps 2-5 row gather, warps 6-9 epilogue
+constexpr int MAX_E = 1024;
+constexpr int A_LAG = 2;           // cp.async groups kept in flight before a stage is published
+constexpr int A_STAGE_BYTES = BM * BK * 2;
+
+template <int BN> struct Cfg {
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int B_STAGE_BYTES = BN * BK * 2;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int SMEM_BYTES =
+      1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + BAR_BYTES + 2 * (MAX_E + 1) * 4;
+};
+
+struct S2SParams {
+  const uint8_t* X; int64_t x_row_bytes; int64_t x_rows;
+  const uint8_t* bias; int64_t bias_row_elems;
+  uint8_t* Y; int64_t y_row_bytes;
+  const int64_t* sorted_idx; const int64_t* offsets;
+  int64_t R;
+  int K, N, E, fan_out, x_grouped, y_grouped, is_bf16, bias_vec;
+  uint32_t idesc;
+  int32_t* status;
+};
+
+// Shared by all roles: offsets -> per-expert segment starts and the exclusive prefix of tiles per expert.
+__device__ __forceinline__ void build_tile_table(const int64_t* __restrict__ offsets, int64_t R, int E, int units_per_mtile,
+                                                 int32_t* seg_start, int32_t* tile_prefix, int tid, int nthreads) {
+  for (int e = tid; e < E; e += nthreads) {
+    int64_t v = offsets[e];
+    v = v < 0 ? 0 : (v > R ? R : v);
+    seg_start[e + 1] = static_cast<int32_t>(v);
+  }
+  if (tid == 0) seg_start[0] = 0;
+  __syncthreads();
+  if (tid < 32) {
+    const int per = (E + 31) / 32;
+    const int beg = min(tid * per, E), end = min(beg + per, E);
+    int sum = 0;
+    for (int e = beg; e < end; ++e) {
+      const int cnt = max(0, seg_start[e + 1] - seg_start[e]);
+      sum += ((cnt + BM - 1) / BM) * units_per_mtile;
+    }
+    int inc = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, inc, o);
+      if (tid >= o) inc += v;
+    }
+    int run = inc - sum;
+    for (int e = beg; e < end; ++e) {
+      tile_prefix[e] = run;
+      const int cnt = max(0, seg_start[e + 1] - seg_start[e]);
+      run += ((cnt + BM - 1) / BM) * units_per_mtile;
+    }
+    if (tid == 31) tile_prefix[E] = inc;
+  }
 }
+
+struct Tile { int e, m0, rows, n0; };
+
+__device__ __forceinline__ Tile decode_tile(int t, const int32_t* tile_prefix, const int32_t* seg_start, int E, int BN) {
+  int lo = 0, hi = E;
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (tile_prefix[mid] <= t) lo = mid; else hi = mid;
+  }
+  Tile tl;
+  tl.e = lo;
+  const int local = t - tile_prefix[lo];
+  const int cnt = seg_start[lo + 1] - seg_start[lo];
+  const int m_tiles = (cnt + BM - 1) / BM;
+  const int n_tile = local / m_tiles, m_tile = local - n_tile * m_tiles;
+  tl.m0 = seg_start[lo] + m_tile * BM;
+  tl.rows = min(BM, seg_start[lo + 1] - tl.m0);
+  tl.n0 = n_tile * BN;
+  return tl;
+}
+
+template <int BN, bool B_KMAJOR>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const S2SParams p) {
+  using C = Cfg<BN>;
+  constexpr int STAGES = C::STAGES;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + C::B_STAGE_BYTES));
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  int32_t* seg_start = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(bars) + C::BAR_BYTES);
+  int32_t* tile_prefix = seg_start + (MAX_E + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1 + 128);   // TMA thread (expect_tx) + 128 gather threads
+      mbar_init(empty_bar(s), 1);        // tcgen05.commit
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);        // tcgen05.commit
+      mbar_init(tempty_bar(b), 128);     // epilogue threads
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_w);
+  }
+  build_tile_table(p.offsets, p.R, p.E, n_tiles, seg_start, tile_prefix, tid, NUM_THREADS);
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  const int total_tiles = tile_prefix[p.E];
+
+  if (warp == 0) {
+    // ---------------- weight tiles: TMA producer -------------------------------------------------------
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, BN);
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait_warp(empty_bar(s), ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+        if (lane == 0) {
+          mbar_arrive_expect_tx(full_bar(s), C::B_STAGE_BYTES);
+          const uint32_t dst = smem_u32(sB + s * C::B_STAGE_BYTES);
+          if (B_KMAJOR) {
+            tma_load_3d(dst, &tmap_w, full_bar(s), kb * BK, tl.n0, tl.e);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_3d(dst + j * (64 * BK * 2), &tmap_w, full_bar(s), tl.n0 + j * 64, kb * BK, tl.e);
+          }
+        }
+        __syncwarp();
+      }
+    }
+    if (!ok) {  // give copies already in flight time to land before the CTA goes away
+      for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer -----------------------------------------------------------------------
+    int it = 0, tile_iter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
+      const int buf = tile_iter & 1;
+      const uint32_t tph = (tile_iter >> 1) & 1;
+      if (!mbar_wait_warp(tempty_bar(buf), tph ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait_warp(full_bar(s), ph, abort_flag, p.status, 3)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(sB + s * C::B_STAGE_BYTES);
+#pragma unroll
+          for (int j = 0; j < BK / UMMA_K; ++j) {
+            const uint64_t adesc = make_smem_desc_sw128(a_addr + j * (UMMA_K * 2), 16, 1024);
+            const uint64_t bdesc = B_KMAJOR ? make_smem_desc_sw128(b_addr + j * (UMMA_K * 2), 16, 1024)
+                                            : make_smem_desc_sw128(b_addr + j * (UMMA_K * 128), 64 * BK * 2, 1024);
+            umma_f16(d_tmem, adesc, bdesc, p.idesc, (kb | j) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(s));
+        }
+        __syncwarp();
+      }
+      if (ok && lane == 0) umma_commit(tfull_bar(buf));
+      __syncwarp();
+    }
+  } else if (warp < 6) {
+    // ---------------- token rows: cp.async gather into the swizzled A tile -----------------------------
+    const int ptid = tid - 64;
+    const int chunk = ptid & 7;          // 16-byte chunk of the 128-byte K slice
+    const int row_base = ptid >> 3;      // rows row_base + 16*i
+    const uint32_t dst_off = row_base * 128 + ((chunk ^ (row_base & 7)) << 4);
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, BN);
+      const uint8_t* rowptr[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int r = row_base + 16 * i;
+        const uint8_t* ptr = nullptr;
+        if (r < tl.rows) {
+          const int64_t m = tl.m0 + r;
+          const int64_t in = p.x_grouped ? m : p.sorted_idx[m] / p.fan_out;
+          if (in >= 0 && in < p.x_rows) ptr = p.X + in * p.x_row_bytes + chunk * 16;
+        }
+        rowptr[i] = ptr;
+      }
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait_warp(empty_bar(s), ph ^ 1, abort_flag, p.status, 4)) { ok = false; break; }
+        const bool k_ok = (kb * BK + chunk * 8) < p.K;
+        const uint32_t dst = smem_u32(sA + s * A_STAGE_BYTES) + dst_off;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const bool v = k_ok && rowptr[i] != nullptr;
+          cp_async16(dst + i * 2048, v ? rowptr[i] + static_cast<int64_t>(kb) * (BK * 2) : p.X, v ? 16u : 0u);
+        }
+        cp_async_commit();
+        if (it >= A_LAG) {
+          cp_async_wait<A_LAG>();
+          fence_proxy_async_smem();
+          mbar_arrive(full_bar((it - A_LAG) % STAGES));
+        }
+      }
+    }
+    cp_async_wait<0>();
+    fence_proxy_async_smem();
+    if (ok) {
+      for (int j = max(0, it - A_LAG); j < it; ++j) mbar_arrive(full_bar(j % STAGES));
+    }
+  } else {
+    // ---------------- epilogue: TMEM -> registers -> bias -> 16-bit -> global rows ----------------------
+    const int q = warp & 3;              // TMEM lane quarter this warp may read
+    const int r = q * 32 + lane;
+    int tile_iter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, BN);
+      const int buf = tile_iter & 1;
+      const uint32_t tph = (tile_iter >> 1) & 1;
+      bool valid = r < tl.rows;
+      int64_t out_row = 0;
+      if (valid) {
+        const int64_t m = tl.m0 + r;
+        out_row = p.y_grouped ? m : p.sorted_idx[m];
+        valid = out_row >= 0 && out_row < p.R;
+      }
+      uint8_t* yrow = p.Y + out_row * p.y_row_bytes;
+      const uint8_t* brow = p.bias ? p.bias + static_cast<int64_t>(tl.e) * p.bias_row_elems * 2 : nullptr;
+      if (!mbar_wait_warp(tfull_bar(buf), tph, abort_flag, p.status, 5)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        const int n = tl.n0 + c * 32;
+        if (n >= p.N) break;
+        uint32_t acc[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, acc);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int nn = n + g * 8;
+            if (nn < p.N) {
+              float v[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(acc[g * 8 + j]);
+              if (brow) {
+                if (p.bias_vec) {
+                  const uint4 bv = __ldg(reinterpret_cast<const uint4*>(brow + nn * 2));
+                  const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    float lo, hi;
+                    if (p.is_bf16) {
+                      const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&bw[j]);
+                      lo = __low2float(h); hi = __high2float(h);
+                    } else {
+                      const __half2 h = *reinterpret_cast<const __half2*>(&bw[j]);
+                      lo = __low2float(h); hi = __high2float(h);
+                    }
+                    v[2 * j] += lo; v[2 * j + 1] += hi;
+                  }
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    const uint16_t raw = __ldg(reinterpret_cast<const uint16_t*>(brow + (nn + j) * 2));
+                    v[j] += p.is_bf16 ? __bfloat162float(__ushort_as_bfloat16(raw)) : __half2float(__ushort_as_half(raw));
+                  }
+                }
+              }
+              uint32_t o[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                if (p.is_bf16) {
+                  const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                  o[j] = *reinterpret_cast<const uint32_t*>(&h);
+                } else {
+                  const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+                  o[j] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+              }
+              *reinterpret_cast<uint4*>(yrow + nn * 2) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(tempty_bar(buf));
+    }
+  }
+
+  // ---------------- teardown ---------------------------------------------------------------------------
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Weight gradient: DWt[e] (N x K) = DY_e^T (N x rows_e) . X_e (rows_e x K), replacing the reference's _groupXtY
+// (scattermoe/kernels/ops.py:247-366). Token rows are the contraction dimension, so both operands are fed
+// "MN-major": the DY slab by TMA (2-D map over (feature, row)), the X slab by cp.async row gather, which also
+// serves the still un-grouped input (row = slot / fan_out) and zero-fills the rows past the segment end, the
+// only masking the ragged segments need. A tile is 128 DY features x BNW X features of one expert.
+struct WGradParams {
+  const uint8_t* X; int64_t x_row_bytes; int64_t x_rows;
+  uint8_t* DW; int64_t dw_e_bytes; int64_t dw_row_bytes;
+  const int64_t* gather_idx; const int64_t* offsets;
+  int64_t R;
+  int K, N, E, fan_out, is_bf16;
+  uint32_t idesc;
+  int32_t* status;
+};
+
+template <int BNW>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const WGradParams p) {
+  using C = Cfg<BNW>;
+  constexpr int STAGES = C::STAGES;
+  constexpr int CPR = BNW / 8;          // 16-byte chunks per gathered row
+  constexpr int RPP = 128 / CPR;        // rows covered by the 128 gather threads in one pass
+  constexpr int NI = BK / RPP;          // passes per stage
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + C::B_STAGE_BYTES));
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  int32_t* seg_start = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(bars) + C::BAR_BYTES);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_tiles = (p.N + BM - 1) / BM;
+  const int k_tiles = (p.K + BNW - 1) / BNW;
+  const int tiles_per_e = n_tiles * k_tiles;
+  const int total_tiles = p.E * tiles_per_e;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1 + 128);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 128);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_dy);
+    seg_start[0] = 0;
+  }
+  for (int e = tid; e < p.E; e += NUM_THREADS) {
+    int64_t v = p.offsets[e];
+    v = v < 0 ? 0 : (v > p.R ? p.R : v);
+    seg_start[e + 1] = static_cast<int32_t>(v);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), C::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+
+  // tile t -> expert, DY-feature tile, X-feature tile (fastest), and the expert's row segment
+  auto decode = [&](int t, int& e, int& n0, int& k0, int& m_beg, int& m_end) {
+    e = t / tiles_per_e;
+    const int rem = t - e * tiles_per_e;
+    const int nt = rem / k_tiles;
+    n0 = nt * BM;
+    k0 = (rem - nt * k_tiles) * BNW;
+    m_beg = seg_start[e];
+    m_end = max(m_beg, seg_start[e + 1]);
+  };
+
+  if (warp == 0) {
+    // ---------------- DY slabs: TMA producer --------------------------------------------------------------
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int e, n0, k0, m_beg, m_end;
+      decode(t, e, n0, k0, m_beg, m_end);
+      const int nchunks = (m_end - m_beg + BK - 1) / BK;
+      for (int c = 0; c < nchunks; ++c, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait_warp(empty_bar(s), ph ^ 1, abort_flag, p.status, 11)) { ok = false; break; }
+        if (lane == 0) {
+          mbar_arrive_expect_tx(full_bar(s), A_STAGE_BYTES);
+          const uint32_t dst = smem_u32(sA + s * A_STAGE_BYTES);
+          tma_load_2d(dst, &tmap_dy, full_bar(s), n0, m_beg + c * BK);
+          tma_load_2d(dst + 64 * BK * 2, &tmap_dy, full_bar(s), n0 + 64, m_beg + c * BK);
+        }
+        __syncwarp();
+      }
+    }
+    if (!ok) {
+      for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer --------------------------------------------------------------------------
+    int it = 0, tile_iter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int e, n0, k0, m_beg, m_end;
+      decode(t, e, n0, k0, m_beg, m_end);
+      const int nchunks = (m_end - m_beg + BK - 1) / BK;
+      if (nchunks == 0) continue;       // the epilogue writes zeros, no accumulator involved
+      const int buf = tile_iter & 1;
+      const uint32_t tph = (tile_iter >> 1) & 1;
+      if (!mbar_wait_warp(tempty_bar(buf), tph ^ 1, abort_flag, p.status, 12)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + buf * BNW;
+      for (int c = 0; c < nchunks; ++c, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait_warp(full_bar(s), ph, abort_flag, p.status, 13)) { ok = false; break; }
+        tc_fence_after_sync();
+        if (lane == 0) {
+          const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
+          const uint32_t b_addr = smem_u32(sB + s * C::B_STAGE_BYTES);
+#pragma unroll
+          for (int j = 0; j < BK / UMMA_K; ++j) {
+            const uint64_t adesc = make_smem_desc_sw128(a_addr + j * (UMMA_K * 128), 64 * BK * 2, 1024);
+            const uint64_t bdesc = make_smem_desc_sw128(b_addr + j * (UMMA_K * 128), 64 * BK * 2, 1024);
+            umma_f16(d_tmem, adesc, bdesc, p.idesc, (c | j) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar(s));
+        }
+        __syncwarp();
+      }
+      if (ok && lane == 0) umma_commit(tfull_bar(buf));
+      __syncwarp();
+      ++tile_iter;
+    }
+  } else if (warp < 6) {
+    // ---------------- X slabs: cp.async row gather (zero-fill past the segment end) ----------------------
+    const int ptid = tid - 64;
+    const int chunk = ptid % CPR;
+    const int row_base = ptid / CPR;                 // rows row_base + RPP*i
+    const uint32_t box_off = (chunk >> 3) * (64 * BK * 2);
+    // lanes 0..15 of each warp fetch the source-row offsets the warp needs for one stage
+    const int rows_per_warp_pass = 32 / CPR == 0 ? 1 : 32 / CPR;   // 1 (BNW=256) or 2 (BNW=128)
+    const int wrow0 = (warp - 2) * rows_per_warp_pass;
+    const int my_half = (rows_per_warp_pass == 2) ? (lane >> 4) : 0;
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int e, n0, k0, m_beg, m_end;
+      decode(t, e, n0, k0, m_beg, m_end);
+      const int nchunks = (m_end - m_beg + BK - 1) / BK;
+      const bool k_ok = (k0 + chunk * 8) < p.K;
+      const int64_t col_bytes = static_cast<int64_t>(k0 + chunk * 8) * 2;
+      for (int c = 0; c < nchunks; ++c, ++it) {
+        // source offsets of this stage's rows: lane l < 16 looks up row (half h, pass i)
+        long long my_off = -1;
+        if (lane < 16) {
+          const int h = (rows_per_warp_pass == 2) ? (lane >> 3) : 0;
+          const int i = (rows_per_warp_pass == 2) ? (lane & 7) : lane;
+          if (i < NI) {
+            const int64_t m = static_cast<int64_t>(m_beg) + c * BK + wrow0 + h + RPP * i;
+            if (m < m_end) {
+              const int64_t row = p.gather_idx ? p.gather_idx[m] / p.fan_out : m;
+              if (row >= 0 && row < p.x_rows) my_off = row * p.x_row_bytes;
+            }
+          }
+        }
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait_warp(empty_bar(s), ph ^ 1, abort_flag, p.status, 14)) { ok = false; break; }
+        const uint32_t dst = smem_u32(sB + s * C::B_STAGE_BYTES) + box_off;
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+          const int src_lane = (rows_per_warp_pass == 2) ? (my_half * 8 + i) : i;
+          const long long off = __shfl_sync(0xffffffffu, my_off, src_lane);
+          const bool v = k_ok && off >= 0;
+          const int row = row_base + RPP * i;     // token row inside the 64-row slab
+          cp_async16(dst + row * 128 + (((chunk & 7) ^ (row & 7)) << 4), v ? p.X + off + col_bytes : p.X,
+                     v ? 16u : 0u);
+        }
+        cp_async_commit();
+        if (it >= A_LAG) {
+          cp_async_wait<A_LAG>();
+          fence_proxy_async_smem();
+          mbar_arrive(full_bar((it - A_LAG) % STAGES));
+        }
+      }
+    }
+    cp_async_wait<0>();
+    fence_proxy_async_smem();
+    if (ok) {
+      for (int j = max(0, it - A_LAG); j < it; ++j) mbar_arrive(full_bar(j % STAGES));
+    }
+  } else {
+    // ---------------- epilogue: rows = DY features, columns = X features -----------------------------------
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    int tile_iter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int e, n0, k0, m_beg, m_end;
+      decode(t, e, n0, k0, m_beg, m_end);
+      const int nchunks = (m_end - m_beg + BK - 1) / BK;
+      const bool valid = (n0 + r) < p.N;
+      uint8_t* drow = p.DW + static_cast<int64_t>(e) * p.dw_e_bytes + static_cast<int64_t>(n0 + r) * p.dw_row_bytes;
+      if (nchunks == 0) {
+        if (valid) {
+          for (int kk = k0; kk < min(k0 + BNW, p.K); kk += 8)
+            *reinterpret_cast<uint4*>(drow + kk * 2) = make_uint4(0, 0, 0, 0);
+        }
+        continue;
+      }
+      const int buf = tile_iter & 1;
+      const uint32_t tph = (tile_iter >> 1) & 1;
+      if (!mbar_wait_warp(tfull_bar(buf), tph, abort_flag, p.status, 15)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BNW;
+#pragma unroll 1
+      for (int c = 0; c < BNW / 32; ++c) {
+        const int kk0 = k0 + c * 32;
+        if (kk0 >= p.K) break;
+        uint32_t acc[32];
+        tmem_ld_32x32b_x32(taddr + c * 32, acc);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int kk = kk0 + g * 8;
+            if (kk < p.K) {
+              uint32_t o[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float lo = __uint_as_float(acc[g * 8 + 2 * j]), hi = __uint_as_float(acc[g * 8 + 2 * j + 1]);
+                if (p.is_bf16) {
+                  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                  o[j] = *reinterpret_cast<const uint32_t*>(&h);
+                } else {
+                  const __half2 h = __floats2half2_rn(lo, hi);
+                  o[j] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+              }
+              *reinterpret_cast<uint4*>(drow + kk * 2) = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(tempty_bar(buf));
+      ++tile_iter;
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// Db[e][n] = sum of DY[m][n] over expert e's rows (the bias gradient, ops.py:358-366). HBM-bound column sum:
+// a block owns one expert and 64 columns, 8 row lanes x 32 column pairs, fp32 accumulation.
+template <typename T2, bool IS_BF16>
+__global__ void __launch_bounds__(256)
+bias_grad_kernel(const uint8_t* __restrict__ DY, int64_t dy_row_bytes, const int64_t* __restrict__ offsets, int64_t R,
+                 uint8_t* __restrict__ Db, int64_t sdbe, int64_t sdbn, int N) {
+  __shared__ float red[8][64];
+  const int e = blockIdx.y;
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int n = blockIdx.x * 64 + cx * 2;
+  int64_t beg = e ? offsets[e - 1] : 0, end = offsets[e];
+  beg = beg < 0 ? 0 : (beg > R ? R : beg);
+  end = end < beg ? beg : (end > R ? R : end);
+  float a0 = 0.f, a1 = 0.f;
+  if (n < N) {
+    for (int64_t m = beg + ry; m < end; m += 8) {
+      const T2 v = *reinterpret_cast<const T2*>(DY + m * dy_row_bytes + n * 2);
+      a0 += __low2float(v);
+      a1 += __high2float(v);
+    }
+  }
+  red[ry][cx * 2] = a0;
+  red[ry][cx * 2 + 1] = a1;
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += red[i][threadIdx.x];
+    const int nn = blockIdx.x * 64 + threadIdx.x;
+    if (nn < N) {
+      uint16_t* out = reinterpret_cast<uint16_t*>(Db) + static_cast<int64_t>(e) * sdbe + nn * sdbn;
+      if (IS_BF16) *out = __bfloat16_as_ushort(__float2bfloat16_rn(s));
+      else *out = __half_as_ushort(__float2half_rn(s));
+    }
+  }
+}
+
+// ---- host side -----------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// rank-3 map over (inner, outer, expert) of 16-bit elements with a 128-byte swizzled box.
+static bool encode_map3(CUtensorMap* map, bool bf16, const void* base, uint64_t d0, uint64_t d1, uint64_t d2,
+                        uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[3] = {d0, d1, d2};
+  const cuuint64_t strides[2] = {stride1_bytes, stride2_bytes};
+  const cuuint32_t box[3] = {box0, box1, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS;
+}
+
+static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <int BN, bool B_KMAJOR>
+static int launch_s2s_cfg(const CUtensorMap& map, const S2SParams& p, int grid, cudaStream_t stream) {
+  static std::mutex mu;
+  static bool configured[64] = {false};
+  int dev = 0;
+  SMOE_CUDA(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+      SMOE_CUDA(cudaFuncSetAttribute(s2s_tc_kernel<BN, B_KMAJOR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg<BN>::SMEM_BYTES));
+      if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+  }
+  s2s_tc_kernel<BN, B_KMAJOR><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(map, p);
+  SMOE_LAUNCH_CHECK();
+  return SMOE_OK;
+}
+
+// rank-2 map over (feature, row) of 16-bit elements, 64 x 64 box, 128-byte swizzle.
+static bool encode_map2(CUtensorMap* map, bool bf16, const void* base, uint64_t d0, uint64_t d1,
+                        uint64_t stride1_bytes) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {d0, d1};
+  const cuuint64_t strides[1] = {stride1_bytes};
+  const cuuint32_t box[2] = {64, BK};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                         const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS;
+}
+
+template <int BNW>
+static int launch_wgrad_cfg(const CUtensorMap& map, const WGradParams& p, int grid, cudaStream_t stream) {
+  static std::mutex mu;
+  static bool configured[64] = {false};
+  int dev = 0;
+  SMOE_CUDA(cudaGetDevice(&dev));
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+      SMOE_CUDA(cudaFuncSetAttribute(wgrad_tc_kernel<BNW>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     Cfg<BNW>::SMEM_BYTES));
+      if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+  }
+  wgrad_tc_kernel<BNW><<<grid, NUM_THREADS, Cfg<BNW>::SMEM_BYTES, stream>>>(map, p);
+  SMOE_LAUNCH_CHECK();
+  return SMOE_OK;
+}
+
+}  // namespace tc
+
+int launch_s2s_tc(const S2SArgs& a) {
+  using namespace tc;
+  if (a.dtype != SMOE_BF16 && a.dtype != SMOE_F16) return SMOE_ERR_UNSUPPORTED;
+  if (a.K < 8 || a.K % 8 || a.N % 8 || a.E > MAX_E) return SMOE_ERR_UNSUPPORTED;
+  if (a.sxk != 1 || a.sxm % 8 || !al16(a.X)) return SMOE_ERR_UNSUPPORTED;
+  if (a.syn != 1 || a.sym % 8 || !al16(a.Y)) return SMOE_ERR_UNSUPPORTED;
+  if (a.bias && a.sbn != 1) return SMOE_ERR_UNSUPPORTED;
+  if (!al16(a.W) || a.swe % 8 || a.swe < 0) return SMOE_ERR_UNSUPPORTED;
+  const bool k_major = (a.swk == 1 && a.swn % 8 == 0 && a.swn >= a.K);
+  const bool n_major = (a.swn == 1 && a.swk % 8 == 0 && a.swk >= a.N);
+  if (!k_major && !n_major) return SMOE_ERR_UNSUPPORTED;
+  DeviceInfo di;
+  if (int rc = get_device_info(&di)) return rc;
+  if (di.cc_major != 10) return SMOE_ERR_UNSUPPORTED;
+
+  const bool bf16 = a.dtype == SMOE_BF16;
+  const int BN = a.N > 128 ? 256 : 128;
+  CUtensorMap map;
+  const uint64_t e_stride = (a.E > 1 ? static_cast<uint64_t>(a.swe) : static_cast<uint64_t>(a.K) * a.N) * 2;
+  bool ok;
+  if (k_major)
+    ok = encode_map3(&map, bf16, a.W, a.K, a.N, a.E, static_cast<uint64_t>(a.swn) * 2, e_stride, BK, BN);
+  else
+    ok = encode_map3(&map, bf16, a.W, a.N, a.K, a.E, static_cast<uint64_t>(a.swk) * 2, e_stride, 64, BK);
+  if (!ok) return SMOE_ERR_UNSUPPORTED;
+
+  S2SParams p;
+  p.X = static_cast<const uint8_t*>(a.X); p.x_row_bytes = a.sxm * 2; p.x_rows = a.x_rows;
+  p.bias = static_cast<const uint8_t*>(a.bias); p.bias_row_elems = a.sbe;
+  p.Y = static_cast<uint8_t*>(a.Y); p.y_row_bytes = a.sym * 2;
+  p.sorted_idx = a.sorted_idx; p.offsets = a.offsets; p.R = a.R;
+  p.K = a.K; p.N = a.N; p.E = a.E; p.fan_out = a.fan_out; p.x_grouped = a.x_grouped; p.y_grouped = a.y_grouped;
+  p.is_bf16 = bf16 ? 1 : 0;
+  p.bias_vec = (a.bias && al16(a.bias) && a.sbe % 8 == 0) ? 1 : 0;
+  p.idesc = make_idesc_f16(bf16, false, !k_major, BM, BN);
+  p.status = a.status;
+
+  const int64_t max_tiles = (cdiv64(a.R, BM) + a.E) * cdiv(a.N, BN);
+  const int grid = static_cast<int>(max_tiles < di.sm_count ? max_tiles : di.sm_count);
+  if (BN == 256)
+    return k_major ? launch_s2s_cfg<256, true>(map, p, grid, a.stream) : launch_s2s_cfg<256, false>(map, p, grid, a.stream);
+  return k_major ? launch_s2s_cfg<128, true>(map, p, grid, a.stream) : launch_s2s_cfg<128, false>(map, p, grid, a.stream);
+}
+
+int launch_wgrad_tc(const WGradArgs& a) {
+  using namespace tc;
+  if (a.dtype != SMOE_BF16 && a.dtype != SMOE_F16) return SMOE_ERR_UNSUPPORTED;
+  if (a.K % 8 || a.N % 8 || a.E > MAX_E || a.R == 0) return SMOE_ERR_UNSUPPORTED;
+  if (a.sxk != 1 || a.sxm % 8 || !al16(a.X)) return SMOE_ERR_UNSUPPORTED;
+  if (a.sdyn != 1 || a.sdym % 8 || a.sdym < a.N || !al16(a.DY)) return SMOE_ERR_UNSUPPORTED;
+  if (a.sdwk != 1 || a.sdwn % 8 || a.sdwe % 8 || !al16(a.DW)) return SMOE_ERR_UNSUPPORTED;
+  DeviceInfo di;
+  if (int rc = get_device_info(&di)) return rc;
+  if (di.cc_major != 10) return SMOE_ERR_UNSUPPORTED;
+  const bool bf16 = a.dtype == SMOE_BF16;
+  CUtensorMap map;
+  if (!encode_map2(&map, bf16, a.DY, a.N, a.R, static_cast<uint64_t>(a.sdym) * 2)) return SMOE_ERR_UNSUPPORTED;
+  const int BNW = a.K > 128 ? 256 : 128;
+  WGradParams p;
+  p.X = static_cast<const uint8_t*>(a.X); p.x_row_bytes = a.sxm * 2; p.x_rows = a.x_rows;
+  p.DW = static_cast<uint8_t*>(a.DW); p.dw_e_bytes = a.sdwe * 2; p.dw_row_bytes = a.sdwn * 2;
+  p.gather_idx = a.gather_idx; p.offsets = a.offsets; p.R = a.R;
+  p.K = a.K; p.N = a.N; p.E = a.E; p.fan_out = a.fan_out; p.is_bf16 = bf16 ? 1 : 0;
+  p.idesc = make_idesc_f16(bf16, true, true, BM, BNW);
+  p.status = a.status;
+  const int64_t total = static_cast<int64_t>(a.E) * cdiv(a.N, BM) * cdiv(a.K, BNW);
+  const int grid = static_cast<int>(total < di.sm_count ? total : di.sm_count);
+  int rc = (BNW == 256) ? launch_wgrad_cfg<256>(map, p, grid, a.stream) : launch_wgrad_cfg<128>(map, p, grid, a.stream);
+  if (rc != SMOE_OK) return rc;
+  if (a.Db) {
+    dim3 g(static_cast<unsigned>(cdiv(a.N, 64)), static_cast<unsigned>(a.E));
+    if (bf16)
+      bias_grad_kernel<__nv_bfloat162, true><<<g, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.DY), a.sdym * 2, a.offsets,
+                                                                     a.R, static_cast<uint8_t*>(a.Db), a.sdbe, a.sdbn, a.N);
+    else
+      bias_grad_kernel<__half2, false><<<g, 256, 0, a.stream>>>(static_cast<const uint8_t*>(a.DY), a.sdym * 2, a.offsets, a.R,
+                                                               static_cast<uint8_t*>(a.Db), a.sdbe, a.sdbn, a.N);
+    SMOE_LAUNCH_CHECK();
+  }
+  return SMOE_OK;
+}
+
+}  // namespace smoe

@@ -10,7 +10,11 @@ group_bwd_W, ParallelLinear forward/backward, MLP, GLUMLP and the two Hugging Fa
 not of a restatement. Inputs come from seeded torch generators and are stored beside the
 outputs, so the tests never need the reference at run time.
 
-bf16 tensors are stored widened to float32 (exact), index tensors as int64.
+Cases flagged `bf16` hold inputs that are exactly representable in bfloat16 (generated, rounded to bf16,
+widened back to float32) and outputs the reference computed from them in float32: the Triton interpreter
+of this Triton release does not store bf16 tensors correctly, so the reference cannot be run in bf16 on a
+CPU. An implementation under test runs those cases in bf16 and is compared with the bf16 tolerance
+(rtol 2e-2 / atol 2e-2). Index tensors are stored as int64.
 """
 import argparse
 import os
@@ -83,17 +87,18 @@ def main():
                     se, ss, off = scattermoe.flatten_sort_count(idx, num_experts=E)
                     rows = T * k if x_grouped else T
                     kk = 1 if x_grouped else k
-                    X = torch.randn(rows, K, generator=gen).to(dtype)
+                    X = torch.randn(rows, K, generator=gen).to(dtype).float()
                     n_major = (case % 2 == 0)
                     if n_major:
-                        W = (torch.randn(E, K, N, generator=gen) * 0.1).to(dtype)
+                        W = (torch.randn(E, K, N, generator=gen) * 0.1).to(dtype).float()
                     else:
-                        W = (torch.randn(E, N, K, generator=gen) * 0.1).to(dtype).permute(0, 2, 1)
-                    b = (torch.randn(E, N, generator=gen) * 0.1).to(dtype) if case % 4 < 2 else None
+                        W = (torch.randn(E, N, K, generator=gen) * 0.1).to(dtype).float().permute(0, 2, 1)
+                    b = (torch.randn(E, N, generator=gen) * 0.1).to(dtype).float() if case % 4 < 2 else None
                     Y = ops.scatter2scatter(X, W, se, ss, kk, b=b, x_grouped=x_grouped, y_grouped=y_grouped)
                     save(f"s2s_{case}", X=npy(X), W=npy(W.contiguous()), b=npy(b), expert_idxs=npy(idx),
                          E=np.int64(E), k=np.int64(kk), x_grouped=np.bool_(x_grouped), y_grouped=np.bool_(y_grouped),
-                         w_n_contiguous=np.bool_(n_major), bf16=np.bool_(dtype == torch.bfloat16), Y=npy(Y))
+                         w_n_contiguous=np.bool_(n_major), bf16=np.bool_(dtype == torch.bfloat16), Y=npy(Y),
+                         sorted_expert_idxs=npy(se), sorted_scattered_idxs=npy(ss), expert_offsets=npy(off))
                     case += 1
 
     # ---- group ------------------------------------------------------------------------
@@ -103,11 +108,12 @@ def main():
         gen = torch.Generator().manual_seed(200 + i)
         w, idx = routing(gen, T, E, k)
         se, ss, off = scattermoe.flatten_sort_count(idx, num_experts=E)
-        A = torch.randn(T, K, generator=gen).to(dtype)
-        coeff = w.to(dtype).flatten() if with_coeff else None
+        A = torch.randn(T, K, generator=gen).to(dtype).float()
+        coeff = w.to(dtype).float().flatten() if with_coeff else None
         Y = ops.group(A, ss, coeff=coeff, fan_out=k)
         save(f"group_{i}", A=npy(A), coeff=npy(coeff), expert_idxs=npy(idx), E=np.int64(E), k=np.int64(k),
-             bf16=np.bool_(dtype == torch.bfloat16), Y=npy(Y))
+             bf16=np.bool_(dtype == torch.bfloat16), Y=npy(Y),
+             sorted_expert_idxs=npy(se), sorted_scattered_idxs=npy(ss), expert_offsets=npy(off))
 
     # ---- group_bwd_W (with an empty expert and bias) ------------------------------------
     for i, (dtype, T, E, k, K, N, has_bias) in enumerate([(torch.float32, 61, 8, 2, 40, 72, True),
@@ -116,23 +122,23 @@ def main():
         gen = torch.Generator().manual_seed(300 + i)
         _, idx = routing(gen, T, E, k, skew=True)
         se, ss, off = scattermoe.flatten_sort_count(idx, num_experts=E)
-        X = torch.randn(T * k, K, generator=gen).to(dtype)
-        DY = torch.randn(T * k, N, generator=gen).to(dtype)
+        X = torch.randn(T * k, K, generator=gen).to(dtype).float()
+        DY = torch.randn(T * k, N, generator=gen).to(dtype).float()
         DW, Db = ops.group_bwd_W(DY, X, off, E, has_bias=has_bias)
         save(f"gbw_{i}", X=npy(X), DY=npy(DY), expert_idxs=npy(idx), E=np.int64(E),
-             bf16=np.bool_(dtype == torch.bfloat16), DW=npy(DW.contiguous()), Db=npy(Db))
+             bf16=np.bool_(dtype == torch.bfloat16), DW=npy(DW.contiguous()), Db=npy(Db),
+             sorted_expert_idxs=npy(se), sorted_scattered_idxs=npy(ss), expert_offsets=npy(off))
 
     # ---- MLP / GLUMLP forward + backward ------------------------------------------------
     def run_module(name, mod, T, E, k, d, dtype, seed, renorm):
         gen = torch.Generator().manual_seed(seed)
         w, idx = routing(gen, T, E, k, renorm=renorm)
-        w = w.to(dtype).requires_grad_()
-        X = torch.randn(T, d, generator=gen).to(dtype).requires_grad_()
-        DY = torch.randn(T, d, generator=gen).to(dtype)
+        w = w.to(dtype).float().requires_grad_()
+        X = torch.randn(T, d, generator=gen).to(dtype).float().requires_grad_()
+        DY = torch.randn(T, d, generator=gen).to(dtype).float()
         with torch.no_grad():
             for p in mod.parameters():
-                p.copy_(torch.randn(p.shape, generator=gen) * (0.05 if p.dim() == 3 else 0.02))
-        mod = mod.to(dtype)
+                p.copy_((torch.randn(p.shape, generator=gen) * (0.05 if p.dim() == 3 else 0.02)).to(dtype).float())
         Y = mod(X, w, idx)
         params = dict(mod.named_parameters())
         leaves = [X, w] + list(params.values())

@@ -1,0 +1,76 @@
+"""The C-ABI shared library: it loads without a GPU, exports every symbol the header declares, and rejects
+malformed arguments with status codes (no compute call is made here)."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+import scattermoe_b200
+from scattermoe_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "scattermoe_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(smoe_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported_and_bound():
+    lib = _lib.load()
+    names = declared_symbols()
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(lib, n), "library does not export %s" % n
+        assert n in _lib.SIGNATURES, "no ctypes signature for %s" % n
+    assert sorted(_lib.SIGNATURES) == names
+
+
+def test_version_and_library_location():
+    assert _lib.load().smoe_version() == 1
+    path = scattermoe_b200.library_path()
+    assert os.path.dirname(path) == os.path.join(ROOT, "scattermoe_b200"), "the library must live in-tree"
+
+
+def test_argument_validation_needs_no_device():
+    lib = _lib.load()
+    # E out of range, negative R: rejected before any CUDA call
+    assert lib.smoe_sort_count(None, 4, 0, None, None, None, None, 0, None) == _lib.SMOE_ERR_BAD_ARG
+    assert "E=0" in _lib.last_error()
+    assert lib.smoe_sort_count(None, -1, 8, None, None, None, None, 0, None) == _lib.SMOE_ERR_BAD_ARG
+    assert lib.smoe_sort_count_workspace_bytes(32768, 8) >= 16 * 8 * 4
+    assert lib.smoe_offsets_from_sorted(None, -5, 8, None, None) == _lib.SMOE_ERR_BAD_ARG
+    # unknown dtype
+    rc = lib.smoe_group(256, 4, 4, 1, 256, None, 1, 256, 4, 1, 4, 4, 7, None)   # never dereferenced
+    assert rc == _lib.SMOE_ERR_BAD_ARG and "dtype" in _lib.last_error()
+    # index length must be rows * fan_out (reference assertion, ops.py:124-125)
+    rc = lib.smoe_scatter2scatter(None, 3, 8, 1, None, 0, 0, 0, None, 0, 0, None, 8, 1, None, None, None,
+                                  7, 8, 8, 2, 2, 0, 0, 0, 0, 0, None, None)
+    assert rc == _lib.SMOE_ERR_BAD_ARG
+    with pytest.raises(AssertionError):
+        _lib.check(rc, "smoe_scatter2scatter")
+
+
+def test_cpu_tensors_fail_loudly():
+    """No CPU fallback: handing CPU tensors to any op is an error, not a slow path."""
+    from scattermoe_b200.kernels import ops
+    idx = torch.zeros(4, dtype=torch.int64)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        scattermoe_b200.flatten_sort_count(torch.zeros(2, 2, dtype=torch.int64), 4)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.scatter2scatter(torch.zeros(4, 8), torch.zeros(2, 8, 8), idx, idx, 1)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.group(torch.zeros(4, 8), idx)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.group_bwd_W(torch.zeros(4, 8), torch.zeros(4, 8), torch.zeros(2, dtype=torch.int64), 2)
+
+
+def test_missing_library_is_an_import_error(monkeypatch, tmp_path):
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib._build, "LIB_PATH", str(tmp_path / "nope.so"))
+    monkeypatch.setattr(_lib._build, "build", lambda *a, **k: (_ for _ in ()).throw(RuntimeError("nvcc not found")))
+    with pytest.raises(ImportError, match="no fallback"):
+        _lib.load()

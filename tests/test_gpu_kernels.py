@@ -1,0 +1,183 @@
+"""Kernel-level parity on the GPU through the C ABI: golden vectors from the reference, and the oracle on
+seeded inputs, for both the tensor-core (tcgen05) and the CUDA-core paths."""
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle"))
+import scattermoe_oracle as oracle  # noqa: E402
+from util import as_dtype, assert_close, golden_names, load_golden  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    import scattermoe_b200 as sm
+    from scattermoe_b200.kernels import ops
+    ops.FORCE_PATH = None
+    yield
+    ops.FORCE_PATH = None
+    sm.check_device_status()      # no kernel may have given up on a wait
+
+
+def _dev(t):
+    return None if t is None else t.cuda()
+
+
+@pytest.mark.parametrize("path", ["auto", "simt"])
+@pytest.mark.parametrize("name", golden_names("s2s_"))
+def test_scatter2scatter_golden(name, path):
+    from scattermoe_b200.kernels import ops
+    g = load_golden(name)
+    X, b = as_dtype(g, g["X"]), as_dtype(g, g.get("b"))
+    W = as_dtype(g, g["W"])
+    if not g["w_n_contiguous"]:
+        W = W.permute(0, 2, 1).contiguous().permute(0, 2, 1)     # K-contiguous storage, as the reference ran it
+    ops.FORCE_PATH = None if path == "auto" else path
+    Y = ops.scatter2scatter(_dev(X), _dev(W), _dev(g["sorted_expert_idxs"]), _dev(g["sorted_scattered_idxs"]), g["k"],
+                            b=_dev(b), x_grouped=g["x_grouped"], y_grouped=g["y_grouped"])
+    assert_close(name, Y, g["Y"], g["bf16"])
+    with_off = ops.scatter2scatter(_dev(X), _dev(W), _dev(g["sorted_expert_idxs"]), _dev(g["sorted_scattered_idxs"]),
+                                   g["k"], b=_dev(b), x_grouped=g["x_grouped"], y_grouped=g["y_grouped"],
+                                   expert_offsets=_dev(g["expert_offsets"]))
+    assert torch.equal(with_off, Y)
+
+
+@pytest.mark.parametrize("name", golden_names("group_"))
+def test_group_golden(name):
+    from scattermoe_b200.kernels import ops
+    g = load_golden(name)
+    A, c = as_dtype(g, g["A"]), as_dtype(g, g.get("coeff"))
+    Y = ops.group(_dev(A), _dev(g["sorted_scattered_idxs"]), coeff=_dev(c), fan_out=g["k"])
+    assert_close(name, Y, g["Y"], g["bf16"])
+    out = torch.empty_like(Y)
+    assert ops.group(_dev(A), _dev(g["sorted_scattered_idxs"]), coeff=_dev(c), fan_out=g["k"], out=out) is out
+    assert torch.equal(out, Y)
+
+
+@pytest.mark.parametrize("path", ["auto", "simt"])
+@pytest.mark.parametrize("name", golden_names("gbw_"))
+def test_group_bwd_w_golden(name, path):
+    from scattermoe_b200.kernels import ops
+    g = load_golden(name)
+    ops.FORCE_PATH = None if path == "auto" else path
+    DW, Db = ops.group_bwd_W(_dev(as_dtype(g, g["DY"])), _dev(as_dtype(g, g["X"])), _dev(g["expert_offsets"]), g["E"],
+                             has_bias="Db" in g)
+    assert DW.shape == g["DW"].shape and DW.stride(1) == 1, "(E,K,N) view of an (E,N,K) buffer"
+    assert_close(name + ".DW", DW, g["DW"], g["bf16"])
+    if "Db" in g:
+        assert_close(name + ".Db", Db, g["Db"], g["bf16"])
+    counts = torch.bincount(g["expert_idxs"].flatten(), minlength=g["E"])
+    assert bool((DW.cpu()[counts == 0] == 0).all())
+
+
+def _routing(T, E, k, seed, skew=False):
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(T, E, generator=g)
+    if skew:
+        logits[:, : max(1, E // 3)] -= 30.0
+        logits[:, -1] += 2.0
+    p = torch.softmax(logits, -1)
+    w, idx = torch.topk(p, k)
+    return w / w.sum(-1, keepdim=True), idx, g
+
+
+TC_SHAPES = [
+    # T, E, k, K, N
+    (300, 4, 2, 64, 128),
+    (1000, 8, 2, 256, 512),
+    (513, 8, 3, 320, 264),      # K and N tails (not multiples of 64 / 256)
+    (64, 16, 4, 128, 2880 // 4),  # many small experts, N = 720
+    (2048, 8, 2, 1024, 384),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("w_layout", ["k_contig", "n_contig"])
+@pytest.mark.parametrize("mode", [(False, True), (True, False), (True, True), (False, False)])
+@pytest.mark.parametrize("shape", TC_SHAPES)
+def test_scatter2scatter_tensor_core_vs_oracle(shape, mode, w_layout, dtype):
+    from scattermoe_b200.kernels import ops
+    T, E, k, K, N = shape
+    x_grouped, y_grouped = mode
+    _, idx, g = _routing(T, E, k, seed=T + K + N, skew=(T % 2 == 1))
+    se, ss, off = oracle.flatten_sort_count(idx, E)
+    kk = 1 if x_grouped else k
+    X = torch.randn(T * k if x_grouped else T, K, generator=g).to(dtype)
+    if w_layout == "n_contig":
+        W = (torch.randn(E, K, N, generator=g) * 0.05).to(dtype)
+    else:
+        W = (torch.randn(E, N, K, generator=g) * 0.05).to(dtype).permute(0, 2, 1)
+    b = (torch.randn(E, N, generator=g) * 0.1).to(dtype) if (T + K) % 3 else None
+    ops.FORCE_PATH = "tc"
+    Y = ops.scatter2scatter(_dev(X), _dev(W), _dev(se), _dev(ss), kk, b=_dev(b), x_grouped=x_grouped,
+                            y_grouped=y_grouped, expert_offsets=_dev(off))
+    assert ops.last_path_was_tensor_core()
+    want = oracle.scatter2scatter(X.float(), W.float(), se, ss, kk, b=None if b is None else b.float(),
+                                  x_grouped=x_grouped, y_grouped=y_grouped)
+    assert_close("Y", Y, want, True)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("gathered", [False, True])
+@pytest.mark.parametrize("shape", [(300, 4, 2, 64, 128), (1000, 8, 2, 256, 512), (513, 8, 3, 320, 264),
+                                   (40, 16, 4, 136, 72), (2048, 8, 2, 384, 1024)])
+def test_group_bwd_w_tensor_core_vs_oracle(shape, gathered, dtype):
+    from scattermoe_b200.kernels import ops
+    T, E, k, K, N = shape
+    _, idx, g = _routing(T, E, k, seed=T + K + N + 1, skew=True)
+    se, ss, off = oracle.flatten_sort_count(idx, E)
+    DY = torch.randn(T * k, N, generator=g).to(dtype)
+    if gathered:
+        X = torch.randn(T, K, generator=g).to(dtype)
+        Xg = oracle.group(X, ss, fan_out=k)
+    else:
+        Xg = X = torch.randn(T * k, K, generator=g).to(dtype)
+    ops.FORCE_PATH = "tc"
+    DW, Db = ops.group_bwd_W(_dev(DY), _dev(X), _dev(off), E, has_bias=True,
+                             x_gather_idx=_dev(ss) if gathered else None, fan_out=k if gathered else 1)
+    assert ops.last_path_was_tensor_core()
+    wDW, wDb = oracle.group_bwd_W(DY.float(), Xg.float(), off, E, has_bias=True)
+    scale = max(1.0, float((T * k / E) ** 0.5))     # sums over ~R/E rows of unit-variance products
+    assert_close("DW", DW.float().cpu() / scale, wDW / scale, True)
+    assert_close("Db", Db.float().cpu() / scale, wDb / scale, True)
+    counts = torch.bincount(idx.flatten(), minlength=E)
+    assert bool((DW.cpu()[counts == 0] == 0).all()) and bool((Db.cpu()[counts == 0] == 0).all())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,k,N", [(1, 2, 8), (33, 3, 100), (200, 4, 512), (64, 1, 72)])
+def test_topk_reduce_and_gate_grad(T, k, N, dtype):
+    from scattermoe_b200.kernels import ops
+    g = torch.Generator().manual_seed(T + k + N)
+    Yx = torch.randn(T * k, N, generator=g).to(dtype)
+    gates = torch.rand(T, k, generator=g).to(dtype)
+    go = torch.randn(T, N, generator=g).to(dtype)
+    bf16 = dtype == torch.bfloat16
+    out = ops.topk_reduce(_dev(Yx), _dev(gates), T, k)
+    want = (gates.float().unsqueeze(1) @ Yx.float().view(T, k, N)).squeeze(1)
+    assert_close("reduce", out, want, bf16)
+    out = ops.topk_reduce(_dev(Yx), None, T, k)
+    assert_close("sum", out, Yx.float().view(T, k, N).sum(1), bf16)
+    dg = ops.gate_grad(_dev(Yx), _dev(go), T, k)
+    want = (Yx.float().view(T, k, N) @ go.float().unsqueeze(-1)).squeeze(-1)
+    if bf16:
+        torch.testing.assert_close(dg.float().cpu(), want, rtol=2e-2, atol=2e-2 * N ** 0.5)
+    else:
+        torch.testing.assert_close(dg.cpu(), want, rtol=1e-4, atol=1e-4)
+
+
+def test_shape_contract_violations_raise_assertion_errors():
+    from scattermoe_b200.kernels import ops
+    idx = torch.zeros(6, dtype=torch.int64, device="cuda")
+    X = torch.zeros(4, 8, device="cuda")
+    W = torch.zeros(2, 8, 8, device="cuda")
+    with pytest.raises(AssertionError):
+        ops.scatter2scatter(X, W, idx, idx, 2)          # 6 != 4 * 2   (ops.py:125)
+    with pytest.raises(AssertionError):
+        ops.group(X, idx, fan_out=1)                    # ops.py:380
+    with pytest.raises(AssertionError):
+        ops.scatter2scatter(X, W, idx[:4], idx[:4], 1, out=torch.zeros(3, 8, device="cuda"))   # ops.py:132

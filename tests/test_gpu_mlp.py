@@ -1,0 +1,227 @@
+"""Module-level parity on the GPU: MLP / GLUMLP / ParallelExperts / the Hugging Face patches against the
+reference's golden outputs and the dense per-expert oracle, forward and every gradient."""
+import os
+import sys
+
+import pytest
+import torch
+from torch import nn
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "oracle"))
+import scattermoe_oracle as oracle  # noqa: E402
+from util import assert_close, load_golden  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    import scattermoe_b200 as sm
+    from scattermoe_b200.kernels import ops
+    ops.FORCE_PATH = None
+    ops.ALLOW_TF32 = True
+    yield
+    ops.FORCE_PATH = None
+    sm.check_device_status()
+
+
+def _load_module(g, cls, **kw):
+    import scattermoe_b200 as sm
+    w1 = g["param.experts.weight"]
+    w2 = g["param.output_experts.weight"]
+    E, d = w1.shape[0], w1.shape[2]
+    hidden = w2.shape[2]
+    bias = "param.experts.bias" in g
+    m = getattr(sm.mlp, cls)(d, hidden, E, g["k"], bias=bias, **kw)
+    sd = {k[len("param."):]: v for k, v in g.items() if k.startswith("param.")}
+    m.load_state_dict(sd)
+    dt = torch.bfloat16 if g["bf16"] else torch.float32
+    return m.cuda().to(dt), dt
+
+
+@pytest.mark.parametrize("name,cls,kw", [
+    ("mlp_gelu_fp32", "MLP", dict(activation=nn.GELU())),
+    ("mlp_gelu_fp32_bias", "MLP", dict(activation=nn.GELU())),
+    ("mlp_gelu_fp32_T1", "MLP", dict(activation=nn.GELU())),
+    ("glumlp_silu_fp32", "GLUMLP", {}),
+    ("glumlp_silu_bf16", "GLUMLP", {}),
+    ("mlp_gelu_bf16", "MLP", dict(activation=nn.GELU())),
+])
+def test_module_golden(name, cls, kw):
+    g = load_golden(name)
+    m, dt = _load_module(g, cls, **kw)
+    X = g["X"].to(dt).cuda().requires_grad_()
+    p = g["expert_p"].to(dt).cuda().requires_grad_()
+    Y = m(X, p, g["expert_idxs"].cuda())
+    params = dict(m.named_parameters())
+    grads = torch.autograd.grad(Y, [X, p] + list(params.values()), g["DY"].to(dt).cuda())
+    bf16 = g["bf16"]
+    assert_close(name + ".Y", Y, g["Y"], bf16)
+    assert_close(name + ".dX", grads[0], g["dX"], bf16)
+    assert_close(name + ".dg", grads[1], g["d_expert_p"], bf16)
+    for (n, _), gr in zip(params.items(), grads[2:]):
+        assert_close(name + ".grad." + n, gr, g["grad." + n], bf16)
+
+
+# The reference's own test grid (tests/test_mlp.py:36-44): fp32, E=8, GELU, TF32 off, max abs diff < 1e-4
+# on Y, dX, d(gates), dW1, dW2 (and both bias grads), against the dense loop.
+GRID = [(xd, (4 * xd) // k, k) for xd in [128, 256, 512, 600, 100] for k in [2, 3, 4]]
+
+
+@pytest.mark.parametrize("bias", [False, True])
+@pytest.mark.parametrize("length", [1, 256, 512])
+@pytest.mark.parametrize("x_dim,h_dim,k", GRID)
+def test_reference_test_grid(length, x_dim, h_dim, k, bias):
+    import scattermoe_b200 as sm
+    sm.kernels.ops.ALLOW_TF32 = False
+    E = 8
+    g = torch.Generator().manual_seed(length * 7 + x_dim + k + int(bias))
+    logits = torch.randn(length, E, generator=g)
+    weights = torch.softmax(logits, dim=-1)
+    k_weights, k_idxs = torch.topk(weights, k)      # no renormalisation, as in the reference test
+    X = torch.randn(length, x_dim, generator=g)
+    DY = torch.randn(length, x_dim, generator=g)
+    torch.manual_seed(0)
+    m = sm.mlp.MLP(x_dim, h_dim, E, k, bias=bias, activation=nn.GELU())
+    if bias:
+        nn.init.normal_(m.experts.bias, std=0.02)
+        nn.init.normal_(m.output_experts.bias, std=0.02)
+    w1, w2 = m.experts.weight.detach().clone(), m.output_experts.weight.detach().clone()
+    b1 = m.experts.bias.detach().clone() if bias else None
+    b2 = m.output_experts.bias.detach().clone() if bias else None
+    m = m.cuda()
+    Xc = X.cuda().requires_grad_()
+    pc = k_weights.cuda().requires_grad_()
+    Y = m(Xc, pc, k_idxs.cuda())
+    params = dict(m.named_parameters())
+    grads = torch.autograd.grad(Y, [Xc, pc] + list(params.values()), DY.cuda())
+    want = oracle.moe_mlp_forward_backward(X, k_weights, k_idxs, w1.permute(0, 2, 1), w2.permute(0, 2, 1), b1, b2,
+                                           oracle.act_gelu, DY)
+    assert_close("Y", Y, want["y"], False)
+    assert_close("dX", grads[0], want["d_x"], False)
+    assert_close("dg", grads[1], want["d_expert_p"], False)
+    got = dict(zip(params.keys(), grads[2:]))
+    assert_close("dW1", got["experts.weight"], want["d_w1"].permute(0, 2, 1), False)
+    assert_close("dW2", got["output_experts.weight"], want["d_w2"].permute(0, 2, 1), False)
+    if bias:
+        assert_close("db1", got["experts.bias"], want["d_b1"], False)
+        assert_close("db2", got["output_experts.bias"], want["d_b2"], False)
+
+
+def test_leading_shape_is_restored_and_grouped_flags():
+    import scattermoe_b200 as sm
+    torch.manual_seed(1)
+    m = sm.mlp.GLUMLP(64, 32, 4, 2).cuda().bfloat16()
+    x = torch.randn(2, 5, 64, device="cuda", dtype=torch.bfloat16)
+    p = torch.softmax(torch.randn(10, 4, device="cuda"), -1)
+    w, idx = torch.topk(p, 2)
+    y = m(x, w.bfloat16(), idx)
+    assert y.shape == (2, 5, 64)
+
+
+def test_hf_gpt_oss_patch_golden():
+    import scattermoe_b200  # noqa: F401  (installs the patch)
+    from transformers.models.gpt_oss.modeling_gpt_oss import GptOssExperts
+    from transformers.models.gpt_oss.configuration_gpt_oss import GptOssConfig
+    g = load_golden("hf_gpt_oss_experts")
+    cfg = GptOssConfig(hidden_size=64, intermediate_size=48, num_local_experts=8, num_experts_per_tok=4,
+                       num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1, head_dim=32)
+    ex = GptOssExperts(cfg)
+    ex.load_state_dict({k[len("param."):]: v for k, v in g.items() if k.startswith("param.")})
+    ex = ex.cuda()
+    for rw_key in ("routing_weights_topk", "routing_weights_full"):     # (T,k) of new routers, (T,E) of old ones
+        hs = g["hidden_states"].cuda().requires_grad_()
+        rw = g[rw_key].cuda().requires_grad_()
+        out = ex(hs, router_indices=g["router_indices"].cuda(), routing_weights=rw)
+        params = dict(ex.named_parameters())
+        grads = torch.autograd.grad(out, [hs, rw] + list(params.values()), g["DY"].cuda())
+        assert_close("Y", out, g["Y"], False)
+        assert_close("dX", grads[0], g["d_hidden_states"], False)
+        d_rw = grads[1] if rw_key.endswith("topk") else torch.gather(grads[1], 1, g["router_indices"].cuda())
+        assert_close("dg", d_rw, g["d_routing_weights_topk"], False)
+        for (n, _), gr in zip(params.items(), grads[2:]):
+            assert_close("grad." + n, gr, g["grad." + n], False)
+
+
+def test_hf_granite_patch_golden():
+    import scattermoe_b200 as sm
+    from transformers.models.granitemoehybrid.modeling_granitemoehybrid import GraniteMoeHybridMoE
+    from transformers.models.granitemoehybrid.configuration_granitemoehybrid import GraniteMoeHybridConfig
+    g = load_golden("hf_granitemoehybrid_moe")
+    cfg = GraniteMoeHybridConfig(hidden_size=64, intermediate_size=48, num_local_experts=8, num_experts_per_tok=2,
+                                 num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1,
+                                 shared_intermediate_size=32)
+    moe = GraniteMoeHybridMoE(cfg)
+    moe.load_state_dict({k[len("param."):]: v for k, v in g.items() if k.startswith("param.")})
+    moe = moe.cuda()
+    x = g["layer_input"].cuda().requires_grad_()
+    res = moe(x)
+    if sm.utils.replace_moe.GRANITE_RETURNS_ROUTER_LOGITS:
+        out, logits = res
+        assert_close("router_logits", logits, g["router_logits"], False)
+    else:
+        out = res
+        assert torch.is_tensor(out)
+    params = dict(moe.named_parameters())
+    grads = torch.autograd.grad(out, [x] + list(params.values()), g["DY"].cuda())
+    assert_close("Y", out, g["Y"], False)
+    assert_close("dX", grads[0], g["dX"], False)
+    for (n, _), gr in zip(params.items(), grads[1:]):
+        assert_close("grad." + n, gr, g["grad." + n], False)
+
+
+BF16_LAYERS = [
+    # name, T, d, F, E, k, kind, bias
+    ("glu", 1024, 512, 384, 8, 2, "glu_silu", False),
+    ("gpt_oss", 512, 320, 320, 16, 4, "gpt_oss", True),
+    ("zipf", 2048, 256, 128, 32, 8, "glu_silu", False),
+]
+
+
+@pytest.mark.parametrize("name,T,d,F,E,k,kind,bias", BF16_LAYERS)
+def test_bf16_layers_against_fp32_dense_loop(name, T, d, F, E, k, kind, bias):
+    """Scaled-down copies of the benchmark layers in bf16 on the tensor-core path against the fp32 dense
+    loop on the same (bf16-rounded) inputs; rtol 2e-2 / atol 2e-2 after normalising gradients to unit scale."""
+    import scattermoe_b200 as sm
+    from scattermoe_b200.utils.replace_moe import gpt_oss_glu
+    cfg = "granite_zipf" if name == "zipf" else ("gpt_oss_20b" if kind == "gpt_oss" else "mixtral_8x7b")
+    p, idx = oracle.make_routing(cfg, T, E, k, seed=1)
+    g = torch.Generator().manual_seed(2)
+    bf = torch.bfloat16
+    n1 = 2 * F
+    x = torch.randn(T, d, generator=g).to(bf)
+    w1 = (torch.randn(E, d, n1, generator=g) * 0.05).to(bf)
+    w2 = (torch.randn(E, F, d, generator=g) * 0.05).to(bf)
+    b1 = (torch.randn(E, n1, generator=g) * 0.02).to(bf) if bias else None
+    b2 = (torch.randn(E, d, generator=g) * 0.02).to(bf) if bias else None
+    go = torch.randn(T, d, generator=g).to(bf)
+    p = p.to(bf)
+    act = oracle.act_gpt_oss if kind == "gpt_oss" else oracle.act_glu_second_half
+    want = oracle.moe_mlp_forward_backward(x, p, idx, w1, w2, b1, b2, act, go, compute_dtype=torch.float32)
+
+    leaves = [t.cuda().requires_grad_() for t in (x, p, w1, w2)]
+    xb, pb, w1b, w2b = leaves
+    bl = [t.cuda().requires_grad_() for t in (b1, b2)] if bias else []
+    routing = sm.flatten_sort_count(idx.cuda(), E)
+    up = sm.parallel_linear(xb, w1b, k, *routing, expert_biases=bl[0] if bias else None, grouped_out=True)
+    if kind == "gpt_oss":
+        h = gpt_oss_glu(up, 1.702, 7.0)
+    else:
+        lin, gate = up.chunk(2, dim=-1)
+        h = torch.nn.functional.silu(gate) * lin
+    y = sm.parallel_linear(h, w2b, 1, *routing, expert_biases=bl[1] if bias else None, grouped_in=True, gates=pb)
+    grads = torch.autograd.grad(y, leaves + bl, go.cuda())
+    assert sm.kernels.ops.last_path_was_tensor_core()
+
+    def cmp(nm, got, ref):
+        s = max(ref.abs().max().item(), 1e-6) if nm != "y" else 1.0
+        s = max(s / 4, 1.0) if nm != "y" else 1.0
+        assert_close(nm, got.float().cpu() / s, ref / s, True)
+    cmp("y", y, want["y"])
+    cmp("dx", grads[0], want["d_x"])
+    cmp("dp", grads[1], want["d_expert_p"])
+    cmp("dw1", grads[2], want["d_w1"])
+    cmp("dw2", grads[3], want["d_w2"])
+    if bias:
+        cmp("db1", grads[4], want["d_b1"])
+        cmp("db2", grads[5], want["d_b2"])
