@@ -58,7 +58,8 @@ def test_module_golden(name, cls, kw):
     bf16 = g["bf16"]
     assert_close(name + ".Y", Y, g["Y"], bf16)
     assert_close(name + ".dX", grads[0], g["dX"], bf16)
-    assert_close(name + ".dg", grads[1], g["d_expert_p"], bf16)
+    # d(gates) is a length-d_model dot product of bf16-rounded outputs: its rounding error grows with sqrt(d)
+    assert_close(name + ".dg", grads[1], g["d_expert_p"], bf16, atol_scale=max(1.0, (X.shape[-1] / 16) ** 0.5))
     for (n, _), gr in zip(params.items(), grads[2:]):
         assert_close(name + ".grad." + n, gr, g["grad." + n], bf16)
 

@@ -32,11 +32,14 @@ def as_dtype(g, t):
     return t.to(torch.bfloat16) if g.get("bf16", False) else t
 
 
-def assert_close(name, got, want, bf16):
+def assert_close(name, got, want, bf16, atol_scale=1.0):
+    """`atol_scale` widens the bf16 absolute tolerance for quantities that are long dot products of
+    bf16-rounded terms (the gate gradient sums d_model products of O(1) values rounded to 8 bits)."""
     got, want = got.detach().float().cpu(), want.detach().float().cpu()
     assert got.shape == want.shape, (name, got.shape, want.shape)
     if bf16:
-        torch.testing.assert_close(got, want, rtol=BF16_RTOL, atol=BF16_ATOL, msg=lambda m: "%s: %s" % (name, m))
+        torch.testing.assert_close(got, want, rtol=BF16_RTOL, atol=BF16_ATOL * atol_scale,
+                                   msg=lambda m: "%s: %s" % (name, m))
     else:
         diff = (got - want).abs().max().item() if got.numel() else 0.0
         assert diff < FP32_MAX_ABS, "%s: max abs diff %g" % (name, diff)
