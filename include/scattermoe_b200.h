@@ -40,7 +40,8 @@ enum smoe_dtype { SMOE_F32 = 0, SMOE_BF16 = 1, SMOE_F16 = 2 };
 enum smoe_flags {
   SMOE_FLAG_ALLOW_TF32 = 1,   /* fp32 inputs may use reduced-precision tensor cores (ops.py:7 ALLOW_TF32) */
   SMOE_FLAG_FORCE_SIMT = 2,   /* take the CUDA-core kernel even where a tensor-core kernel exists */
-  SMOE_FLAG_FORCE_TC = 4      /* fail with SMOE_ERR_UNSUPPORTED instead of taking the CUDA-core kernel */
+  SMOE_FLAG_FORCE_TC = 4,     /* fail with SMOE_ERR_UNSUPPORTED instead of taking the CUDA-core kernel */
+  SMOE_FLAG_GATHER_ROWS = 8   /* feed grouped inputs through the row-gather path too (testing / comparison) */
 };
 
 /* fused epilogues of smoe_scatter2scatter (what sits between / after the two expert linears) */
@@ -126,6 +127,23 @@ int smoe_topk_reduce(const void* Yx, int64_t stride_yxm, const void* gates, int6
 int smoe_gate_grad(const void* Yx, int64_t stride_yxm, const void* grad_out, int64_t stride_gom,
                    void* d_gates, int64_t stride_dgt, int64_t stride_dgk,
                    int64_t T, int32_t k, int32_t N, int32_t dtype, void* stream);
+
+/* ---- activation between the two expert linears ---------------------------------------------------------
+ * Replaces the PyTorch elementwise ops + autograd of scattermoe/mlp.py:41 (MLP), :81-87 (GLUMLP),
+ * scattermoe/utils/replace_moe.py:76-83 (granite) and :39-43 (gpt-oss) with one pass per direction.
+ * U is the (rows, n_up) up-projection, H the (rows, F) hidden activations, inner strides 1:
+ *   layout 0 PLAIN       n_up = F    H[j] = act(U[j])
+ *   layout 1 GLU_SECOND  n_up = 2F   H[j] = act(U[F+j]) * U[j]
+ *   layout 2 GLU_FIRST   n_up = 2F   H[j] = act(U[j]) * U[F+j]
+ *   layout 3 GPT_OSS     n_up = 2F   g = min(U[2j], limit), u = clamp(U[2j+1], -limit, limit),
+ *                                    H[j] = (u + 1) * g * sigmoid(alpha * g)        (act ignored)
+ *   act: 0 SiLU, 1 GELU (erf), 2 GELU (tanh), 3 ReLU, 4 identity.
+ * smoe_activation_backward writes DU = dL/dU (rows, n_up) from U and DH = dL/dH. */
+int smoe_activation_forward(const void* U, int64_t stride_um, void* H, int64_t stride_hm, int64_t rows, int32_t F,
+                            int32_t layout, int32_t act, float alpha, float limit, int32_t dtype, void* stream);
+int smoe_activation_backward(const void* U, int64_t stride_um, const void* DH, int64_t stride_dhm, void* DU,
+                             int64_t stride_dum, int64_t rows, int32_t F, int32_t layout, int32_t act, float alpha,
+                             float limit, int32_t dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -8,7 +8,7 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
-from ctypes import c_char_p, c_int32, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int32, c_int64, c_size_t, c_void_p
 
 import torch
 
@@ -24,6 +24,7 @@ SMOE_ERR_UNSUPPORTED = 2
 FLAG_ALLOW_TF32 = 1
 FLAG_FORCE_SIMT = 2
 FLAG_FORCE_TC = 4
+FLAG_GATHER_ROWS = 8
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 
@@ -55,6 +56,9 @@ SIGNATURES = {
     "smoe_group": ([_P, _I64, _I64, _I64, _P, _P, _I32, _P, _I64, _I64, _I64, _I32, _I32, _P], c_int32),
     "smoe_topk_reduce": ([_P, _I64, _P, _I64, _I64, _P, _I64, _I64, _I32, _I32, _I32, _P], c_int32),
     "smoe_gate_grad": ([_P, _I64, _P, _I64, _P, _I64, _I64, _I64, _I32, _I32, _I32, _P], c_int32),
+    "smoe_activation_forward": ([_P, _I64, _P, _I64, _I64, _I32, _I32, _I32, c_float, c_float, _I32, _P], c_int32),
+    "smoe_activation_backward": ([_P, _I64, _P, _I64, _P, _I64, _I64, _I32, _I32, _I32, c_float, c_float, _I32, _P],
+                                 c_int32),
 }
 
 

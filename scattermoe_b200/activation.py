@@ -1,0 +1,91 @@
+"""The activation between the two expert linears as one fused pass per direction.
+
+The reference applies `self.activation` with ordinary PyTorch ops (scattermoe/mlp.py:41, :81-87;
+scattermoe/utils/replace_moe.py:39-43, :76-83). When the callable is one this library knows (SiLU, GELU, ReLU,
+identity) the modules route through `fused_activation` instead: a single kernel forward, a single kernel
+backward, nothing kept for backward but the up-projection itself. Any other callable keeps the reference's
+behaviour (it is simply called).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+from torch import nn
+
+from . import _lib
+
+LAYOUT_PLAIN, LAYOUT_GLU_SECOND, LAYOUT_GLU_FIRST, LAYOUT_GPT_OSS = 0, 1, 2, 3
+ACT_SILU, ACT_GELU_ERF, ACT_GELU_TANH, ACT_RELU, ACT_IDENTITY = 0, 1, 2, 3, 4
+
+FUSE = True    # set False to fall back to calling the activation object with PyTorch ops
+
+
+def resolve_activation(fn) -> Optional[int]:
+    """Activation code for a module / function this library fuses, else None."""
+    if fn is None:
+        return None
+    if isinstance(fn, nn.SiLU) or fn is torch.nn.functional.silu:
+        return ACT_SILU
+    if isinstance(fn, nn.GELU):
+        return ACT_GELU_TANH if getattr(fn, "approximate", "none") == "tanh" else ACT_GELU_ERF
+    if fn is torch.nn.functional.gelu:
+        return ACT_GELU_ERF
+    if isinstance(fn, nn.ReLU) or fn is torch.nn.functional.relu:
+        return ACT_RELU
+    if isinstance(fn, nn.Identity):
+        return ACT_IDENTITY
+    name = type(fn).__name__.lower()
+    if name in ("siluactivation", "silu", "swish"):          # Hugging Face ACT2FN["silu"]
+        return ACT_SILU
+    if name in ("geluactivation",):
+        return ACT_GELU_ERF
+    return None
+
+
+def _call(backward, up, dh, out, F, layout, act, alpha, limit):
+    lib = _lib.load()
+    code = _lib.DTYPE_CODE[up.dtype]
+    rows = up.size(0)
+    with torch.cuda.device(up.device):
+        if backward:
+            rc = lib.smoe_activation_backward(up.data_ptr(), up.stride(0), dh.data_ptr(), dh.stride(0), out.data_ptr(),
+                                              out.stride(0), rows, F, layout, act, alpha, limit, code,
+                                              _lib.stream_ptr(up.device))
+        else:
+            rc = lib.smoe_activation_forward(up.data_ptr(), up.stride(0), out.data_ptr(), out.stride(0), rows, F,
+                                             layout, act, alpha, limit, code, _lib.stream_ptr(up.device))
+    _lib.check(rc, "smoe_activation_backward" if backward else "smoe_activation_forward")
+
+
+class FusedActivation(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, up: torch.Tensor, layout: int, act: int, alpha: float, limit: float):
+        _lib.require_cuda(up, "up")
+        if up.stride(-1) != 1:
+            up = up.contiguous()
+        n_up = up.size(1)
+        F = n_up if layout == LAYOUT_PLAIN else n_up // 2
+        if layout != LAYOUT_PLAIN and n_up % 2:
+            raise AssertionError("gated activation needs an even number of up-projection columns")
+        h = torch.empty((up.size(0), F), dtype=up.dtype, device=up.device)
+        _call(False, up, None, h, F, layout, act, alpha, limit)
+        ctx.save_for_backward(up)
+        ctx.cfg = (F, layout, act, alpha, limit)
+        return h
+
+    @staticmethod
+    def backward(ctx, dh: torch.Tensor):
+        (up,) = ctx.saved_tensors
+        F, layout, act, alpha, limit = ctx.cfg
+        if dh.stride(-1) != 1 or dh.dtype != up.dtype:
+            dh = dh.to(up.dtype).contiguous()
+        d_up = torch.empty_like(up)
+        _call(True, up, dh, d_up, F, layout, act, alpha, limit)
+        return d_up, None, None, None, None
+
+
+def fused_activation(up: torch.Tensor, layout: int, act: int = ACT_SILU, alpha: float = 1.702,
+                     limit: float = 7.0) -> torch.Tensor:
+    """(rows, n_up) -> (rows, F); see include/scattermoe_b200.h for the layouts."""
+    return FusedActivation.apply(up, layout, act, float(alpha), float(limit))

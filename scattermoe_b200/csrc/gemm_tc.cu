@@ -53,6 +53,7 @@ struct S2SParams {
   const int64_t* sorted_idx; const int64_t* offsets;
   int64_t R;
   int K, N, E, fan_out, x_grouped, y_grouped, is_bf16, bias_vec;
+  int a_by_tma;        // X is grouped and TMA-addressable: the row tiles come by TMA, the gather warps stay idle
   uint32_t idesc;
   int32_t* status;
 };
@@ -113,7 +114,8 @@ __device__ __forceinline__ Tile decode_tile(int t, const int32_t* tile_prefix, c
 
 template <int BN, bool B_KMAJOR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const S2SParams p) {
+s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+              const S2SParams p) {
   using C = Cfg<BN>;
   constexpr int STAGES = C::STAGES;
   extern __shared__ uint8_t smem_raw[];
@@ -138,8 +140,8 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const S2SParams p) {
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), 1 + 128);   // TMA thread (expect_tx) + 128 gather threads
-      mbar_init(empty_bar(s), 1);        // tcgen05.commit
+      mbar_init(full_bar(s), p.a_by_tma ? 1 : 1 + 128);   // TMA thread (expect_tx) [+ 128 gather threads]
+      mbar_init(empty_bar(s), 1);                         // tcgen05.commit
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);        // tcgen05.commit
@@ -148,6 +150,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const S2SParams p) {
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmap_w);
+    if (p.a_by_tma) tma_prefetch_desc(&tmap_x);
   }
   build_tile_table(p.offsets, p.R, p.E, n_tiles, seg_start, tile_prefix, tid, NUM_THREADS);
   if (warp == 1) {
@@ -171,7 +174,8 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const S2SParams p) {
         const uint32_t ph = (it / STAGES) & 1;
         if (!mbar_wait_warp(empty_bar(s), ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
         if (lane == 0) {
-          mbar_arrive_expect_tx(full_bar(s), C::B_STAGE_BYTES);
+          mbar_arrive_expect_tx(full_bar(s), C::B_STAGE_BYTES + (p.a_by_tma ? A_STAGE_BYTES : 0));
+          if (p.a_by_tma) tma_load_2d(smem_u32(sA + s * A_STAGE_BYTES), &tmap_x, full_bar(s), kb * BK, tl.m0);
           const uint32_t dst = smem_u32(sB + s * C::B_STAGE_BYTES);
           if (B_KMAJOR) {
             tma_load_3d(dst, &tmap_w, full_bar(s), kb * BK, tl.n0, tl.e);
@@ -219,6 +223,8 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const S2SParams p) {
       if (ok && lane == 0) umma_commit(tfull_bar(buf));
       __syncwarp();
     }
+  } else if (warp < 6 && p.a_by_tma) {
+    // grouped input: the TMA warp feeds both operands, nothing to gather
   } else if (warp < 6) {
     // ---------------- token rows: cp.async gather into the swizzled A tile -----------------------------
     const int ptid = tid - 64;
@@ -368,13 +374,15 @@ struct WGradParams {
   const int64_t* gather_idx; const int64_t* offsets;
   int64_t R;
   int K, N, E, fan_out, is_bf16;
+  int x_by_tma;        // X is grouped and TMA-addressable: whole 64-row slabs come by TMA, ragged tails by cp.async
   uint32_t idesc;
   int32_t* status;
 };
 
 template <int BNW>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const WGradParams p) {
+wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_x,
+                const WGradParams p) {
   using C = Cfg<BNW>;
   constexpr int STAGES = C::STAGES;
   constexpr int CPR = BNW / 8;          // 16-byte chunks per gathered row
@@ -413,6 +421,7 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const WGradParams p
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&tmap_dy);
+    tma_prefetch_desc(&tmap_x);
     seg_start[0] = 0;
   }
   for (int e = tid; e < p.E; e += NUM_THREADS) {
@@ -429,16 +438,24 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const WGradParams p
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
 
-  // tile t -> expert, DY-feature tile, X-feature tile (fastest), and the expert's row segment
+  // tile t -> expert, DY-feature tile, X-feature tile and the expert's row segment. Inside one expert the
+  // X-feature tiles are walked in bands of KBAND: a band's X slabs (KBAND * BNW features of the expert's
+  // rows) stay in L2 while every DY-feature tile passes over them, so both operands stream from HBM about once.
+  constexpr int KBAND = 16;
   auto decode = [&](int t, int& e, int& n0, int& k0, int& m_beg, int& m_end) {
     e = t / tiles_per_e;
     const int rem = t - e * tiles_per_e;
-    const int nt = rem / k_tiles;
+    const int band = rem / (n_tiles * KBAND);
+    const int in_band = rem - band * n_tiles * KBAND;
+    const int bandw = min(KBAND, k_tiles - band * KBAND);
+    const int nt = in_band / bandw;
     n0 = nt * BM;
-    k0 = (rem - nt * k_tiles) * BNW;
+    k0 = (band * KBAND + (in_band - nt * bandw)) * BNW;
     m_beg = seg_start[e];
     m_end = max(m_beg, seg_start[e + 1]);
   };
+  // a 64-row slab of X comes by TMA unless X is gathered or the slab crosses the end of the segment
+  auto slab_by_tma = [&](int c, int m_beg, int m_end) { return p.x_by_tma && (m_beg + (c + 1) * BK <= m_end); };
 
   if (warp == 0) {
     // ---------------- DY slabs: TMA producer --------------------------------------------------------------
@@ -453,10 +470,17 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const WGradParams p
         const uint32_t ph = (it / STAGES) & 1;
         if (!mbar_wait_warp(empty_bar(s), ph ^ 1, abort_flag, p.status, 11)) { ok = false; break; }
         if (lane == 0) {
-          mbar_arrive_expect_tx(full_bar(s), A_STAGE_BYTES);
+          const bool x_too = slab_by_tma(c, m_beg, m_end);
+          mbar_arrive_expect_tx(full_bar(s), A_STAGE_BYTES + (x_too ? C::B_STAGE_BYTES : 0));
           const uint32_t dst = smem_u32(sA + s * A_STAGE_BYTES);
           tma_load_2d(dst, &tmap_dy, full_bar(s), n0, m_beg + c * BK);
           tma_load_2d(dst + 64 * BK * 2, &tmap_dy, full_bar(s), n0 + 64, m_beg + c * BK);
+          if (x_too) {
+            const uint32_t dstb = smem_u32(sB + s * C::B_STAGE_BYTES);
+#pragma unroll
+            for (int j = 0; j < BNW / 64; ++j)
+              tma_load_2d(dstb + j * (64 * BK * 2), &tmap_x, full_bar(s), k0 + j * 64, m_beg + c * BK);
+          }
         }
         __syncwarp();
       }
@@ -518,32 +542,41 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const WGradParams p
       const int nchunks = (m_end - m_beg + BK - 1) / BK;
       const bool k_ok = (k0 + chunk * 8) < p.K;
       const int64_t col_bytes = static_cast<int64_t>(k0 + chunk * 8) * 2;
-      for (int c = 0; c < nchunks; ++c, ++it) {
-        // source offsets of this stage's rows: lane l < 16 looks up row (half h, pass i)
-        long long my_off = -1;
-        if (lane < 16) {
+      // Byte offset of the source row that lane l < 16 looks up for slab c (half h, pass i), -1 = zero row.
+      // Looked up three slabs ahead so that the index load is off the critical path of the copies.
+      auto row_offset = [&](int c) -> long long {
+        long long off = -1;
+        if (lane < 16 && c < nchunks) {
           const int h = (rows_per_warp_pass == 2) ? (lane >> 3) : 0;
           const int i = (rows_per_warp_pass == 2) ? (lane & 7) : lane;
           if (i < NI) {
             const int64_t m = static_cast<int64_t>(m_beg) + c * BK + wrow0 + h + RPP * i;
             if (m < m_end) {
               const int64_t row = p.gather_idx ? p.gather_idx[m] / p.fan_out : m;
-              if (row >= 0 && row < p.x_rows) my_off = row * p.x_row_bytes;
+              if (row >= 0 && row < p.x_rows) off = row * p.x_row_bytes;
             }
           }
         }
+        return off;
+      };
+      long long off0 = row_offset(0), off1 = row_offset(1), off2 = row_offset(2);
+      for (int c = 0; c < nchunks; ++c, ++it) {
+        const long long my_off = off0;
+        off0 = off1; off1 = off2; off2 = row_offset(c + 3);
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
         if (!mbar_wait_warp(empty_bar(s), ph ^ 1, abort_flag, p.status, 14)) { ok = false; break; }
-        const uint32_t dst = smem_u32(sB + s * C::B_STAGE_BYTES) + box_off;
+        if (!slab_by_tma(c, m_beg, m_end)) {
+          const uint32_t dst = smem_u32(sB + s * C::B_STAGE_BYTES) + box_off;
 #pragma unroll
-        for (int i = 0; i < NI; ++i) {
-          const int src_lane = (rows_per_warp_pass == 2) ? (my_half * 8 + i) : i;
-          const long long off = __shfl_sync(0xffffffffu, my_off, src_lane);
-          const bool v = k_ok && off >= 0;
-          const int row = row_base + RPP * i;     // token row inside the 64-row slab
-          cp_async16(dst + row * 128 + (((chunk & 7) ^ (row & 7)) << 4), v ? p.X + off + col_bytes : p.X,
-                     v ? 16u : 0u);
+          for (int i = 0; i < NI; ++i) {
+            const int src_lane = (rows_per_warp_pass == 2) ? (my_half * 8 + i) : i;
+            const long long off = __shfl_sync(0xffffffffu, my_off, src_lane);
+            const bool v = k_ok && off >= 0;
+            const int row = row_base + RPP * i;     // token row inside the 64-row slab
+            cp_async16(dst + row * 128 + (((chunk & 7) ^ (row & 7)) << 4), v ? p.X + off + col_bytes : p.X,
+                       v ? 16u : 0u);
+          }
         }
         cp_async_commit();
         if (it >= A_LAG) {
@@ -700,7 +733,8 @@ static bool encode_map3(CUtensorMap* map, bool bf16, const void* base, uint64_t 
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 template <int BN, bool B_KMAJOR>
-static int launch_s2s_cfg(const CUtensorMap& map, const S2SParams& p, int grid, cudaStream_t stream) {
+static int launch_s2s_cfg(const CUtensorMap& map, const CUtensorMap& map_x, const S2SParams& p, int grid,
+                          cudaStream_t stream) {
   static std::mutex mu;
   static bool configured[64] = {false};
   int dev = 0;
@@ -713,19 +747,19 @@ static int launch_s2s_cfg(const CUtensorMap& map, const S2SParams& p, int grid, 
       if (dev >= 0 && dev < 64) configured[dev] = true;
     }
   }
-  s2s_tc_kernel<BN, B_KMAJOR><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(map, p);
+  s2s_tc_kernel<BN, B_KMAJOR><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(map, map_x, p);
   SMOE_LAUNCH_CHECK();
   return SMOE_OK;
 }
 
-// rank-2 map over (feature, row) of 16-bit elements, 64 x 64 box, 128-byte swizzle.
+// rank-2 map over (feature, row) of 16-bit elements, box0 x box1 box (64 x 64 by default), 128-byte swizzle.
 static bool encode_map2(CUtensorMap* map, bool bf16, const void* base, uint64_t d0, uint64_t d1,
-                        uint64_t stride1_bytes) {
+                        uint64_t stride1_bytes, uint32_t box0 = 64, uint32_t box1 = BK) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return false;
   const cuuint64_t dims[2] = {d0, d1};
   const cuuint64_t strides[1] = {stride1_bytes};
-  const cuuint32_t box[2] = {64, BK};
+  const cuuint32_t box[2] = {box0, box1};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult rc = fn(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
                          const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -735,7 +769,8 @@ static bool encode_map2(CUtensorMap* map, bool bf16, const void* base, uint64_t 
 }
 
 template <int BNW>
-static int launch_wgrad_cfg(const CUtensorMap& map, const WGradParams& p, int grid, cudaStream_t stream) {
+static int launch_wgrad_cfg(const CUtensorMap& map, const CUtensorMap& map_x, const WGradParams& p, int grid,
+                            cudaStream_t stream) {
   static std::mutex mu;
   static bool configured[64] = {false};
   int dev = 0;
@@ -748,7 +783,7 @@ static int launch_wgrad_cfg(const CUtensorMap& map, const WGradParams& p, int gr
       if (dev >= 0 && dev < 64) configured[dev] = true;
     }
   }
-  wgrad_tc_kernel<BNW><<<grid, NUM_THREADS, Cfg<BNW>::SMEM_BYTES, stream>>>(map, p);
+  wgrad_tc_kernel<BNW><<<grid, NUM_THREADS, Cfg<BNW>::SMEM_BYTES, stream>>>(map, map_x, p);
   SMOE_LAUNCH_CHECK();
   return SMOE_OK;
 }
@@ -792,11 +827,17 @@ int launch_s2s_tc(const S2SArgs& a) {
   p.idesc = make_idesc_f16(bf16, false, !k_major, BM, BN);
   p.status = a.status;
 
+  CUtensorMap map_x = map;   // placeholder when the rows are gathered: the kernel then never touches it
+  p.a_by_tma = (a.x_grouped && !(a.flags & SMOE_FLAG_GATHER_ROWS) && a.sxm >= a.K &&
+                encode_map2(&map_x, bf16, a.X, a.K, a.x_rows, static_cast<uint64_t>(a.sxm) * 2, 64, BM)) ? 1 : 0;
+
   const int64_t max_tiles = (cdiv64(a.R, BM) + a.E) * cdiv(a.N, BN);
   const int grid = static_cast<int>(max_tiles < di.sm_count ? max_tiles : di.sm_count);
   if (BN == 256)
-    return k_major ? launch_s2s_cfg<256, true>(map, p, grid, a.stream) : launch_s2s_cfg<256, false>(map, p, grid, a.stream);
-  return k_major ? launch_s2s_cfg<128, true>(map, p, grid, a.stream) : launch_s2s_cfg<128, false>(map, p, grid, a.stream);
+    return k_major ? launch_s2s_cfg<256, true>(map, map_x, p, grid, a.stream)
+                   : launch_s2s_cfg<256, false>(map, map_x, p, grid, a.stream);
+  return k_major ? launch_s2s_cfg<128, true>(map, map_x, p, grid, a.stream)
+                 : launch_s2s_cfg<128, false>(map, map_x, p, grid, a.stream);
 }
 
 int launch_wgrad_tc(const WGradArgs& a) {
@@ -813,7 +854,11 @@ int launch_wgrad_tc(const WGradArgs& a) {
   CUtensorMap map;
   if (!encode_map2(&map, bf16, a.DY, a.N, a.R, static_cast<uint64_t>(a.sdym) * 2)) return SMOE_ERR_UNSUPPORTED;
   const int BNW = a.K > 128 ? 256 : 128;
+  CUtensorMap map_x = map;   // placeholder when X is gathered: the kernel then never touches it
+  const bool x_by_tma = a.gather_idx == nullptr && a.sxm >= a.K &&
+                        encode_map2(&map_x, bf16, a.X, a.K, a.x_rows, static_cast<uint64_t>(a.sxm) * 2);
   WGradParams p;
+  p.x_by_tma = x_by_tma ? 1 : 0;
   p.X = static_cast<const uint8_t*>(a.X); p.x_row_bytes = a.sxm * 2; p.x_rows = a.x_rows;
   p.DW = static_cast<uint8_t*>(a.DW); p.dw_e_bytes = a.sdwe * 2; p.dw_row_bytes = a.sdwn * 2;
   p.gather_idx = a.gather_idx; p.offsets = a.offsets; p.R = a.R;
@@ -822,7 +867,8 @@ int launch_wgrad_tc(const WGradArgs& a) {
   p.status = a.status;
   const int64_t total = static_cast<int64_t>(a.E) * cdiv(a.N, BM) * cdiv(a.K, BNW);
   const int grid = static_cast<int>(total < di.sm_count ? total : di.sm_count);
-  int rc = (BNW == 256) ? launch_wgrad_cfg<256>(map, p, grid, a.stream) : launch_wgrad_cfg<128>(map, p, grid, a.stream);
+  int rc = (BNW == 256) ? launch_wgrad_cfg<256>(map, map_x, p, grid, a.stream)
+                        : launch_wgrad_cfg<128>(map, map_x, p, grid, a.stream);
   if (rc != SMOE_OK) return rc;
   if (a.Db) {
     dim3 g(static_cast<unsigned>(cdiv(a.N, 64)), static_cast<unsigned>(a.E));

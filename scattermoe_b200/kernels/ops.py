@@ -20,6 +20,7 @@ from .. import _lib
 BLOCK_M = 128        # rows of the expert-sorted slot list per tensor-core tile (ops.py:6)
 ALLOW_TF32 = True    # fp32 inputs may use reduced-precision tensor cores (ops.py:7); read at call time
 FORCE_PATH = None    # testing hook: None (automatic) | "simt" | "tc"
+GATHER_ROWS = False  # testing hook: feed grouped inputs through the cp.async row-gather path instead of TMA
 
 
 def _flags() -> int:
@@ -28,6 +29,8 @@ def _flags() -> int:
         f |= _lib.FLAG_FORCE_SIMT
     elif FORCE_PATH == "tc":
         f |= _lib.FLAG_FORCE_TC
+    if GATHER_ROWS:
+        f |= _lib.FLAG_GATHER_ROWS
     return f
 
 

@@ -8,6 +8,7 @@ base class here.
 import torch
 from torch import nn
 
+from . import activation as _act
 from .parallel_experts import ParallelExperts, flatten_sort_count
 
 
@@ -53,7 +54,10 @@ class MLP(_ExpertMLPBase):
         super().__init__(input_size, hidden_size, num_experts, top_k, bias, activation)
 
     def _activate(self, up):
-        return self.activation(up)
+        code = _act.resolve_activation(self.activation) if _act.FUSE else None
+        if code is None or up.dim() != 2:
+            return self.activation(up)
+        return _act.fused_activation(up, _act.LAYOUT_PLAIN, code)
 
 
 class GLUMLP(_ExpertMLPBase):
@@ -66,5 +70,8 @@ class GLUMLP(_ExpertMLPBase):
         super().__init__(input_size, hidden_size, num_experts, top_k, bias, activation)
 
     def _activate(self, up):
-        linear_half, gate_half = up.chunk(2, dim=-1)
-        return self.activation(gate_half) * linear_half
+        code = _act.resolve_activation(self.activation) if _act.FUSE else None
+        if code is None or up.dim() != 2:
+            linear_half, gate_half = up.chunk(2, dim=-1)
+            return self.activation(gate_half) * linear_half
+        return _act.fused_activation(up, _act.LAYOUT_GLU_SECOND, code)

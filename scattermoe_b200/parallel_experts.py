@@ -65,6 +65,13 @@ def flatten_sort_count(expert_idxs: torch.Tensor, num_experts: int):
         return sorted_e, sorted_idx, offsets
 
 
+# Un-grouped 16-bit inputs are first copied into expert order (one HBM pass, `kernels.ops.group`) so that the
+# tensor-core kernels of the forward AND of the weight gradient read them with TMA; the copy is kept for
+# backward, where the reference makes the same copy anyway (parallel_experts.py:99). Measured on B200 the
+# TMA-fed kernels run ~2x faster than the cp.async row gather for the weight gradient. False: gather in-kernel.
+GROUP_INPUT_COPY = True
+
+
 def _rowmajor(t: torch.Tensor) -> torch.Tensor:
     return t if t.stride(-1) == 1 else t.contiguous()
 
@@ -73,8 +80,10 @@ class ParallelLinear(torch.autograd.Function):
     """parallel_experts.py:25-134, same argument order and return arity.
 
     Differences that are not visible in results: the top-k reductions are dedicated kernels instead of
-    batched matmuls (:44-46, :79, :123), the un-grouped input is gathered inside the weight-gradient kernel
-    instead of being copied by `group` (:99), and gradients nobody asked for are not computed.
+    batched matmuls (:44-46, :79, :123); the expert-order copy of an un-grouped input that the reference makes
+    in backward (:99) is made once in forward and shared by the forward GEMM and the weight gradient (see
+    GROUP_INPUT_COPY; with it off both kernels gather the rows themselves and no copy exists); gradients
+    nobody asked for are not computed.
     """
 
     @staticmethod
@@ -85,17 +94,26 @@ class ParallelLinear(torch.autograd.Function):
                 gates: Optional[torch.Tensor] = None,
                 grouped_in: bool = False, grouped_out: bool = False):
         x = _rowmajor(x)
-        output = kernels.ops.scatter2scatter(
-            X=x, W=expert_weights, b=expert_biases, k=k,
-            sorted_expert_idxs=sorted_expert_idxs, sorted_scattered_idxs=sorted_scattered_idxs,
-            x_grouped=grouped_in, y_grouped=grouped_out, expert_offsets=expert_offsets)
+        x_in_expert_order = None
+        if (not grouped_in and GROUP_INPUT_COPY and x.dtype in (torch.bfloat16, torch.float16)
+                and x.size(1) % 8 == 0 and x.is_cuda):
+            x_in_expert_order = kernels.ops.group(x, sorted_scattered_idxs, fan_out=k)
+            output = kernels.ops.scatter2scatter(
+                X=x_in_expert_order, W=expert_weights, b=expert_biases, k=1,
+                sorted_expert_idxs=sorted_expert_idxs, sorted_scattered_idxs=sorted_scattered_idxs,
+                x_grouped=True, y_grouped=grouped_out, expert_offsets=expert_offsets)
+        else:
+            output = kernels.ops.scatter2scatter(
+                X=x, W=expert_weights, b=expert_biases, k=k,
+                sorted_expert_idxs=sorted_expert_idxs, sorted_scattered_idxs=sorted_scattered_idxs,
+                x_grouped=grouped_in, y_grouped=grouped_out, expert_offsets=expert_offsets)
         if gates is not None:
             output_expanded = output.view(gates.size(0), gates.size(1), output.size(-1))
             output = kernels.ops.topk_reduce(output, gates, gates.size(0), gates.size(1))
         else:
             output_expanded = None
         ctx.save_for_backward(x, expert_weights, expert_biases, sorted_expert_idxs, sorted_scattered_idxs,
-                              expert_offsets, gates, output_expanded)
+                              expert_offsets, gates, output_expanded, x_in_expert_order)
         ctx.grouped_in = grouped_in
         ctx.grouped_out = grouped_out
         ctx.k = k
@@ -104,7 +122,7 @@ class ParallelLinear(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out: torch.Tensor):
         (x, expert_weights, expert_biases, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
-         gates, output_expanded) = ctx.saved_tensors
+         gates, output_expanded, x_in_expert_order) = ctx.saved_tensors
         k = ctx.k
         grouped_in = ctx.grouped_in
         grouped_out = ctx.grouped_out
@@ -136,10 +154,13 @@ class ParallelLinear(torch.autograd.Function):
                 grouped_grad_out = kernels.ops.group(grad_out, sorted_scattered_idxs, fan_out=gate_fan,
                                                      coeff=gates_flat, out=grouped_grad_out)
             if need_w or need_b:
+                x_rows_grouped = grouped_in or x_in_expert_order is not None
                 d_weights, d_biases = kernels.ops.group_bwd_W(
-                    DY=grouped_grad_out, X=x, expert_offsets=expert_offsets, E=expert_weights.size(0),
+                    DY=grouped_grad_out, X=x if grouped_in else (x_in_expert_order if x_rows_grouped else x),
+                    expert_offsets=expert_offsets, E=expert_weights.size(0),
                     has_bias=expert_biases is not None,
-                    x_gather_idx=None if grouped_in else sorted_scattered_idxs, fan_out=1 if grouped_in else k)
+                    x_gather_idx=None if x_rows_grouped else sorted_scattered_idxs,
+                    fan_out=1 if x_rows_grouped else k)
             if need_x:
                 d_expanded_input = kernels.ops.scatter2scatter(
                     X=grouped_grad_out, x_grouped=True, W=expert_weights.permute(0, 2, 1),

@@ -19,6 +19,7 @@ import logging
 import torch
 from torch.nn import functional as F
 
+from .. import activation as _act
 from ..parallel_experts import flatten_sort_count, parallel_linear
 
 PATCHED = {}      # class name -> original forward
@@ -41,6 +42,8 @@ def replace_function(cls, fun_name):
 
 def gpt_oss_glu(gate_up: torch.Tensor, alpha: float, limit: float) -> torch.Tensor:
     """Clamped SwiGLU on interleaved gate/up columns (replace_moe.py:39-43)."""
+    if _act.FUSE and gate_up.is_cuda and gate_up.dim() == 2:
+        return _act.fused_activation(gate_up, _act.LAYOUT_GPT_OSS, _act.ACT_SILU, alpha, limit)
     gate, up = gate_up[..., ::2], gate_up[..., 1::2]
     gate = gate.clamp(min=None, max=limit)
     up = up.clamp(min=-limit, max=limit)
@@ -101,10 +104,14 @@ try:
         probs = probs.to(tokens.dtype)
         routing = flatten_sort_count(selected_experts, num_experts=self.router.num_experts)
         # experts: the FIRST half of the up-projection is the activated one here (replace_moe.py:76-83)
-        gate_half, linear_half = parallel_linear(
-            tokens, self.input_linear.weight.transpose(2, 1), self.router.top_k, *routing,
-            grouped_in=False, grouped_out=True).chunk(2, dim=-1)
-        hidden = self.activation(gate_half) * linear_half
+        up = parallel_linear(tokens, self.input_linear.weight.transpose(2, 1), self.router.top_k, *routing,
+                             grouped_in=False, grouped_out=True)
+        code = _act.resolve_activation(self.activation) if _act.FUSE else None
+        if code is None:
+            gate_half, linear_half = up.chunk(2, dim=-1)
+            hidden = self.activation(gate_half) * linear_half
+        else:
+            hidden = _act.fused_activation(up, _act.LAYOUT_GLU_FIRST, code)
         layer_output = parallel_linear(hidden, self.output_linear.weight.transpose(2, 1), 1, *routing,
                                        grouped_in=True, grouped_out=False, gates=probs)
         layer_output = layer_output.view(bsz, length, emb_size)

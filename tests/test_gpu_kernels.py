@@ -181,3 +181,54 @@ def test_shape_contract_violations_raise_assertion_errors():
         ops.group(X, idx, fan_out=1)                    # ops.py:380
     with pytest.raises(AssertionError):
         ops.scatter2scatter(X, W, idx[:4], idx[:4], 1, out=torch.zeros(3, 8, device="cuda"))   # ops.py:132
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,F", [(5, 8), (33, 133), (100, 256), (7, 20)])
+@pytest.mark.parametrize("layout,act", [("plain", "gelu"), ("plain", "silu"), ("glu_second", "silu"),
+                                        ("glu_second", "gelu"), ("glu_first", "silu"), ("gpt_oss", None)])
+def test_fused_activation_forward_and_backward(rows, F, layout, act, dtype):
+    """One-pass activation kernels against the PyTorch formulas the reference uses (mlp.py:41, :81-87;
+    replace_moe.py:39-43, :76-83), forward and autograd backward."""
+    from scattermoe_b200 import activation as A
+    g = torch.Generator().manual_seed(rows * 31 + F)
+    n_up = F if layout == "plain" else 2 * F
+    up = (torch.randn(rows, n_up, generator=g) * 3).to(dtype)     # wide enough to hit the gpt-oss clamps at +-7
+    dh = torch.randn(rows, F, generator=g).to(dtype)
+    ref_in = up.float().requires_grad_()
+    fn = {"gelu": torch.nn.functional.gelu, "silu": torch.nn.functional.silu, None: None}[act]
+    if layout == "plain":
+        ref = fn(ref_in)
+    elif layout == "glu_second":
+        ref = oracle.act_glu_second_half(ref_in, fn)
+    elif layout == "glu_first":
+        ref = oracle.act_glu_first_half(ref_in, fn)
+    else:
+        ref = oracle.act_gpt_oss(ref_in)
+    (ref_grad,) = torch.autograd.grad(ref, ref_in, dh.float())
+    code = {"gelu": A.ACT_GELU_ERF, "silu": A.ACT_SILU, None: A.ACT_SILU}[act]
+    lay = {"plain": A.LAYOUT_PLAIN, "glu_second": A.LAYOUT_GLU_SECOND, "glu_first": A.LAYOUT_GLU_FIRST,
+           "gpt_oss": A.LAYOUT_GPT_OSS}[layout]
+    x = up.cuda().requires_grad_()
+    h = A.fused_activation(x, lay, code, 1.702, 7.0)
+    (gx,) = torch.autograd.grad(h, x, dh.cuda())
+    bf16 = dtype == torch.bfloat16
+    if bf16:
+        torch.testing.assert_close(h.float().cpu(), ref.detach(), rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(gx.float().cpu(), ref_grad, rtol=2e-2, atol=4e-2)
+    else:
+        torch.testing.assert_close(h.cpu(), ref.detach(), rtol=1e-5, atol=1e-5)
+        torch.testing.assert_close(gx.cpu(), ref_grad, rtol=1e-5, atol=2e-5)
+
+
+def test_activation_resolution():
+    from torch import nn
+    from scattermoe_b200 import activation as A
+    assert A.resolve_activation(nn.SiLU()) == A.ACT_SILU
+    assert A.resolve_activation(nn.GELU()) == A.ACT_GELU_ERF
+    assert A.resolve_activation(nn.GELU(approximate="tanh")) == A.ACT_GELU_TANH
+    assert A.resolve_activation(nn.ReLU()) == A.ACT_RELU
+    assert A.resolve_activation(nn.Identity()) == A.ACT_IDENTITY
+    assert A.resolve_activation(nn.Tanh()) is None and A.resolve_activation(lambda t: t) is None
+    from transformers.activations import ACT2FN
+    assert A.resolve_activation(ACT2FN["silu"]) == A.ACT_SILU

@@ -56,12 +56,18 @@ def test_module_golden(name, cls, kw):
     params = dict(m.named_parameters())
     grads = torch.autograd.grad(Y, [X, p] + list(params.values()), g["DY"].to(dt).cuda())
     bf16 = g["bf16"]
+
+    def scale(ref):
+        # bf16 cases: the stored outputs are fp32 results, the run under test rounds every intermediate to
+        # bf16 as the reference's bf16 run does; gradients are sums of many such terms with magnitudes of
+        # several units, so the absolute tolerance is applied after bringing them to unit scale.
+        return max(1.0, ref.abs().max().item() / 4) if bf16 else 1.0
+
     assert_close(name + ".Y", Y, g["Y"], bf16)
-    assert_close(name + ".dX", grads[0], g["dX"], bf16)
-    # d(gates) is a length-d_model dot product of bf16-rounded outputs: its rounding error grows with sqrt(d)
-    assert_close(name + ".dg", grads[1], g["d_expert_p"], bf16, atol_scale=max(1.0, (X.shape[-1] / 16) ** 0.5))
+    assert_close(name + ".dX", grads[0], g["dX"], bf16, atol_scale=scale(g["dX"]))
+    assert_close(name + ".dg", grads[1], g["d_expert_p"], bf16, atol_scale=scale(g["d_expert_p"]))
     for (n, _), gr in zip(params.items(), grads[2:]):
-        assert_close(name + ".grad." + n, gr, g["grad." + n], bf16)
+        assert_close(name + ".grad." + n, gr, g["grad." + n], bf16, atol_scale=scale(g["grad." + n]))
 
 
 # The reference's own test grid (tests/test_mlp.py:36-44): fp32, E=8, GELU, TF32 off, max abs diff < 1e-4
@@ -107,6 +113,35 @@ def test_reference_test_grid(length, x_dim, h_dim, k, bias):
     if bias:
         assert_close("db1", got["experts.bias"], want["d_b1"], False)
         assert_close("db2", got["output_experts.bias"], want["d_b2"], False)
+
+
+@pytest.mark.parametrize("group_copy,gather_rows", [(True, False), (False, False), (False, True)])
+def test_input_feeding_variants_agree(group_copy, gather_rows):
+    """The three ways the tensor-core kernels can be fed (expert-order copy + TMA, in-kernel cp.async row gather
+    of the un-grouped input, cp.async gather of grouped inputs too) give the same layer outputs and gradients."""
+    import scattermoe_b200 as sm
+    from scattermoe_b200 import parallel_experts as pe
+    from scattermoe_b200.kernels import ops
+    torch.manual_seed(3)
+    T, d, F, E, k = 777, 256, 192, 8, 2
+    m = sm.mlp.GLUMLP(d, F, E, k).cuda().bfloat16()
+    x = torch.randn(T, d, device="cuda", dtype=torch.bfloat16)
+    p, idx = torch.topk(torch.softmax(torch.randn(T, E, device="cuda"), -1), k)
+    dy = torch.randn(T, d, device="cuda", dtype=torch.bfloat16)
+
+    def run():
+        xx, pp = x.clone().requires_grad_(), p.bfloat16().requires_grad_()
+        y = m(xx, pp, idx)
+        return [y] + list(torch.autograd.grad(y, [xx, pp, m.experts.weight, m.output_experts.weight], dy))
+    base = run()
+    old = pe.GROUP_INPUT_COPY
+    try:
+        pe.GROUP_INPUT_COPY, ops.GATHER_ROWS = group_copy, gather_rows
+        got = run()
+    finally:
+        pe.GROUP_INPUT_COPY, ops.GATHER_ROWS = old, False
+    for a, b in zip(got, base):
+        torch.testing.assert_close(a.float(), b.float(), rtol=1e-2, atol=1e-2 * max(1.0, b.float().abs().max().item()))
 
 
 def test_leading_shape_is_restored_and_grouped_flags():
