@@ -65,6 +65,22 @@ int smoe_sort_count(const int64_t* expert_idxs, int64_t R, int32_t E,
                     int64_t* sorted_expert_idxs, int64_t* sorted_scattered_idxs, int64_t* expert_offsets,
                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* Allocation-free variant of smoe_sort_count. It has no counterpart in the reference. It exists for hosts that
+ * bind this C ABI directly and cannot obtain device memory at call time: servers that hand the whole HBM to
+ * their own arena at start-up and forbid cudaMalloc on the request path (it synchronises the device and can fail
+ * once memory is fragmented), or embedders without a device allocator at all. The caller passes only inputs
+ * and outputs; the block histograms go to a 512 KiB array built into the library (one per GPU that loads it,
+ * held until the process exits). Limit: ceil(R / 2048) * E <= smoe_sort_count_static_capacity() (131072), e.g.
+ * R <= 2^21 slots at E = 128; larger requests return SMOE_ERR_WORKSPACE. The call performs no cudaMalloc,
+ * cudaFree or other allocating call. The first call on each device looks up the array's device address (a
+ * host-side set-up step, done with that device current): make that first call before any stream capture.
+ * All calls on one device share the array: calls that may overlap on the GPU (different streams) race; calls
+ * issued in order on one stream do not, and nothing has to be cleared between them. */
+int64_t smoe_sort_count_static_capacity(void);
+int smoe_sort_count_static(const int64_t* expert_idxs, int64_t R, int32_t E,
+                           int64_t* sorted_expert_idxs, int64_t* sorted_scattered_idxs, int64_t* expert_offsets,
+                           void* stream);
+
 /* Inclusive end offsets from the sorted ids alone. The reference's kernels.ops.scatter2scatter
  * (scattermoe/kernels/ops.py:120) receives no offsets and masks rows per expert inside the kernel
  * (:81-91); this build's grouped GEMM walks expert segments, so callers that only hold the sorted ids

@@ -6,6 +6,8 @@
 // the (expert-major) block histograms, and a stable scatter that recomputes the warp-local ranks.
 #include <stdarg.h>
 
+#include <mutex>
+
 #include "smoe_common.cuh"
 
 namespace smoe {
@@ -154,6 +156,35 @@ __global__ void offsets_from_sorted_kernel(const int64_t* __restrict__ sorted_e,
   for (int64_t e = prev; e < cur; ++e) expert_offsets[e] = m;
 }
 
+// ---- the allocation-free variant ----------------------------------------------------------------------
+// Scratch for smoe_sort_count_static: the per-block histograms live in this fixed array instead of a
+// caller-provided workspace. Every GPU that loads the library carries these 512 KiB until the process exits.
+constexpr int SC_STATIC_INTS = 128 * 1024;
+static __device__ __align__(256) int32_t g_sort_scratch[SC_STATIC_INTS];
+
+// Host code cannot pass `g_sort_scratch` to a kernel: in host code that name is a stand-in for the symbol, not
+// a device address. The address is looked up once per device, with that device current, and cached.
+static int static_scratch_address(int32_t** out) {
+  static std::mutex mu;
+  static int32_t* cached[64] = {nullptr};
+  int dev = 0;
+  SMOE_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  if (dev >= 0 && dev < 64 && cached[dev]) {
+    *out = cached[dev];
+    return SMOE_OK;
+  }
+  void* ptr = nullptr;
+  SMOE_CUDA(cudaGetSymbolAddress(&ptr, g_sort_scratch));
+  if (ptr == nullptr) {
+    set_error("sort_count_static: cudaGetSymbolAddress returned a null address");
+    return SMOE_ERR_CUDA;
+  }
+  if (dev >= 0 && dev < 64) cached[dev] = static_cast<int32_t*>(ptr);
+  *out = static_cast<int32_t*>(ptr);
+  return SMOE_OK;
+}
+
 }  // namespace smoe
 
 using namespace smoe;
@@ -218,4 +249,25 @@ extern "C" int smoe_offsets_from_sorted(const int64_t* sorted_expert_idxs, int64
                                                                                       expert_offsets);
   SMOE_LAUNCH_CHECK();
   return SMOE_OK;
+}
+
+extern "C" int64_t smoe_sort_count_static_capacity(void) { return SC_STATIC_INTS; }
+
+extern "C" int smoe_sort_count_static(const int64_t* expert_idxs, int64_t R, int32_t E, int64_t* sorted_expert_idxs,
+                                      int64_t* sorted_scattered_idxs, int64_t* expert_offsets, void* stream) {
+  SMOE_CHECK_ARG(R >= 0 && R < (int64_t(1) << 31), "sort_count_static: R=%lld out of range [0, 2^31)", (long long)R);
+  SMOE_CHECK_ARG(E >= 1 && E <= SC_MAX_E, "sort_count_static: E=%d out of range [1, %d]", E, SC_MAX_E);
+  const int64_t need = cdiv64(R > 0 ? R : 1, SC_CHUNK) * E;
+  if (need > SC_STATIC_INTS) {
+    set_error("sort_count_static: ceil(R/%d) * E = %lld exceeds the built-in scratch of %d entries (R=%lld, E=%d); "
+              "use smoe_sort_count with a caller-provided workspace", SC_CHUNK, (long long)need, SC_STATIC_INTS,
+              (long long)R, E);
+    return SMOE_ERR_WORKSPACE;
+  }
+  int32_t* scratch = nullptr;
+  if (int rc = static_scratch_address(&scratch)) return rc;
+  // Same kernels as smoe_sort_count. The histogram pass writes every scratch entry the later passes read, so
+  // nothing left behind by an earlier call needs clearing.
+  return smoe_sort_count(expert_idxs, R, E, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, scratch,
+                         static_cast<size_t>(SC_STATIC_INTS) * sizeof(int32_t), stream);
 }
