@@ -7,8 +7,11 @@ gates and both expert weight tensors) of the layer on one batch of seeded synthe
 line. `value` is device-timed with the inputs resident in HBM; `e2e` repeats the measurement with the
 step's inputs copied from pinned host memory and its results copied back inside the timed region.
 
-N > 1 (launched by torch.distributed.run, one rank per GPU): every rank runs the same layer on its own shard
-of tokens (weak scaling, no data-path collective); time is the max over ranks.
+N > 1 (launched by torch.distributed.run, one rank per GPU): expert parallel, strong scaling. The layer's experts
+are partitioned across the ranks, the workload's tokens are split evenly, and every step exchanges rows with two
+NCCL all-to-all-v's each way (scattermoe_b200.expert_parallel). Time is the max over ranks, `value` the global
+tokens per second. (The gpt-oss workload, whose block has biases and its own activation, is not expert-parallel
+here: its ranks run replicas on their own token shards, weak scaling.)
 
 `--impl reference` times the reference's CPU path for the same layer (the dense per-expert PyTorch loop the
 reference's own test uses as ground truth) on the host cores, on a bounded sample of the tokens.
@@ -123,7 +126,7 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_layer(name, c, tokens, device, seed):
+def build_layer(name, c, tokens, device, seed, ep_world=1, exchange="nvlink"):
     """Parameters and inputs of one rank: weights ~N(0, 0.02), X ~N(0, 1), softmax top-k routing."""
     import scattermoe_b200 as sm
     g = torch.Generator().manual_seed(seed)
@@ -143,6 +146,16 @@ def build_layer(name, c, tokens, device, seed):
         layer["w2"] = rnd(E, F, d, std=0.02).requires_grad_()
         layer["b1"] = rnd(E, 2 * F, std=0.02).requires_grad_()
         layer["b2"] = rnd(E, d, std=0.02).requires_grad_()
+    elif ep_world > 1:
+        from scattermoe_b200.expert_parallel import ExpertParallelGLUMLP, PeerExpertParallelGLUMLP
+        if exchange == "nvlink":
+            m = PeerExpertParallelGLUMLP(d, F, E, k, global_tokens=tokens * ep_world).to(device=device, dtype=bf)
+        else:
+            m = ExpertParallelGLUMLP(d, F, E, k).to(device=device, dtype=bf)
+        with torch.no_grad():
+            m.experts.weight.copy_(rnd(E // ep_world, 2 * F, d, std=0.02))
+            m.output_experts.weight.copy_(rnd(E // ep_world, d, F, std=0.02))
+        layer["module"] = m
     else:
         m = sm.mlp.GLUMLP(d, F, E, k).to(device=device, dtype=bf)
         with torch.no_grad():
@@ -174,6 +187,37 @@ def run_step(c, layer, x, p, idx, dy):
         leaves = [x, p, m.experts.weight, m.output_experts.weight]
     grads = torch.autograd.grad(y, leaves, dy)
     return y, grads[0]
+
+
+class LaunchCounter:
+    """Counts the kernels this library launches: a proxy in front of the ctypes library that knows how many
+    kernels each C entry point enqueues."""
+    KERNELS = {"smoe_ep_dispatch": 1, "smoe_ep_combine": 1, "smoe_ep_gate_grad": 1, "smoe_sort_count": 3, "smoe_sort_count_static": 3, "smoe_offsets_from_sorted": 1,
+               "smoe_scatter2scatter": 1, "smoe_group_bwd_w": 1, "smoe_group": 1, "smoe_topk_reduce": 1,
+               "smoe_gate_grad": 1, "smoe_activation_forward": 1, "smoe_activation_backward": 1}
+
+    def __init__(self):
+        from scattermoe_b200 import _lib
+        self._mod, self._real, self.count = _lib, _lib.load(), 0
+
+    def __getattr__(self, name):
+        fn = getattr(self._real, name)
+        n = self.KERNELS.get(name, 0)
+        if not n:
+            return fn
+
+        def counted(*a):
+            self.count += n
+            if name == "smoe_group_bwd_w" and a[14]:      # a bias gradient adds its own column-sum kernel
+                self.count += 1
+            return fn(*a)
+        return counted
+
+    def install(self):
+        self._mod._lib = self
+
+    def remove(self):
+        self._mod._lib = self._real
 
 
 class KernelTimer:
@@ -278,6 +322,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--config", default="mixtral_8x7b", choices=sorted(LAYERS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--exchange", default="nvlink", choices=["nvlink", "nccl"],
+                    help="expert-parallel row exchange for N > 1: peer-memory kernels over NVLink, or NCCL all-to-all-v")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-triton-ref", action="store_true")
     args = ap.parse_args()
@@ -288,8 +334,18 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     name, c = args.config, LAYERS[args.config]
     metric = "moe_layer_fwd_bwd_tokens_per_s"
-    config = {"workload": name, "tokens_per_gpu": c["T"], "d_model": c["d"], "d_ffn": c["F"], "experts": c["E"],
-              "top_k": c["k"], "activation": c["kind"], "bias": c["bias"], "parallelism": "replicated layer, token shards",
+    ep = world > 1 and c["kind"] != "gpt_oss"
+    if ep and (c["E"] % world or c["T"] % world):
+        raise SystemExit("expert parallel needs the world size to divide E=%d and T=%d" % (c["E"], c["T"]))
+    tokens_local = c["T"] // world if ep else c["T"]
+    tokens_all = c["T"] if ep else c["T"] * world
+    scaling = "weak" if (world > 1 and not ep) else "strong"
+    config = {"workload": name, "global_tokens": tokens_all, "tokens_per_gpu": tokens_local, "d_model": c["d"],
+              "d_ffn": c["F"], "experts": c["E"], "experts_per_gpu": c["E"] // world if ep else c["E"],
+              "top_k": c["k"], "activation": c["kind"], "bias": c["bias"],
+              "parallelism": ("ep%d: experts partitioned, %s dispatch/combine"
+                              % (world, "NVLink peer-memory" if args.exchange == "nvlink" else "NCCL all-to-all-v")) if ep
+              else ("single GPU" if world == 1 else "replicas on token shards"),
               "l2": "weights and activations exceed L2 (126 MB) every step"}
 
     if args.impl == "reference":
@@ -298,7 +354,7 @@ def main():
         base, sec = cpu_reference(name, c, max(1, min(args.steps, 3)), min(args.warmup, 1))
         line = {"impl": "reference", "metric": metric, "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+                "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
                 "cpu_baseline": base,
                 "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
@@ -315,7 +371,8 @@ def main():
 
     import scattermoe_b200 as sm
     peaks = load_peaks()
-    layer, host = build_layer(name, c, c["T"], device, seed=rank)
+    layer, host = build_layer(name, c, tokens_local, device, seed=rank, ep_world=world if ep else 1,
+                             exchange=args.exchange)
     dev_in = {n: t.to(device) for n, t in host.items()}
 
     def barrier():
@@ -357,13 +414,22 @@ def main():
     sm.check_device_status(device)
     timer = KernelTimer()
     timer.install()
+    counter = LaunchCounter()
+    counter.install()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
     ms_total = timed(resident_step, args.steps)
     clocks = sampler.stop() if sampler else None
+    counter.remove()
     timer.remove()
     ksum = timer.summary()
+    mod = layer.get("module")
+    if getattr(mod, "last_rows_dev", None) is not None:
+        # peer-memory expert parallelism launches its GEMMs over worst-case-sized buffers; count the live rows only
+        live = float(mod.last_rows_dev.item()) / mod.buffers.capacity
+        for d_ in ksum.values():
+            d_["flops"] *= live
     tensor_core = sm.kernels.ops.last_path_was_tensor_core()
 
     for _ in range(2):
@@ -377,9 +443,8 @@ def main():
         return
 
     ms_step = ms_total / args.steps
-    tokens_all = c["T"] * world
     value = tokens_all / (ms_step / 1e3)
-    fwd_flops, fb_flops = layer_flops(c, c["T"])
+    fwd_flops, fb_flops = layer_flops(c, tokens_all)
     h2d = sum(host[n].numel() * host[n].element_size() for n in ("x", "p", "idx", "dy"))
     d2h = sum(t.numel() * t.element_size() for t in out_host.values())
     dom = ksum.get("scatter2scatter", dict(launches=0, ms=0.0, flops=0.0))
@@ -395,17 +460,16 @@ def main():
                                    "avg_launch_ms": wg["ms"] / wg["launches"],
                                    "frac": wg["flops"] / (wg["ms"] / 1e3) / 1e12 / peak}
     line = {"metric": metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": scaling,
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
-            "layer_tflops": fb_flops * world / (ms_step / 1e3) / 1e12,
-            "layer_frac_of_bf16_peak": fb_flops / (ms_step / 1e3) / 1e12 / peak,
+            "layer_tflops": fb_flops / (ms_step / 1e3) / 1e12,
+            "layer_frac_of_bf16_peak": fb_flops / world / (ms_step / 1e3) / 1e12 / peak,
             "tensor_core_path": bool(tensor_core),
             "roofline": roofline,
             "e2e": {"value": tokens_all / (ms_e2e / args.steps / 1e3), "unit": "tokens/s",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps},
-            # kernels of this library per step: 3 routing (histogram, scan, scatter) + 4 scatter2scatter + 2
-            # group_bwd_w (+ 2 bias-gradient sums with biases) + 2 top-k reductions + gate gradient + group
-            "gpu_launches": (13 + (2 if c["bias"] else 0)) * args.steps,
+            # kernels of this library launched by this rank inside the timed region (counted at the C-ABI boundary)
+            "gpu_launches": counter.count,
             "clocks": clocks}
     if world == 1 and not args.no_triton_ref:
         line["reference_gpu"] = time_reference_triton(name, c, host, device)

@@ -154,12 +154,40 @@ int smoe_gate_grad(const void* Yx, int64_t stride_yxm, const void* grad_out, int
  *   layout 3 GPT_OSS     n_up = 2F   g = min(U[2j], limit), u = clamp(U[2j+1], -limit, limit),
  *                                    H[j] = (u + 1) * g * sigmoid(alpha * g)        (act ignored)
  *   act: 0 SiLU, 1 GELU (erf), 2 GELU (tanh), 3 ReLU, 4 identity.
- * smoe_activation_backward writes DU = dL/dU (rows, n_up) from U and DH = dL/dH. */
-int smoe_activation_forward(const void* U, int64_t stride_um, void* H, int64_t stride_hm, int64_t rows, int32_t F,
-                            int32_t layout, int32_t act, float alpha, float limit, int32_t dtype, void* stream);
+ * smoe_activation_backward writes DU = dL/dU (rows, n_up) from U and DH = dL/dH.
+ * `rows_dev` (nullable device int64): when the live row count is only known on the device (expert-parallel
+ * receive buffers sized for the worst case) only min(rows, *rows_dev) rows are processed. */
+int smoe_activation_forward(const void* U, int64_t stride_um, void* H, int64_t stride_hm, int64_t rows,
+                            const int64_t* rows_dev, int32_t F, int32_t layout, int32_t act, float alpha, float limit,
+                            int32_t dtype, void* stream);
 int smoe_activation_backward(const void* U, int64_t stride_um, const void* DH, int64_t stride_dhm, void* DU,
-                             int64_t stride_dum, int64_t rows, int32_t F, int32_t layout, int32_t act, float alpha,
-                             float limit, int32_t dtype, void* stream);
+                             int64_t stride_dum, int64_t rows, const int64_t* rows_dev, int32_t F, int32_t layout,
+                             int32_t act, float alpha, float limit, int32_t dtype, void* stream);
+
+/* ---- expert-parallel row exchange over NVLink peer memory -----------------------------------------------
+ * No counterpart in the reference (it has no multi-GPU code). `peer_bufs` is a HOST array of `world` device
+ * pointers, entry w = the (capacity_rows, peer_stride_rows) row buffer of rank w mapped into this process (e.g.
+ * a symmetric-memory allocation); entry `rank` is the local buffer. The calls only enqueue plain peer loads /
+ * stores; ordering against the other ranks (a barrier between phases) is the caller's.
+ *
+ * smoe_ep_dispatch: for every position m of this rank's expert-sorted slot list (global expert e, slot s):
+ *     peer[e / (E/world)][dst_offsets[e] + (m - first position of e)] = X[s / fan_out, :] * coeff[s]
+ *   `dst_offsets[e]` = first row reserved for this rank's rows of expert e in the owner's buffer (the owner's
+ *   buffer is then expert-grouped without any further copy). `slot_dest[s]` (nullable out) records
+ *   (owner rank << 40 | row) per slot for the way back.
+ * smoe_ep_combine:   out[t, :] = sum_j gates[t, j] * peer[rank(t,j)][row(t,j), :]   (gates nullable: plain sum)
+ * smoe_ep_gate_grad: d_gates[t, j] = <peer[rank(t,j)][row(t,j), :], grad_out[t, :]> */
+int smoe_ep_dispatch(const void* X, int64_t x_rows, int64_t stride_xm, const int64_t* sorted_expert_idxs,
+                     const int64_t* sorted_scattered_idxs, const int64_t* expert_offsets, const int64_t* dst_offsets,
+                     const void* coeff, int32_t fan_out, void* const* peer_bufs, int64_t peer_stride_rows,
+                     int64_t capacity_rows, int64_t* slot_dest, int64_t R, int32_t K, int32_t E, int32_t world,
+                     int32_t dtype, void* stream);
+int smoe_ep_combine(void* const* peer_bufs, int64_t peer_stride_rows, const int64_t* slot_dest, const void* gates,
+                    int64_t stride_gt, int64_t stride_gk, void* out, int64_t stride_om, int64_t T, int32_t k, int32_t N,
+                    int32_t world, int32_t dtype, void* stream);
+int smoe_ep_gate_grad(void* const* peer_bufs, int64_t peer_stride_rows, const int64_t* slot_dest, const void* grad_out,
+                      int64_t stride_gom, void* d_gates, int64_t stride_dgt, int64_t stride_dgk, int64_t T, int32_t k,
+                      int32_t N, int32_t world, int32_t dtype, void* stream);
 
 #ifdef __cplusplus
 }

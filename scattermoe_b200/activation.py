@@ -43,17 +43,19 @@ def resolve_activation(fn) -> Optional[int]:
     return None
 
 
-def _call(backward, up, dh, out, F, layout, act, alpha, limit):
+def _call(backward, up, dh, out, F, layout, act, alpha, limit, rows_dev=None):
+    """`rows_dev`: optional device int64 scalar with the live row count (rows beyond it are left untouched)."""
     lib = _lib.load()
     code = _lib.DTYPE_CODE[up.dtype]
     rows = up.size(0)
+    rd = 0 if rows_dev is None else rows_dev.data_ptr()
     with torch.cuda.device(up.device):
         if backward:
             rc = lib.smoe_activation_backward(up.data_ptr(), up.stride(0), dh.data_ptr(), dh.stride(0), out.data_ptr(),
-                                              out.stride(0), rows, F, layout, act, alpha, limit, code,
+                                              out.stride(0), rows, rd, F, layout, act, alpha, limit, code,
                                               _lib.stream_ptr(up.device))
         else:
-            rc = lib.smoe_activation_forward(up.data_ptr(), up.stride(0), out.data_ptr(), out.stride(0), rows, F,
+            rc = lib.smoe_activation_forward(up.data_ptr(), up.stride(0), out.data_ptr(), out.stride(0), rows, rd, F,
                                              layout, act, alpha, limit, code, _lib.stream_ptr(up.device))
     _lib.check(rc, "smoe_activation_backward" if backward else "smoe_activation_forward")
 

@@ -84,10 +84,11 @@ __device__ __forceinline__ void store_vec(T* p, const float (&f)[V]) {
 // One thread per V hidden columns of one row. V = 16/sizeof(T) on the vector path, 1 otherwise.
 template <typename T, int LAYOUT, int V>
 __global__ void __launch_bounds__(256)
-act_forward_kernel(const T* __restrict__ U, int64_t su, T* __restrict__ H, int64_t sh, int64_t rows, int F, int act,
-                   float alpha, float limit) {
+act_forward_kernel(const T* __restrict__ U, int64_t su, T* __restrict__ H, int64_t sh, int64_t rows,
+                   const int64_t* __restrict__ rows_dev, int F, int act, float alpha, float limit) {
   const int vec_per_row = F / V;
   const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (rows_dev) rows = min(rows, *rows_dev);     // live row count known only on the device
   if (gid >= rows * vec_per_row) return;
   const int64_t r = gid / vec_per_row;
   const int j = static_cast<int>(gid - r * vec_per_row) * V;
@@ -123,9 +124,11 @@ act_forward_kernel(const T* __restrict__ U, int64_t su, T* __restrict__ H, int64
 template <typename T, int LAYOUT, int V>
 __global__ void __launch_bounds__(256)
 act_backward_kernel(const T* __restrict__ U, int64_t su, const T* __restrict__ DH, int64_t sdh, T* __restrict__ DU,
-                    int64_t sdu, int64_t rows, int F, int act, float alpha, float limit) {
+                    int64_t sdu, int64_t rows, const int64_t* __restrict__ rows_dev, int F, int act, float alpha,
+                    float limit) {
   const int vec_per_row = F / V;
   const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (rows_dev) rows = min(rows, *rows_dev);
   if (gid >= rows * vec_per_row) return;
   const int64_t r = gid / vec_per_row;
   const int j = static_cast<int>(gid - r * vec_per_row) * V;
@@ -179,7 +182,7 @@ static inline bool aligned16p(const void* p) { return (reinterpret_cast<uintptr_
 
 template <typename T, int LAYOUT>
 static int act_launch(bool backward, const void* U, int64_t su, const void* DH, int64_t sdh, void* OUT, int64_t so,
-                      int64_t rows, int F, int act, float alpha, float limit, cudaStream_t stream) {
+                      int64_t rows, const int64_t* rows_dev, int F, int act, float alpha, float limit, cudaStream_t stream) {
   constexpr int VV = 16 / sizeof(T);
   // GPT_OSS scalar path pairs columns itself (V = 1 reads u[2j], u[2j+1]); vector path needs whole vectors
   bool vec = F % VV == 0 && su % VV == 0 && so % VV == 0 && aligned16p(U) && aligned16p(OUT);
@@ -190,15 +193,15 @@ static int act_launch(bool backward, const void* U, int64_t su, const void* DH, 
   if (vec) {
     if (backward)
       act_backward_kernel<T, LAYOUT, VV><<<grid, 256, 0, stream>>>((const T*)U, su, (const T*)DH, sdh, (T*)OUT, so, rows,
-                                                                  F, act, alpha, limit);
+                                                                  rows_dev, F, act, alpha, limit);
     else
-      act_forward_kernel<T, LAYOUT, VV><<<grid, 256, 0, stream>>>((const T*)U, su, (T*)OUT, so, rows, F, act, alpha, limit);
+      act_forward_kernel<T, LAYOUT, VV><<<grid, 256, 0, stream>>>((const T*)U, su, (T*)OUT, so, rows, rows_dev, F, act, alpha, limit);
   } else {
     if (backward)
       act_backward_kernel<T, LAYOUT, 1><<<grid, 256, 0, stream>>>((const T*)U, su, (const T*)DH, sdh, (T*)OUT, so, rows,
-                                                                 F, act, alpha, limit);
+                                                                 rows_dev, F, act, alpha, limit);
     else
-      act_forward_kernel<T, LAYOUT, 1><<<grid, 256, 0, stream>>>((const T*)U, su, (T*)OUT, so, rows, F, act, alpha, limit);
+      act_forward_kernel<T, LAYOUT, 1><<<grid, 256, 0, stream>>>((const T*)U, su, (T*)OUT, so, rows, rows_dev, F, act, alpha, limit);
   }
   SMOE_LAUNCH_CHECK();
   return SMOE_OK;
@@ -206,29 +209,30 @@ static int act_launch(bool backward, const void* U, int64_t su, const void* DH, 
 
 template <typename T>
 static int act_dispatch_layout(int layout, bool backward, const void* U, int64_t su, const void* DH, int64_t sdh,
-                               void* OUT, int64_t so, int64_t rows, int F, int act, float alpha, float limit,
-                               cudaStream_t stream) {
+                               void* OUT, int64_t so, int64_t rows, const int64_t* rows_dev, int F, int act, float alpha,
+                               float limit, cudaStream_t stream) {
   switch (layout) {
-    case LAYOUT_PLAIN: return act_launch<T, LAYOUT_PLAIN>(backward, U, su, DH, sdh, OUT, so, rows, F, act, alpha, limit, stream);
-    case LAYOUT_GLU_SECOND: return act_launch<T, LAYOUT_GLU_SECOND>(backward, U, su, DH, sdh, OUT, so, rows, F, act, alpha, limit, stream);
-    case LAYOUT_GLU_FIRST: return act_launch<T, LAYOUT_GLU_FIRST>(backward, U, su, DH, sdh, OUT, so, rows, F, act, alpha, limit, stream);
-    case LAYOUT_GPT_OSS: return act_launch<T, LAYOUT_GPT_OSS>(backward, U, su, DH, sdh, OUT, so, rows, F, act, alpha, limit, stream);
+    case LAYOUT_PLAIN: return act_launch<T, LAYOUT_PLAIN>(backward, U, su, DH, sdh, OUT, so, rows, rows_dev, F, act, alpha, limit, stream);
+    case LAYOUT_GLU_SECOND: return act_launch<T, LAYOUT_GLU_SECOND>(backward, U, su, DH, sdh, OUT, so, rows, rows_dev, F, act, alpha, limit, stream);
+    case LAYOUT_GLU_FIRST: return act_launch<T, LAYOUT_GLU_FIRST>(backward, U, su, DH, sdh, OUT, so, rows, rows_dev, F, act, alpha, limit, stream);
+    case LAYOUT_GPT_OSS: return act_launch<T, LAYOUT_GPT_OSS>(backward, U, su, DH, sdh, OUT, so, rows, rows_dev, F, act, alpha, limit, stream);
   }
   set_error("activation: unknown layout %d", layout);
   return SMOE_ERR_BAD_ARG;
 }
 
 static int act_entry(bool backward, const void* U, int64_t su, const void* DH, int64_t sdh, void* OUT, int64_t so,
-                     int64_t rows, int F, int layout, int act, float alpha, float limit, int dtype, void* stream) {
+                     int64_t rows, const int64_t* rows_dev, int F, int layout, int act, float alpha, float limit,
+                     int dtype, void* stream) {
   SMOE_CHECK_ARG(rows >= 0 && F >= 0, "activation: bad sizes rows=%lld F=%d", (long long)rows, F);
   SMOE_CHECK_ARG(act >= ACT_SILU && act <= ACT_IDENTITY, "activation: unknown function %d", act);
   if (rows == 0 || F == 0) return SMOE_OK;
   SMOE_CHECK_ARG(U && OUT && (!backward || DH), "activation: null pointer");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
-    case SMOE_F32: return act_dispatch_layout<float>(layout, backward, U, su, DH, sdh, OUT, so, rows, F, act, alpha, limit, st);
-    case SMOE_BF16: return act_dispatch_layout<__nv_bfloat16>(layout, backward, U, su, DH, sdh, OUT, so, rows, F, act, alpha, limit, st);
-    case SMOE_F16: return act_dispatch_layout<__half>(layout, backward, U, su, DH, sdh, OUT, so, rows, F, act, alpha, limit, st);
+    case SMOE_F32: return act_dispatch_layout<float>(layout, backward, U, su, DH, sdh, OUT, so, rows, rows_dev, F, act, alpha, limit, st);
+    case SMOE_BF16: return act_dispatch_layout<__nv_bfloat16>(layout, backward, U, su, DH, sdh, OUT, so, rows, rows_dev, F, act, alpha, limit, st);
+    case SMOE_F16: return act_dispatch_layout<__half>(layout, backward, U, su, DH, sdh, OUT, so, rows, rows_dev, F, act, alpha, limit, st);
   }
   set_error("activation: unknown dtype %d", dtype);
   return SMOE_ERR_BAD_ARG;
@@ -237,13 +241,16 @@ static int act_entry(bool backward, const void* U, int64_t su, const void* DH, i
 }  // namespace smoe
 
 extern "C" int smoe_activation_forward(const void* U, int64_t stride_um, void* H, int64_t stride_hm, int64_t rows,
-                                       int32_t F, int32_t layout, int32_t act, float alpha, float limit, int32_t dtype,
-                                       void* stream) {
-  return smoe::act_entry(false, U, stride_um, nullptr, 0, H, stride_hm, rows, F, layout, act, alpha, limit, dtype, stream);
+                                       const int64_t* rows_dev, int32_t F, int32_t layout, int32_t act, float alpha,
+                                       float limit, int32_t dtype, void* stream) {
+  return smoe::act_entry(false, U, stride_um, nullptr, 0, H, stride_hm, rows, rows_dev, F, layout, act, alpha, limit,
+                         dtype, stream);
 }
 
 extern "C" int smoe_activation_backward(const void* U, int64_t stride_um, const void* DH, int64_t stride_dhm, void* DU,
-                                        int64_t stride_dum, int64_t rows, int32_t F, int32_t layout, int32_t act,
-                                        float alpha, float limit, int32_t dtype, void* stream) {
-  return smoe::act_entry(true, U, stride_um, DH, stride_dhm, DU, stride_dum, rows, F, layout, act, alpha, limit, dtype, stream);
+                                        int64_t stride_dum, int64_t rows, const int64_t* rows_dev, int32_t F,
+                                        int32_t layout, int32_t act, float alpha, float limit, int32_t dtype,
+                                        void* stream) {
+  return smoe::act_entry(true, U, stride_um, DH, stride_dhm, DU, stride_dum, rows, rows_dev, F, layout, act, alpha, limit,
+                         dtype, stream);
 }

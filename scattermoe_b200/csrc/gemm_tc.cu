@@ -369,6 +369,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
 // serves the still un-grouped input (row = slot / fan_out) and zero-fills the rows past the segment end, the
 // only masking the ragged segments need. A tile is 128 DY features x BNW X features of one expert.
 struct WGradParams {
+  const uint8_t* DY; int64_t dy_row_bytes;
   const uint8_t* X; int64_t x_row_bytes; int64_t x_rows;
   uint8_t* DW; int64_t dw_e_bytes; int64_t dw_row_bytes;
   const int64_t* gather_idx; const int64_t* offsets;
@@ -454,8 +455,12 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_consta
     m_beg = seg_start[e];
     m_end = max(m_beg, seg_start[e + 1]);
   };
-  // a 64-row slab of X comes by TMA unless X is gathered or the slab crosses the end of the segment
-  auto slab_by_tma = [&](int c, int m_beg, int m_end) { return p.x_by_tma && (m_beg + (c + 1) * BK <= m_end); };
+  // A 64-row slab that crosses the end of the expert's segment is "ragged": both operands of it are copied with
+  // cp.async, which zero-fills the rows past the end. Rows past the end are either another expert's or not
+  // initialised at all; zeroing BOTH sides keeps a stray NaN/Inf there from reaching this expert's gradient.
+  // Whole slabs: DY always by TMA; X by TMA unless it has to be gathered.
+  auto slab_ragged = [&](int c, int m_beg, int m_end) { return m_beg + (c + 1) * BK > m_end; };
+  auto slab_by_tma = [&](int c, int m_beg, int m_end) { return p.x_by_tma && !slab_ragged(c, m_beg, m_end); };
 
   if (warp == 0) {
     // ---------------- DY slabs: TMA producer --------------------------------------------------------------
@@ -471,10 +476,14 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_consta
         if (!mbar_wait_warp(empty_bar(s), ph ^ 1, abort_flag, p.status, 11)) { ok = false; break; }
         if (lane == 0) {
           const bool x_too = slab_by_tma(c, m_beg, m_end);
-          mbar_arrive_expect_tx(full_bar(s), A_STAGE_BYTES + (x_too ? C::B_STAGE_BYTES : 0));
-          const uint32_t dst = smem_u32(sA + s * A_STAGE_BYTES);
-          tma_load_2d(dst, &tmap_dy, full_bar(s), n0, m_beg + c * BK);
-          tma_load_2d(dst + 64 * BK * 2, &tmap_dy, full_bar(s), n0 + 64, m_beg + c * BK);
+          if (slab_ragged(c, m_beg, m_end)) {
+            mbar_arrive(full_bar(s));          // nothing comes by TMA for this slab
+          } else {
+            mbar_arrive_expect_tx(full_bar(s), A_STAGE_BYTES + (x_too ? C::B_STAGE_BYTES : 0));
+            const uint32_t dst = smem_u32(sA + s * A_STAGE_BYTES);
+            tma_load_2d(dst, &tmap_dy, full_bar(s), n0, m_beg + c * BK);
+            tma_load_2d(dst + 64 * BK * 2, &tmap_dy, full_bar(s), n0 + 64, m_beg + c * BK);
+          }
           if (x_too) {
             const uint32_t dstb = smem_u32(sB + s * C::B_STAGE_BYTES);
 #pragma unroll
@@ -566,6 +575,20 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_consta
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
         if (!mbar_wait_warp(empty_bar(s), ph ^ 1, abort_flag, p.status, 14)) { ok = false; break; }
+        if (slab_ragged(c, m_beg, m_end)) {
+          // DY slab of the ragged tail: 64 rows x 128 features = 1024 16-byte chunks, 8 per thread
+          const int a_chunk = ptid & 15, a_row0 = ptid >> 4;
+          const bool n_ok = (n0 + a_chunk * 8) < p.N;
+          const uint32_t dsta = smem_u32(sA + s * A_STAGE_BYTES) + (a_chunk >> 3) * (64 * BK * 2);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int row = a_row0 + 8 * i;
+            const int64_t m = static_cast<int64_t>(m_beg) + c * BK + row;
+            const bool v = n_ok && m < m_end;
+            cp_async16(dsta + row * 128 + (((a_chunk & 7) ^ (row & 7)) << 4),
+                       v ? p.DY + m * p.dy_row_bytes + static_cast<int64_t>(n0 + a_chunk * 8) * 2 : p.DY, v ? 16u : 0u);
+          }
+        }
         if (!slab_by_tma(c, m_beg, m_end)) {
           const uint32_t dst = smem_u32(sB + s * C::B_STAGE_BYTES) + box_off;
 #pragma unroll
@@ -858,6 +881,7 @@ int launch_wgrad_tc(const WGradArgs& a) {
   const bool x_by_tma = a.gather_idx == nullptr && a.sxm >= a.K &&
                         encode_map2(&map_x, bf16, a.X, a.K, a.x_rows, static_cast<uint64_t>(a.sxm) * 2);
   WGradParams p;
+  p.DY = static_cast<const uint8_t*>(a.DY); p.dy_row_bytes = a.sdym * 2;
   p.x_by_tma = x_by_tma ? 1 : 0;
   p.X = static_cast<const uint8_t*>(a.X); p.x_row_bytes = a.sxm * 2; p.x_rows = a.x_rows;
   p.DW = static_cast<uint8_t*>(a.DW); p.dw_e_bytes = a.sdwe * 2; p.dw_row_bytes = a.sdwn * 2;

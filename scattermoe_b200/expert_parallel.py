@@ -1,0 +1,391 @@
+"""Expert parallelism for the MoE MLP: experts partitioned across the ranks of one process group, tokens
+data-parallel, one exchange step each way.
+
+The reference has no multi-GPU code at all (no torch.distributed import anywhere; README.md:8 leaves
+distribution to the surrounding framework), so nothing here mirrors a reference file. The layer computes exactly
+what `scattermoe.mlp.GLUMLP` (scattermoe/mlp.py:51-95) computes for the concatenated experts:
+
+    rank r owns experts [r*E/W, (r+1)*E/W) and T/W tokens with their router outputs
+    1. plan      stable sort of the local (token, slot) pairs by global expert id = by destination rank;
+                 per-(rank, expert) counts exchanged with one small all-to-all; ONE host read of 2W integers
+                 (NCCL's all-to-all-v needs its split sizes on the host)
+    2. dispatch  rows copied into expert order (`group` kernel), all-to-all-v; received rows land in local HBM
+    3. experts   local routing sort (k = 1) -> grouped GEMM -> activation -> grouped GEMM on the received rows
+    4. combine   all-to-all-v back, rows return in the sender's expert order, gate-weighted top-k sum
+    backward mirrors 4 -> 1; weight gradients stay local (experts are not replicated, no all-reduce).
+
+Row kernels and the sort are injected (`RowOps`) so that the host logic (plans, split sizes, permutations, the
+autograd wiring of the collectives) can be exercised by CPU `gloo` ranks in the tests with stand-ins defined by
+the tests; the defaults are the CUDA kernels of this package and there is no other implementation in here.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Optional
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from . import activation as _act
+from .kernels import ops
+from .parallel_experts import flatten_sort_count, parallel_linear
+
+
+class RowOps:
+    """The row-level kernels the exchange needs. Default: this package's CUDA kernels."""
+    sort = staticmethod(flatten_sort_count)          # (ids (n, k), E) -> (sorted ids, sorted slot idx, inclusive offsets)
+    group = staticmethod(ops.group)                  # (A, idx, coeff=None, fan_out=1) -> A[idx // fan_out] * coeff[idx]
+    topk_reduce = staticmethod(ops.topk_reduce)      # (expanded (T*k, N), gates or None, T, k) -> (T, N)
+    gate_grad = staticmethod(ops.gate_grad)          # (expanded, grad_out, T, k) -> (T, k)
+
+
+@dataclass
+class Plan:
+    """Everything both exchange directions need; built once per forward."""
+    world: int
+    k: int
+    tokens: int
+    sorted_scattered_idxs: torch.Tensor    # (R_local,) slot of every row in send (expert) order
+    inverse: torch.Tensor                  # (R_local,) position in send order of every slot
+    send_splits: List[int]                 # rows sent to each rank
+    recv_splits: List[int]                 # rows received from each rank
+    recv_expert_ids: torch.Tensor          # (R_recv,) LOCAL expert id of every received row
+    group: Optional[dist.ProcessGroup]
+
+
+def split_sizes_from_counts(counts_by_rank_expert: torch.Tensor) -> torch.Tensor:
+    """(W, E_local) per-destination per-expert counts -> (W,) rows per destination."""
+    return counts_by_rank_expert.sum(dim=1)
+
+
+def make_plan(expert_idxs: torch.Tensor, num_experts: int, group=None, rowops=RowOps) -> Plan:
+    """expert_idxs: (T_local, k) GLOBAL expert ids. Experts are owned in contiguous blocks of E / world."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if num_experts % world:
+        raise AssertionError("num_experts (%d) must be divisible by the world size (%d)" % (num_experts, world))
+    e_local = num_experts // world
+    T, k = expert_idxs.shape
+    sorted_e, sorted_idx, offsets = rowops.sort(expert_idxs, num_experts)
+    counts = torch.diff(offsets, prepend=offsets.new_zeros(1)).view(world, e_local)      # rows per (dest, expert)
+    inverse = torch.empty_like(sorted_idx)
+    inverse[sorted_idx] = torch.arange(sorted_idx.numel(), device=sorted_idx.device, dtype=sorted_idx.dtype)
+    if world == 1:
+        recv_counts = counts
+        splits = [int(T * k)]
+        return Plan(1, k, T, sorted_idx, inverse, splits, splits, sorted_e.clone(), group)
+    recv_counts = torch.empty_like(counts)                                               # rows per (source, expert)
+    dist.all_to_all_single(recv_counts, counts.contiguous(), group=group)
+    both = torch.stack([split_sizes_from_counts(counts), split_sizes_from_counts(recv_counts)]).cpu()   # the one host read
+    send_splits, recv_splits = both[0].tolist(), both[1].tolist()
+    local_ids = torch.arange(e_local, device=counts.device, dtype=torch.int64).repeat(world)
+    recv_expert_ids = torch.repeat_interleave(local_ids, recv_counts.flatten(), output_size=int(sum(recv_splits)))
+    return Plan(world, k, T, sorted_idx, inverse, send_splits, recv_splits, recv_expert_ids, group)
+
+
+class _AllToAllRows(torch.autograd.Function):
+    """all-to-all-v of matrix rows; the gradient travels the opposite way with the split lists swapped."""
+
+    @staticmethod
+    def forward(ctx, rows, send_splits, recv_splits, group):
+        ctx.cfg = (send_splits, recv_splits, group)
+        out = rows.new_empty((int(sum(recv_splits)), rows.size(1)))
+        dist.all_to_all_single(out, rows.contiguous(), recv_splits, send_splits, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        send_splits, recv_splits, group = ctx.cfg
+        back = grad.new_empty((int(sum(send_splits)), grad.size(1)))
+        dist.all_to_all_single(back, grad.contiguous(), send_splits, recv_splits, group=group)
+        return back, None, None, None
+
+
+def all_to_all_rows(rows, send_splits, recv_splits, group):
+    if len(send_splits) == 1:
+        return rows
+    return _AllToAllRows.apply(rows, send_splits, recv_splits, group)
+
+
+class _ToExpertOrder(torch.autograd.Function):
+    """x (T, d) -> one row per (token, slot) in send order. Backward: back to slot order, sum over the k slots."""
+
+    @staticmethod
+    def forward(ctx, x, plan, rowops):
+        ctx.plan, ctx.rowops = plan, rowops
+        return rowops.group(x, plan.sorted_scattered_idxs, fan_out=plan.k)
+
+    @staticmethod
+    def backward(ctx, grad):
+        plan, rowops = ctx.plan, ctx.rowops
+        by_slot = rowops.group(grad.contiguous(), plan.inverse, fan_out=1)
+        dx = by_slot if plan.k == 1 else rowops.topk_reduce(by_slot, None, plan.tokens, plan.k)
+        return dx, None, None
+
+
+class _GatedCombine(torch.autograd.Function):
+    """rows in send order (R, d) + gates (T, k) -> out[t] = sum_j gates[t, j] * row_of_slot(t*k + j)."""
+
+    @staticmethod
+    def forward(ctx, rows, gates, plan, rowops):
+        by_slot = rowops.group(rows.contiguous(), plan.inverse, fan_out=1)
+        ctx.plan, ctx.rowops = plan, rowops
+        ctx.save_for_backward(by_slot, gates)
+        return rowops.topk_reduce(by_slot, gates, plan.tokens, plan.k)
+
+    @staticmethod
+    def backward(ctx, grad):
+        plan, rowops = ctx.plan, ctx.rowops
+        by_slot, gates = ctx.saved_tensors
+        grad = grad.contiguous()
+        d_gates = rowops.gate_grad(by_slot, grad, plan.tokens, plan.k).to(gates.dtype) if ctx.needs_input_grad[1] else None
+        d_rows = rowops.group(grad, plan.sorted_scattered_idxs, coeff=gates.reshape(-1).to(grad.dtype), fan_out=plan.k)
+        return d_rows, d_gates, None, None
+
+
+def dispatch(x: torch.Tensor, plan: Plan, rowops=RowOps) -> torch.Tensor:
+    """(T_local, d) tokens -> (R_recv, d) rows for this rank's experts, ordered by (source rank, local expert)."""
+    return all_to_all_rows(_ToExpertOrder.apply(x, plan, rowops), plan.send_splits, plan.recv_splits, plan.group)
+
+
+def combine(rows: torch.Tensor, gates: torch.Tensor, plan: Plan, rowops=RowOps) -> torch.Tensor:
+    """(R_recv, d) expert outputs in received order -> (T_local, d) gate-weighted sums at the owning rank."""
+    back = all_to_all_rows(rows, plan.recv_splits, plan.send_splits, plan.group)
+    return _GatedCombine.apply(back, gates, plan, rowops)
+
+
+class ExpertParallelGLUMLP(nn.Module):
+    """`GLUMLP` with its experts split across the ranks of `group`. Parameters have the reference's names and
+    layouts for the LOCAL experts: experts.weight (E/W, 2*hidden, input), output_experts.weight (E/W, input, hidden);
+    concatenating the ranks' tensors along dim 0 gives the reference module's parameters."""
+
+    def __init__(self, input_size, hidden_size, num_experts, top_k, group=None, activation=nn.SiLU()):
+        super().__init__()
+        from .parallel_experts import ParallelExperts
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        if num_experts % world:
+            raise AssertionError("num_experts must be divisible by the world size")
+        self.num_experts = num_experts
+        self.local_experts = num_experts // world
+        self.input_size, self.hidden_size = input_size, hidden_size
+        self.top_k = min(top_k, num_experts)
+        self.group = group
+        self.activation = activation
+        self.experts = ParallelExperts(self.local_experts, input_size, 2 * hidden_size)
+        self.output_experts = ParallelExperts(self.local_experts, hidden_size, input_size)
+
+    def local_expert_mlp(self, rows: torch.Tensor, local_expert_ids: torch.Tensor) -> torch.Tensor:
+        """The expert MLP on received rows: every row has exactly one (local) expert, i.e. top_k = 1."""
+        routing = flatten_sort_count(local_expert_ids.view(-1, 1), self.local_experts)
+        up = self.experts(rows, 1, *routing, grouped_out=True)
+        code = _act.resolve_activation(self.activation) if _act.FUSE else None
+        if code is None:
+            linear_half, gate_half = up.chunk(2, dim=-1)
+            hidden = self.activation(gate_half) * linear_half
+        else:
+            hidden = _act.fused_activation(up, _act.LAYOUT_GLU_SECOND, code)
+        return self.output_experts(hidden, 1, *routing, grouped_in=True)
+
+    def forward(self, x: torch.Tensor, expert_p: torch.Tensor, expert_idxs: torch.Tensor):
+        lead = x.shape[:-1]
+        tokens = x.reshape(-1, x.shape[-1])
+        plan = make_plan(expert_idxs.reshape(tokens.size(0), -1), self.num_experts, self.group)
+        rows = dispatch(tokens, plan)
+        out_rows = self.local_expert_mlp(rows, plan.recv_expert_ids)
+        y = combine(out_rows, expert_p.reshape(tokens.size(0), -1), plan)
+        return y.view(*lead, y.size(-1))
+
+
+# ------------------------------------------------------------------------------------------------------------
+# NVLink peer-memory exchange: no all-to-all, no regroup copies, no host synchronisation
+# ------------------------------------------------------------------------------------------------------------
+
+class PeerRowBuffers:
+    """Symmetric (peer-mapped) row buffers of one expert-parallel layer: `x` (dispatched tokens), `y` (expert
+    outputs), `g` (dispatched output gradients), `dx` (input gradients of the dispatched rows). Every rank can
+    address every rank's copy with plain loads and stores over NVLink. Capacity is the worst case (all rows of
+    all ranks routed to one rank) unless told otherwise, so no routing outcome can overflow a buffer."""
+
+    NAMES = ("x", "y", "g", "dx")
+
+    def __init__(self, capacity_rows: int, width: int, dtype, device, group=None):
+        import ctypes
+        import os
+        # plain peer mappings only: this code never uses NVLink multicast
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.capacity, self.width = int(capacity_rows), int(width)
+        self.local, self.ptrs = {}, {}
+        for name in self.NAMES:
+            t = symm.empty((self.capacity, self.width), dtype=dtype, device=device)
+            hdl = symm.rendezvous(t, self.group)
+            self.local[name] = t
+            self.ptrs[name] = (ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs])
+        self._token = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def barrier(self):
+        """Stream-ordered barrier across the ranks: kernels enqueued after it on any rank run after the kernels
+        enqueued before it on every rank. (One tiny NCCL all-reduce; no host synchronisation.)"""
+        dist.all_reduce(self._token, group=self.group)
+
+
+def _ep_call(name, *args):
+    from . import _lib
+    rc = getattr(_lib.load(), name)(*args)
+    _lib.check(rc, name)
+
+
+class _PeerExchangeMLP(torch.autograd.Function):
+    """dispatch -> local expert GLU-MLP -> combine, forward and backward, on peer row buffers."""
+
+    @staticmethod
+    def forward(ctx, x, gates, expert_idxs, w_up, w_down, layer):
+        from . import _lib
+        bufs: PeerRowBuffers = layer.buffers
+        W, rank, E = bufs.world, bufs.rank, layer.num_experts
+        e_local = E // W
+        T, k = expert_idxs.shape
+        R, d = T * k, x.size(1)
+        dev = x.device
+        code = _lib.DTYPE_CODE[x.dtype]
+        stream = _lib.stream_ptr(dev)
+        x = x.contiguous()
+        gates = gates.to(x.dtype).contiguous()
+
+        # 1. local routing sort; every rank learns every rank's per-expert counts (tiny all-gather)
+        sorted_e, sorted_idx, offsets = flatten_sort_count(expert_idxs, E)
+        counts = torch.diff(offsets, prepend=offsets.new_zeros(1))
+        counts_all = torch.empty((W, E), dtype=counts.dtype, device=dev)
+        dist.all_gather_into_tensor(counts_all, counts, group=bufs.group)
+        # 2. where my rows of expert e start in the owner's buffer; my own experts' inclusive offsets
+        tot = counts_all.sum(0).view(W, e_local)
+        ebase = (tot.cumsum(1) - tot).flatten()
+        dst_off = (ebase + (counts_all.cumsum(0) - counts_all)[rank]).contiguous()
+        local_offsets = tot[rank].cumsum(0).contiguous()
+        rows_dev = local_offsets[-1:].contiguous()
+        slot_dest = torch.empty(R, dtype=torch.int64, device=dev)
+        # 3. dispatch: rows go straight to their final, expert-grouped position on the owning rank
+        with torch.cuda.device(dev):
+            _ep_call("smoe_ep_dispatch", x.data_ptr(), T, x.stride(0), sorted_e.data_ptr(), sorted_idx.data_ptr(),
+                     offsets.data_ptr(), dst_off.data_ptr(), 0, k, bufs.ptrs["x"], bufs.width, bufs.capacity,
+                     slot_dest.data_ptr(), R, d, E, W, code, stream)
+        bufs.barrier()
+        # 4. local experts on the received rows (already grouped: no sort, no copy)
+        cap = bufs.capacity
+        dummy = layer.dummy_index(cap, dev)
+        xb, yb = bufs.local["x"], bufs.local["y"]
+        up = ops.scatter2scatter(xb, w_up.permute(0, 2, 1), dummy, dummy, 1, x_grouped=True, y_grouped=True,
+                                 expert_offsets=local_offsets)
+        hidden = torch.empty((cap, w_down.size(2)), dtype=x.dtype, device=dev)
+        _act._call(False, up, None, hidden, hidden.size(1), _act.LAYOUT_GLU_SECOND, layer.act_code, 1.702, 7.0, rows_dev)
+        ops.scatter2scatter(hidden, w_down.permute(0, 2, 1), dummy, dummy, 1, x_grouped=True, y_grouped=True, out=yb,
+                            expert_offsets=local_offsets)
+        bufs.barrier()
+        # 5. combine: pull my tokens' k rows from the owners and reduce with the gates
+        out = torch.empty((T, d), dtype=x.dtype, device=dev)
+        with torch.cuda.device(dev):
+            _ep_call("smoe_ep_combine", bufs.ptrs["y"], bufs.width, slot_dest.data_ptr(), gates.data_ptr(),
+                     gates.stride(0), gates.stride(1), out.data_ptr(), out.stride(0), T, k, d, W, code, stream)
+        layer.last_rows_dev = rows_dev          # live rows of the local buffers (device scalar), for accounting
+        ctx.layer = layer
+        ctx.shape = (T, k, d)
+        ctx.save_for_backward(gates, sorted_e, sorted_idx, offsets, dst_off, local_offsets, rows_dev, slot_dest, up,
+                              hidden, w_up, w_down)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        from . import _lib
+        layer = ctx.layer
+        bufs: PeerRowBuffers = layer.buffers
+        (gates, sorted_e, sorted_idx, offsets, dst_off, local_offsets, rows_dev, slot_dest, up, hidden, w_up,
+         w_down) = ctx.saved_tensors
+        T, k, d = ctx.shape
+        W, E = bufs.world, layer.num_experts
+        dev = grad_out.device
+        grad_out = grad_out.to(up.dtype).contiguous()
+        code = _lib.DTYPE_CODE[up.dtype]
+        stream = _lib.stream_ptr(dev)
+        cap = bufs.capacity
+        dummy = layer.dummy_index(cap, dev)
+        d_gates = torch.empty((T, k), dtype=up.dtype, device=dev)
+        with torch.cuda.device(dev):
+            # gate gradient from the expert outputs still sitting in the owners' buffers
+            _ep_call("smoe_ep_gate_grad", bufs.ptrs["y"], bufs.width, slot_dest.data_ptr(), grad_out.data_ptr(),
+                     grad_out.stride(0), d_gates.data_ptr(), d_gates.stride(0), d_gates.stride(1), T, k, d, W, code, stream)
+            # gate-scaled output gradient dispatched to the same positions the inputs went to
+            _ep_call("smoe_ep_dispatch", grad_out.data_ptr(), T, grad_out.stride(0), sorted_e.data_ptr(),
+                     sorted_idx.data_ptr(), offsets.data_ptr(), dst_off.data_ptr(), gates.data_ptr(), k, bufs.ptrs["g"],
+                     bufs.width, bufs.capacity, 0, T * k, d, E, W, code, stream)
+        bufs.barrier()
+        xb, gb, dxb = bufs.local["x"], bufs.local["g"], bufs.local["dx"]
+        e_local = w_up.size(0)
+        d_hidden = ops.scatter2scatter(gb, w_down, dummy, dummy, 1, x_grouped=True, y_grouped=True,
+                                       expert_offsets=local_offsets)
+        d_w_down, _ = ops.group_bwd_W(gb, hidden, local_offsets, e_local)
+        d_up = torch.empty_like(up)
+        _act._call(True, up, d_hidden, d_up, hidden.size(1), _act.LAYOUT_GLU_SECOND, layer.act_code, 1.702, 7.0, rows_dev)
+        d_w_up, _ = ops.group_bwd_W(d_up, xb, local_offsets, e_local)
+        ops.scatter2scatter(d_up, w_up, dummy, dummy, 1, x_grouped=True, y_grouped=True, out=dxb,
+                            expert_offsets=local_offsets)
+        bufs.barrier()
+        dx = torch.empty((T, d), dtype=up.dtype, device=dev)
+        with torch.cuda.device(dev):
+            _ep_call("smoe_ep_combine", bufs.ptrs["dx"], bufs.width, slot_dest.data_ptr(), 0, 0, 0, dx.data_ptr(),
+                     dx.stride(0), T, k, d, W, code, stream)
+        # weight gradients come back as (E, K, N) views of (E, N, K) buffers = the parameters' own layout
+        return dx, d_gates, None, d_w_up.permute(0, 2, 1), d_w_down.permute(0, 2, 1), None
+
+
+class PeerExpertParallelGLUMLP(ExpertParallelGLUMLP):
+    """Same layer and parameters as `ExpertParallelGLUMLP`, with the two all-to-all-v exchanges replaced by
+    kernels that write / read the peers' row buffers directly over NVLink (csrc/ep.cu): the dispatched rows land
+    expert-grouped at the owner, the combine pulls and reduces in one pass, and nothing is read back to the host.
+    16-bit dtypes, input and hidden sizes that are multiples of 8, SiLU / GELU / ReLU gate activations.
+
+    The buffers belong to the layer and are reused by every step: run one forward (+ backward) at a time per
+    layer, with the same number of steps on every rank.
+    """
+
+    def __init__(self, input_size, hidden_size, num_experts, top_k, group=None, activation=nn.SiLU(),
+                 capacity_rows=None, global_tokens=None):
+        super().__init__(input_size, hidden_size, num_experts, top_k, group=group, activation=activation)
+        self.act_code = _act.resolve_activation(activation)
+        if self.act_code is None:
+            raise AssertionError("PeerExpertParallelGLUMLP needs an activation this library fuses (SiLU, GELU, ReLU)")
+        if input_size % 8 or hidden_size % 8:
+            raise AssertionError("input_size and hidden_size must be multiples of 8")
+        self._capacity_arg, self._global_tokens = capacity_rows, global_tokens
+        self.buffers: Optional[PeerRowBuffers] = None
+        self._dummy = None
+
+    def dummy_index(self, n, device):
+        """Index tensors are not read when both sides of a grouped GEMM are in expert order; the operator's
+        signature still wants them."""
+        if self._dummy is None or self._dummy.numel() != n or self._dummy.device != device:
+            self._dummy = torch.zeros(n, dtype=torch.int64, device=device)
+        return self._dummy
+
+    def _ensure_buffers(self, x, local_rows):
+        if self.buffers is not None:
+            return
+        world = dist.get_world_size(self.group)
+        cap = self._capacity_arg
+        if cap is None:
+            cap = (self._global_tokens * self.top_k) if self._global_tokens else local_rows * world
+        cap = (int(cap) + 127) // 128 * 128
+        self.buffers = PeerRowBuffers(cap, self.input_size, x.dtype, x.device, self.group)
+
+    def forward(self, x: torch.Tensor, expert_p: torch.Tensor, expert_idxs: torch.Tensor):
+        if x.dtype not in (torch.bfloat16, torch.float16):
+            raise AssertionError("PeerExpertParallelGLUMLP runs in bfloat16 / float16")
+        lead = x.shape[:-1]
+        tokens = x.reshape(-1, x.shape[-1])
+        idx = expert_idxs.reshape(tokens.size(0), -1)
+        self._ensure_buffers(tokens, idx.numel())
+        y = _PeerExchangeMLP.apply(tokens, expert_p.reshape(tokens.size(0), -1), idx, self.experts.weight,
+                                   self.output_experts.weight, self)
+        return y.view(*lead, y.size(-1))

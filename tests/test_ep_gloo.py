@@ -1,0 +1,132 @@
+"""Expert-parallel host logic on CPU ranks (gloo, world size 2 and 4): plans, split sizes, permutations, the autograd
+wiring of the two all-to-all-v exchanges. The CUDA row kernels are replaced by torch stand-ins defined HERE (the
+product has no CPU implementation); the expert arithmetic is the oracle's dense loop. The result of the sharded
+run must equal the single-process oracle on the gathered problem, forward and every gradient."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "oracle"))
+
+
+class TorchRowOps:
+    """CPU stand-ins with the signatures of scattermoe_b200.expert_parallel.RowOps."""
+
+    @staticmethod
+    def sort(ids, E):
+        import scattermoe_oracle as oracle
+        return oracle.flatten_sort_count(ids, E)
+
+    @staticmethod
+    def group(A, idx, coeff=None, fan_out=1):
+        rows = A[torch.div(idx, fan_out, rounding_mode="floor")]
+        return rows if coeff is None else rows * coeff.reshape(-1)[idx][:, None]
+
+    @staticmethod
+    def topk_reduce(expanded, gates, T, k):
+        v = expanded.view(T, k, -1)
+        return v.sum(1) if gates is None else (gates.unsqueeze(1) @ v).squeeze(1)
+
+    @staticmethod
+    def gate_grad(expanded, grad_out, T, k):
+        return (expanded.view(T, k, -1) @ grad_out.unsqueeze(-1)).squeeze(-1)
+
+
+def _problem(seed=0, T=48, d=16, F=12, E=8, k=3):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(T, d, generator=g, dtype=torch.float64)
+    logits = torch.randn(T, E, generator=g, dtype=torch.float64)
+    logits[:, 2] -= 50.0                      # an expert nobody routes to
+    p, idx = torch.topk(torch.softmax(logits, -1), k)
+    w1 = torch.randn(E, d, 2 * F, generator=g, dtype=torch.float64) * 0.3
+    w2 = torch.randn(E, F, d, generator=g, dtype=torch.float64) * 0.3
+    dy = torch.randn(T, d, generator=g, dtype=torch.float64)
+    return x, p, idx, w1, w2, dy
+
+
+def _worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import scattermoe_oracle as oracle
+        from scattermoe_b200 import expert_parallel as ep
+        x, p, idx, w1, w2, dy = _problem()
+        T, E = x.size(0), w1.size(0)
+        tl, el = T // world, E // world
+        sl = slice(rank * tl, (rank + 1) * tl)
+        xl = x[sl].clone().requires_grad_()
+        pl = p[sl].clone().requires_grad_()
+        w1l = w1[rank * el:(rank + 1) * el].clone().requires_grad_()
+        w2l = w2[rank * el:(rank + 1) * el].clone().requires_grad_()
+
+        plan = ep.make_plan(idx[sl], E, rowops=TorchRowOps)
+        assert sum(plan.send_splits) == tl * idx.size(1)
+        assert plan.recv_expert_ids.numel() == sum(plan.recv_splits)
+        rows = ep.dispatch(xl, plan, rowops=TorchRowOps)
+        # dense expert arithmetic on the received rows (each row has one local expert)
+        out = torch.zeros(rows.size(0), x.size(1), dtype=rows.dtype)
+        for e in range(el):
+            sel = (plan.recv_expert_ids == e).nonzero().squeeze(-1)
+            if sel.numel():
+                h = oracle.act_glu_second_half(rows[sel] @ w1l[e])
+                out = out.index_add(0, sel, h @ w2l[e])
+        y = ep.combine(out, pl, plan, rowops=TorchRowOps)
+        grads = torch.autograd.grad(y, [xl, pl, w1l, w2l], dy[sl])
+
+        want = oracle.moe_mlp_forward_backward(x, p, idx, w1, w2, None, None, oracle.act_glu_second_half, dy,
+                                               compute_dtype=torch.float64)
+        checks = [("y", y, want["y"][sl]), ("dx", grads[0], want["d_x"][sl]), ("dp", grads[1], want["d_expert_p"][sl]),
+                  ("dw1", grads[2], want["d_w1"][rank * el:(rank + 1) * el]),
+                  ("dw2", grads[3], want["d_w2"][rank * el:(rank + 1) * el])]
+        for name, got, ref in checks:
+            err = (got.detach() - ref).abs().max().item()
+            assert err < 1e-9, "%s rank %d: %g" % (name, rank, err)
+        # the counts every rank received must add up to the global histogram of its experts
+        hist = torch.bincount(idx.flatten(), minlength=E)[rank * el:(rank + 1) * el]
+        assert torch.equal(torch.bincount(plan.recv_expert_ids, minlength=el), hist)
+        ret[rank] = "ok"
+    except Exception as e:  # surface the failure in the parent
+        import traceback
+        ret[rank] = "FAILED: " + traceback.format_exc()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_exchange_on_gloo_ranks(world):
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        procs = [ctx.Process(target=_worker, args=(r, world, port, ret)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout=180)
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                raise AssertionError("a rank did not finish")
+        assert {r: ret.get(r) for r in range(world)} == {r: "ok" for r in range(world)}
+
+
+def test_plan_on_a_single_process_is_the_plain_routing_sort():
+    """Without a process group the plan degenerates to one rank that keeps every row."""
+    from scattermoe_b200 import expert_parallel as ep
+    x, p, idx, w1, w2, dy = _problem(seed=3)
+    plan = ep.make_plan(idx, w1.size(0), rowops=TorchRowOps)
+    assert plan.world == 1 and plan.send_splits == plan.recv_splits == [idx.numel()]
+    assert torch.equal(plan.inverse[plan.sorted_scattered_idxs], torch.arange(idx.numel()))
+    assert torch.equal(plan.recv_expert_ids, torch.sort(idx.flatten()).values)
+    rows = ep.dispatch(x, plan, rowops=TorchRowOps)
+    assert torch.equal(rows, x[plan.sorted_scattered_idxs // idx.size(1)])

@@ -1,0 +1,114 @@
+"""Expert-parallel layer on GPUs: with one rank it must equal `GLUMLP`; with two ranks (NCCL, when the box has two
+GPUs) each rank's outputs and gradients must equal the matching slices of the single-GPU layer on the gathered
+problem. Ranks leave only after all work is done; NVLS is switched off for the child processes."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _problem(T=512, d=256, F=128, E=8, k=2, seed=5):
+    g = torch.Generator().manual_seed(seed)
+    bf = torch.bfloat16
+    x = torch.randn(T, d, generator=g).to(bf)
+    p, idx = torch.topk(torch.softmax(torch.randn(T, E, generator=g), -1), k)
+    w1 = (torch.randn(E, 2 * F, d, generator=g) * 0.05).to(bf)
+    w2 = (torch.randn(E, d, F, generator=g) * 0.05).to(bf)
+    dy = torch.randn(T, d, generator=g).to(bf)
+    return x, p.to(bf), idx, w1, w2, dy
+
+
+def _reference_on(device, x, p, idx, w1, w2, dy):
+    import scattermoe_b200 as sm
+    E, F2, d = w1.shape
+    m = sm.mlp.GLUMLP(d, F2 // 2, E, idx.size(1)).to(device).bfloat16()
+    with torch.no_grad():
+        m.experts.weight.copy_(w1)
+        m.output_experts.weight.copy_(w2)
+    xx, pp = x.to(device).requires_grad_(), p.to(device).requires_grad_()
+    y = m(xx, pp, idx.to(device))
+    g = torch.autograd.grad(y, [xx, pp, m.experts.weight, m.output_experts.weight], dy.to(device))
+    return [t.float().cpu() for t in [y] + list(g)]
+
+
+def _close(name, got, want):
+    s = max(1.0, want.abs().max().item() / 4)
+    torch.testing.assert_close(got.float().cpu() / s, want / s, rtol=2e-2, atol=2e-2, msg=lambda m: name + ": " + m)
+
+
+def test_single_rank_equals_glumlp():
+    import scattermoe_b200 as sm
+    from scattermoe_b200.expert_parallel import ExpertParallelGLUMLP
+    dev = torch.device("cuda", 0)
+    x, p, idx, w1, w2, dy = _problem()
+    want = _reference_on(dev, x, p, idx, w1, w2, dy)
+    m = ExpertParallelGLUMLP(x.size(1), w2.size(2), w1.size(0), idx.size(1)).to(dev).bfloat16()
+    with torch.no_grad():
+        m.experts.weight.copy_(w1)
+        m.output_experts.weight.copy_(w2)
+    xx, pp = x.to(dev).requires_grad_(), p.to(dev).requires_grad_()
+    y = m(xx, pp, idx.to(dev))
+    g = torch.autograd.grad(y, [xx, pp, m.experts.weight, m.output_experts.weight], dy.to(dev))
+    for name, got, ref in zip(("y", "dx", "dp", "dw1", "dw2"), [y] + list(g), want):
+        _close(name, got, ref)
+    sm.check_device_status(dev)
+
+
+def _worker(rank, world, port, ret, peer=False):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import scattermoe_b200 as sm
+        from scattermoe_b200.expert_parallel import ExpertParallelGLUMLP, PeerExpertParallelGLUMLP
+        x, p, idx, w1, w2, dy = _problem()
+        T, E = x.size(0), w1.size(0)
+        tl, el = T // world, E // world
+        ts, es = slice(rank * tl, (rank + 1) * tl), slice(rank * el, (rank + 1) * el)
+        want = _reference_on(dev, x, p, idx, w1, w2, dy)
+        cls = PeerExpertParallelGLUMLP if peer else ExpertParallelGLUMLP
+        m = cls(x.size(1), w2.size(2), E, idx.size(1)).to(dev).bfloat16()
+        with torch.no_grad():
+            m.experts.weight.copy_(w1[es])
+            m.output_experts.weight.copy_(w2[es])
+        xx, pp = x[ts].to(dev).requires_grad_(), p[ts].to(dev).requires_grad_()
+        for _ in range(3):      # repeated: later passes run on warm communicators and reused buffers
+            y = m(xx, pp, idx[ts].to(dev))
+            g = torch.autograd.grad(y, [xx, pp, m.experts.weight, m.output_experts.weight], dy[ts].to(dev))
+        _close("y", y, want[0][ts]); _close("dx", g[0], want[1][ts]); _close("dp", g[1], want[2][ts])
+        _close("dw1", g[2], want[3][es]); _close("dw2", g[3], want[4][es])
+        sm.check_device_status(dev)
+        torch.cuda.synchronize()
+        dist.barrier()
+        ret[rank] = "ok"
+    except Exception:
+        import traceback
+        ret[rank] = "FAILED: " + traceback.format_exc()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("peer", [False, True], ids=["nccl_all_to_all", "nvlink_peer_memory"])
+def test_two_ranks_equal_the_single_gpu_layer(peer):
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, ret, peer)) for r in range(2)]
+        for q in procs:
+            q.start()
+        for q in procs:
+            q.join(timeout=240)
+        for q in procs:
+            if q.is_alive():
+                q.terminate()
+                raise AssertionError("a rank did not finish")
+        assert {r: ret.get(r) for r in range(2)} == {0: "ok", 1: "ok"}
