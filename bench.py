@@ -192,13 +192,14 @@ def run_step(c, layer, x, p, idx, dy):
 class LaunchCounter:
     """Counts the kernels this library launches: a proxy in front of the ctypes library that knows how many
     kernels each C entry point enqueues."""
-    KERNELS = {"smoe_ep_dispatch": 1, "smoe_ep_combine": 1, "smoe_ep_gate_grad": 1, "smoe_sort_count": 3, "smoe_sort_count_static": 3, "smoe_offsets_from_sorted": 1,
+    KERNELS = {"smoe_ep_dispatch": 1, "smoe_ep_return": 1, "smoe_sort_count": 3, "smoe_sort_count_static": 3, "smoe_offsets_from_sorted": 1,
                "smoe_scatter2scatter": 1, "smoe_group_bwd_w": 1, "smoe_group": 1, "smoe_topk_reduce": 1,
                "smoe_gate_grad": 1, "smoe_activation_forward": 1, "smoe_activation_backward": 1}
 
     def __init__(self):
         from scattermoe_b200 import _lib
         self._mod, self._real, self.count = _lib, _lib.load(), 0
+        self.events = []          # (entry point, start event, end event) on the stream the call enqueued on
 
     def __getattr__(self, name):
         fn = getattr(self._real, name)
@@ -210,8 +211,19 @@ class LaunchCounter:
             self.count += n
             if name == "smoe_group_bwd_w" and a[14]:      # a bias gradient adds its own column-sum kernel
                 self.count += 1
-            return fn(*a)
+            s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s0.record()
+            rc = fn(*a)
+            s1.record()
+            self.events.append((name, s0, s1))
+            return rc
         return counted
+
+    def ms_by_entry_point(self):
+        out = {}
+        for name, a, z in self.events:
+            out[name] = out.get(name, 0.0) + a.elapsed_time(z)
+        return out
 
     def install(self):
         self._mod._lib = self
@@ -470,6 +482,8 @@ def main():
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps},
             # kernels of this library launched by this rank inside the timed region (counted at the C-ABI boundary)
             "gpu_launches": counter.count,
+            # device time between the events bracketing each C-ABI call, summed over the timed region, per step
+            "abi_ms_per_step": {k_: round(v_ / args.steps, 4) for k_, v_ in sorted(counter.ms_by_entry_point().items())},
             "clocks": clocks}
     if world == 1 and not args.no_triton_ref:
         line["reference_gpu"] = time_reference_triton(name, c, host, device)

@@ -165,29 +165,27 @@ int smoe_activation_backward(const void* U, int64_t stride_um, const void* DH, i
                              int32_t act, float alpha, float limit, int32_t dtype, void* stream);
 
 /* ---- expert-parallel row exchange over NVLink peer memory -----------------------------------------------
- * No counterpart in the reference (it has no multi-GPU code). `peer_bufs` is a HOST array of `world` device
- * pointers, entry w = the (capacity_rows, peer_stride_rows) row buffer of rank w mapped into this process (e.g.
- * a symmetric-memory allocation); entry `rank` is the local buffer. The calls only enqueue plain peer loads /
- * stores; ordering against the other ranks (a barrier between phases) is the caller's.
+ * No counterpart in the reference (it has no multi-GPU code). `peer_*` arguments are HOST arrays of `world` device
+ * pointers, entry w = that buffer of rank w mapped into this process (e.g. a symmetric-memory allocation); entry
+ * `my_rank` is the local buffer. The calls only enqueue plain peer stores; ordering against the other ranks (a
+ * barrier between phases) is the caller's. Both directions push.
  *
  * smoe_ep_dispatch: for every position m of this rank's expert-sorted slot list (global expert e, slot s):
- *     peer[e / (E/world)][dst_offsets[e] + (m - first position of e)] = X[s / fan_out, :] * coeff[s]
- *   `dst_offsets[e]` = first row reserved for this rank's rows of expert e in the owner's buffer (the owner's
- *   buffer is then expert-grouped without any further copy). `slot_dest[s]` (nullable out) records
- *   (owner rank << 40 | row) per slot for the way back.
- * smoe_ep_combine:   out[t, :] = sum_j gates[t, j] * peer[rank(t,j)][row(t,j), :]   (gates nullable: plain sum)
- * smoe_ep_gate_grad: d_gates[t, j] = <peer[rank(t,j)][row(t,j), :], grad_out[t, :]> */
+ *     row = dst_offsets[e] + (m - first position of e);  owner = e / (E/world)
+ *     peer_bufs[owner][row, :]      = X[s / fan_out, :] * coeff[s]          (coeff nullable)
+ *     peer_return_addr[owner][row]  = my_rank << 40 | s                      (nullable: not recorded)
+ *   `dst_offsets[e]` = first row reserved for this rank's rows of expert e in the owner's (capacity_rows,
+ *   peer_stride_rows) buffer, chosen so that the owner's buffer ends up expert-grouped with no further copy.
+ * smoe_ep_return: for every row i < min(capacity_rows, *live_rows) of the local (capacity_rows, K) result Y:
+ *     (r, s) = return_addr[i];  peer_slot_bufs[r][s, :] = Y[i, :]           (peer buffers are (peer_rows, stride)) */
 int smoe_ep_dispatch(const void* X, int64_t x_rows, int64_t stride_xm, const int64_t* sorted_expert_idxs,
                      const int64_t* sorted_scattered_idxs, const int64_t* expert_offsets, const int64_t* dst_offsets,
                      const void* coeff, int32_t fan_out, void* const* peer_bufs, int64_t peer_stride_rows,
-                     int64_t capacity_rows, int64_t* slot_dest, int64_t R, int32_t K, int32_t E, int32_t world,
-                     int32_t dtype, void* stream);
-int smoe_ep_combine(void* const* peer_bufs, int64_t peer_stride_rows, const int64_t* slot_dest, const void* gates,
-                    int64_t stride_gt, int64_t stride_gk, void* out, int64_t stride_om, int64_t T, int32_t k, int32_t N,
-                    int32_t world, int32_t dtype, void* stream);
-int smoe_ep_gate_grad(void* const* peer_bufs, int64_t peer_stride_rows, const int64_t* slot_dest, const void* grad_out,
-                      int64_t stride_gom, void* d_gates, int64_t stride_dgt, int64_t stride_dgk, int64_t T, int32_t k,
-                      int32_t N, int32_t world, int32_t dtype, void* stream);
+                     int64_t capacity_rows, void* const* peer_return_addr, int32_t my_rank, int64_t R, int32_t K,
+                     int32_t E, int32_t world, int32_t dtype, void* stream);
+int smoe_ep_return(const void* Y, int64_t stride_ym, const int64_t* return_addr, const int64_t* live_rows,
+                   int64_t capacity_rows, void* const* peer_slot_bufs, int64_t peer_stride_rows, int64_t peer_rows,
+                   int32_t K, int32_t world, int32_t dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -87,9 +87,9 @@ __global__ void __launch_bounds__(256)
 act_forward_kernel(const T* __restrict__ U, int64_t su, T* __restrict__ H, int64_t sh, int64_t rows,
                    const int64_t* __restrict__ rows_dev, int F, int act, float alpha, float limit) {
   const int vec_per_row = F / V;
-  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (rows_dev) rows = min(rows, *rows_dev);     // live row count known only on the device
-  if (gid >= rows * vec_per_row) return;
+  for (int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; gid < rows * vec_per_row;
+       gid += static_cast<int64_t>(gridDim.x) * blockDim.x) {
   const int64_t r = gid / vec_per_row;
   const int j = static_cast<int>(gid - r * vec_per_row) * V;
   const T* u = U + r * su;
@@ -119,6 +119,7 @@ act_forward_kernel(const T* __restrict__ U, int64_t su, T* __restrict__ H, int64
     for (int i = 0; i < V; ++i) out[i] = act_fwd(act, gate[i]) * lin[i];
   }
   store_vec<T, V>(H + r * sh + j, out);
+  }
 }
 
 template <typename T, int LAYOUT, int V>
@@ -127,9 +128,9 @@ act_backward_kernel(const T* __restrict__ U, int64_t su, const T* __restrict__ D
                     int64_t sdu, int64_t rows, const int64_t* __restrict__ rows_dev, int F, int act, float alpha,
                     float limit) {
   const int vec_per_row = F / V;
-  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (rows_dev) rows = min(rows, *rows_dev);
-  if (gid >= rows * vec_per_row) return;
+  for (int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; gid < rows * vec_per_row;
+       gid += static_cast<int64_t>(gridDim.x) * blockDim.x) {
   const int64_t r = gid / vec_per_row;
   const int j = static_cast<int>(gid - r * vec_per_row) * V;
   const T* u = U + r * su;
@@ -176,6 +177,7 @@ act_backward_kernel(const T* __restrict__ U, int64_t su, const T* __restrict__ D
     store_vec<T, V>(du + lin_off, dl);
     store_vec<T, V>(du + gate_off, dg);
   }
+  }
 }
 
 static inline bool aligned16p(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -188,7 +190,9 @@ static int act_launch(bool backward, const void* U, int64_t su, const void* DH, 
   bool vec = F % VV == 0 && su % VV == 0 && so % VV == 0 && aligned16p(U) && aligned16p(OUT);
   if (backward) vec = vec && sdh % VV == 0 && aligned16p(DH);
   const int64_t work = rows * (vec ? F / VV : F);
-  const unsigned grid = static_cast<unsigned>(cdiv64(work, 256));
+  // with a device-side row count the host `rows` is only an upper bound: cap the grid, the kernels grid-stride
+  const int64_t blocks = cdiv64(work, 256);
+  const unsigned grid = static_cast<unsigned>(rows_dev && blocks > 148 * 32 ? 148 * 32 : blocks);
   if (grid == 0) return SMOE_OK;
   if (vec) {
     if (backward)

@@ -201,14 +201,13 @@ class ExpertParallelGLUMLP(nn.Module):
 # ------------------------------------------------------------------------------------------------------------
 
 class PeerRowBuffers:
-    """Symmetric (peer-mapped) row buffers of one expert-parallel layer: `x` (dispatched tokens), `y` (expert
-    outputs), `g` (dispatched output gradients), `dx` (input gradients of the dispatched rows). Every rank can
-    address every rank's copy with plain loads and stores over NVLink. Capacity is the worst case (all rows of
-    all ranks routed to one rank) unless told otherwise, so no routing outcome can overflow a buffer."""
+    """Symmetric (peer-mapped) buffers of one expert-parallel layer. At the expert owner: `x` (dispatched tokens),
+    `g` (dispatched output gradients), both (capacity, width) and expert-grouped, and `ret` (capacity,) int64
+    return addresses. At the token owner: `yslot`, `dxslot` (tokens*k, width), one row per (token, slot). Every
+    rank can address every rank's copy with plain stores over NVLink. Capacity is the worst case (all rows of all
+    ranks routed to one rank) unless told otherwise, so no routing outcome can overflow a buffer."""
 
-    NAMES = ("x", "y", "g", "dx")
-
-    def __init__(self, capacity_rows: int, width: int, dtype, device, group=None):
+    def __init__(self, capacity_rows: int, slot_rows: int, width: int, dtype, device, group=None):
         import ctypes
         import os
         # plain peer mappings only: this code never uses NVLink multicast
@@ -217,10 +216,13 @@ class PeerRowBuffers:
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
-        self.capacity, self.width = int(capacity_rows), int(width)
+        self.capacity, self.slot_rows, self.width = int(capacity_rows), int(slot_rows), int(width)
         self.local, self.ptrs = {}, {}
-        for name in self.NAMES:
-            t = symm.empty((self.capacity, self.width), dtype=dtype, device=device)
+        shapes = {"x": ((self.capacity, self.width), dtype), "g": ((self.capacity, self.width), dtype),
+                  "ret": ((self.capacity,), torch.int64),
+                  "yslot": ((self.slot_rows, self.width), dtype), "dxslot": ((self.slot_rows, self.width), dtype)}
+        for name, (shape, dt) in shapes.items():
+            t = symm.empty(shape, dtype=dt, device=device)
             hdl = symm.rendezvous(t, self.group)
             self.local[name] = t
             self.ptrs[name] = (ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs])
@@ -239,7 +241,10 @@ def _ep_call(name, *args):
 
 
 class _PeerExchangeMLP(torch.autograd.Function):
-    """dispatch -> local expert GLU-MLP -> combine, forward and backward, on peer row buffers."""
+    """dispatch -> local expert GLU-MLP -> return, forward and backward, on peer row buffers.
+
+    Buffer reuse is safe because of where the four barriers of a step sit: a rank can only start writing a peer's
+    buffer for the next phase after every rank has passed the barrier that ends the phase that reads it."""
 
     @staticmethod
     def forward(ctx, x, gates, expert_idxs, w_up, w_down, layer):
@@ -265,35 +270,33 @@ class _PeerExchangeMLP(torch.autograd.Function):
         ebase = (tot.cumsum(1) - tot).flatten()
         dst_off = (ebase + (counts_all.cumsum(0) - counts_all)[rank]).contiguous()
         local_offsets = tot[rank].cumsum(0).contiguous()
-        rows_dev = local_offsets[-1:].contiguous()
-        slot_dest = torch.empty(R, dtype=torch.int64, device=dev)
+        rows_dev = local_offsets[-1:]
         # 3. dispatch: rows go straight to their final, expert-grouped position on the owning rank
         with torch.cuda.device(dev):
             _ep_call("smoe_ep_dispatch", x.data_ptr(), T, x.stride(0), sorted_e.data_ptr(), sorted_idx.data_ptr(),
                      offsets.data_ptr(), dst_off.data_ptr(), 0, k, bufs.ptrs["x"], bufs.width, bufs.capacity,
-                     slot_dest.data_ptr(), R, d, E, W, code, stream)
+                     bufs.ptrs["ret"], rank, R, d, E, W, code, stream)
         bufs.barrier()
         # 4. local experts on the received rows (already grouped: no sort, no copy)
         cap = bufs.capacity
         dummy = layer.dummy_index(cap, dev)
-        xb, yb = bufs.local["x"], bufs.local["y"]
+        xb = bufs.local["x"]
         up = ops.scatter2scatter(xb, w_up.permute(0, 2, 1), dummy, dummy, 1, x_grouped=True, y_grouped=True,
                                  expert_offsets=local_offsets)
         hidden = torch.empty((cap, w_down.size(2)), dtype=x.dtype, device=dev)
         _act._call(False, up, None, hidden, hidden.size(1), _act.LAYOUT_GLU_SECOND, layer.act_code, 1.702, 7.0, rows_dev)
-        ops.scatter2scatter(hidden, w_down.permute(0, 2, 1), dummy, dummy, 1, x_grouped=True, y_grouped=True, out=yb,
-                            expert_offsets=local_offsets)
-        bufs.barrier()
-        # 5. combine: pull my tokens' k rows from the owners and reduce with the gates
-        out = torch.empty((T, d), dtype=x.dtype, device=dev)
+        y_rows = ops.scatter2scatter(hidden, w_down.permute(0, 2, 1), dummy, dummy, 1, x_grouped=True, y_grouped=True,
+                                     expert_offsets=local_offsets)
+        # 5. results go home: one row per (token, slot) into the token owner's slot-ordered buffer
         with torch.cuda.device(dev):
-            _ep_call("smoe_ep_combine", bufs.ptrs["y"], bufs.width, slot_dest.data_ptr(), gates.data_ptr(),
-                     gates.stride(0), gates.stride(1), out.data_ptr(), out.stride(0), T, k, d, W, code, stream)
+            _ep_call("smoe_ep_return", y_rows.data_ptr(), y_rows.stride(0), bufs.local["ret"].data_ptr(),
+                     rows_dev.data_ptr(), cap, bufs.ptrs["yslot"], bufs.width, bufs.slot_rows, d, W, code, stream)
+        bufs.barrier()
+        out = ops.topk_reduce(bufs.local["yslot"], gates, T, k)
         layer.last_rows_dev = rows_dev          # live rows of the local buffers (device scalar), for accounting
         ctx.layer = layer
         ctx.shape = (T, k, d)
-        ctx.save_for_backward(gates, sorted_e, sorted_idx, offsets, dst_off, local_offsets, rows_dev, slot_dest, up,
-                              hidden, w_up, w_down)
+        ctx.save_for_backward(gates, sorted_e, sorted_idx, offsets, dst_off, local_offsets, up, hidden, w_up, w_down)
         return out
 
     @staticmethod
@@ -301,53 +304,53 @@ class _PeerExchangeMLP(torch.autograd.Function):
         from . import _lib
         layer = ctx.layer
         bufs: PeerRowBuffers = layer.buffers
-        (gates, sorted_e, sorted_idx, offsets, dst_off, local_offsets, rows_dev, slot_dest, up, hidden, w_up,
-         w_down) = ctx.saved_tensors
+        gates, sorted_e, sorted_idx, offsets, dst_off, local_offsets, up, hidden, w_up, w_down = ctx.saved_tensors
+        rows_dev = local_offsets[-1:]
         T, k, d = ctx.shape
-        W, E = bufs.world, layer.num_experts
+        W, E, rank = bufs.world, layer.num_experts, bufs.rank
         dev = grad_out.device
         grad_out = grad_out.to(up.dtype).contiguous()
         code = _lib.DTYPE_CODE[up.dtype]
         stream = _lib.stream_ptr(dev)
         cap = bufs.capacity
         dummy = layer.dummy_index(cap, dev)
-        d_gates = torch.empty((T, k), dtype=up.dtype, device=dev)
+        # gate gradient: the per-slot expert outputs are still in the local slot buffer
+        d_gates = ops.gate_grad(bufs.local["yslot"], grad_out, T, k) if ctx.needs_input_grad[1] else None
+        # gate-scaled output gradient dispatched to the same positions the inputs went to
         with torch.cuda.device(dev):
-            # gate gradient from the expert outputs still sitting in the owners' buffers
-            _ep_call("smoe_ep_gate_grad", bufs.ptrs["y"], bufs.width, slot_dest.data_ptr(), grad_out.data_ptr(),
-                     grad_out.stride(0), d_gates.data_ptr(), d_gates.stride(0), d_gates.stride(1), T, k, d, W, code, stream)
-            # gate-scaled output gradient dispatched to the same positions the inputs went to
             _ep_call("smoe_ep_dispatch", grad_out.data_ptr(), T, grad_out.stride(0), sorted_e.data_ptr(),
                      sorted_idx.data_ptr(), offsets.data_ptr(), dst_off.data_ptr(), gates.data_ptr(), k, bufs.ptrs["g"],
-                     bufs.width, bufs.capacity, 0, T * k, d, E, W, code, stream)
+                     bufs.width, bufs.capacity, 0, rank, T * k, d, E, W, code, stream)
         bufs.barrier()
-        xb, gb, dxb = bufs.local["x"], bufs.local["g"], bufs.local["dx"]
+        xb, gb = bufs.local["x"], bufs.local["g"]
         e_local = w_up.size(0)
+        # input-gradient chain first, its rows start travelling home ...
         d_hidden = ops.scatter2scatter(gb, w_down, dummy, dummy, 1, x_grouped=True, y_grouped=True,
                                        expert_offsets=local_offsets)
-        d_w_down, _ = ops.group_bwd_W(gb, hidden, local_offsets, e_local)
         d_up = torch.empty_like(up)
         _act._call(True, up, d_hidden, d_up, hidden.size(1), _act.LAYOUT_GLU_SECOND, layer.act_code, 1.702, 7.0, rows_dev)
-        d_w_up, _ = ops.group_bwd_W(d_up, xb, local_offsets, e_local)
-        ops.scatter2scatter(d_up, w_up, dummy, dummy, 1, x_grouped=True, y_grouped=True, out=dxb,
-                            expert_offsets=local_offsets)
-        bufs.barrier()
-        dx = torch.empty((T, d), dtype=up.dtype, device=dev)
+        dx_rows = ops.scatter2scatter(d_up, w_up, dummy, dummy, 1, x_grouped=True, y_grouped=True,
+                                      expert_offsets=local_offsets)
         with torch.cuda.device(dev):
-            _ep_call("smoe_ep_combine", bufs.ptrs["dx"], bufs.width, slot_dest.data_ptr(), 0, 0, 0, dx.data_ptr(),
-                     dx.stride(0), T, k, d, W, code, stream)
+            _ep_call("smoe_ep_return", dx_rows.data_ptr(), dx_rows.stride(0), bufs.local["ret"].data_ptr(),
+                     rows_dev.data_ptr(), cap, bufs.ptrs["dxslot"], bufs.width, bufs.slot_rows, d, W, code, stream)
+        # ... while the two weight gradients run: the barrier that follows them finds the peers' rows already here
+        d_w_down, _ = ops.group_bwd_W(gb, hidden, local_offsets, e_local)
+        d_w_up, _ = ops.group_bwd_W(d_up, xb, local_offsets, e_local)
+        bufs.barrier()
+        dx = ops.topk_reduce(bufs.local["dxslot"], None, T, k) if k > 1 else bufs.local["dxslot"].clone()
         # weight gradients come back as (E, K, N) views of (E, N, K) buffers = the parameters' own layout
         return dx, d_gates, None, d_w_up.permute(0, 2, 1), d_w_down.permute(0, 2, 1), None
 
 
 class PeerExpertParallelGLUMLP(ExpertParallelGLUMLP):
     """Same layer and parameters as `ExpertParallelGLUMLP`, with the two all-to-all-v exchanges replaced by
-    kernels that write / read the peers' row buffers directly over NVLink (csrc/ep.cu): the dispatched rows land
-    expert-grouped at the owner, the combine pulls and reduces in one pass, and nothing is read back to the host.
+    kernels that write the peers' row buffers directly over NVLink (csrc/ep.cu): the dispatched rows land
+    expert-grouped at the owner, results are pushed back to their slots, and nothing is read back to the host.
     16-bit dtypes, input and hidden sizes that are multiples of 8, SiLU / GELU / ReLU gate activations.
 
     The buffers belong to the layer and are reused by every step: run one forward (+ backward) at a time per
-    layer, with the same number of steps on every rank.
+    layer, with the same number of steps and the same number of local tokens per step on every call.
     """
 
     def __init__(self, input_size, hidden_size, num_experts, top_k, group=None, activation=nn.SiLU(),
@@ -361,6 +364,7 @@ class PeerExpertParallelGLUMLP(ExpertParallelGLUMLP):
         self._capacity_arg, self._global_tokens = capacity_rows, global_tokens
         self.buffers: Optional[PeerRowBuffers] = None
         self._dummy = None
+        self.last_rows_dev = None
 
     def dummy_index(self, n, device):
         """Index tensors are not read when both sides of a grouped GEMM are in expert order; the operator's
@@ -371,13 +375,16 @@ class PeerExpertParallelGLUMLP(ExpertParallelGLUMLP):
 
     def _ensure_buffers(self, x, local_rows):
         if self.buffers is not None:
+            if self.buffers.slot_rows != local_rows:
+                raise AssertionError("this layer's peer buffers were sized for %d local (token, slot) rows, got %d"
+                                     % (self.buffers.slot_rows, local_rows))
             return
         world = dist.get_world_size(self.group)
         cap = self._capacity_arg
         if cap is None:
             cap = (self._global_tokens * self.top_k) if self._global_tokens else local_rows * world
         cap = (int(cap) + 127) // 128 * 128
-        self.buffers = PeerRowBuffers(cap, self.input_size, x.dtype, x.device, self.group)
+        self.buffers = PeerRowBuffers(cap, local_rows, self.input_size, x.dtype, x.device, self.group)
 
     def forward(self, x: torch.Tensor, expert_p: torch.Tensor, expert_idxs: torch.Tensor):
         if x.dtype not in (torch.bfloat16, torch.float16):
