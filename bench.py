@@ -126,7 +126,7 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_layer(name, c, tokens, device, seed, ep_world=1, exchange="nvlink"):
+def build_layer(name, c, tokens, device, seed, ep_world=1, exchange="nvlink", chunks=1):
     """Parameters and inputs of one rank: weights ~N(0, 0.02), X ~N(0, 1), softmax top-k routing."""
     import scattermoe_b200 as sm
     g = torch.Generator().manual_seed(seed)
@@ -149,7 +149,8 @@ def build_layer(name, c, tokens, device, seed, ep_world=1, exchange="nvlink"):
     elif ep_world > 1:
         from scattermoe_b200.expert_parallel import ExpertParallelGLUMLP, PeerExpertParallelGLUMLP
         if exchange == "nvlink":
-            m = PeerExpertParallelGLUMLP(d, F, E, k, global_tokens=tokens * ep_world).to(device=device, dtype=bf)
+            m = PeerExpertParallelGLUMLP(d, F, E, k, global_tokens=tokens * ep_world,
+                                         chunks=chunks).to(device=device, dtype=bf)
         else:
             m = ExpertParallelGLUMLP(d, F, E, k).to(device=device, dtype=bf)
         with torch.no_grad():
@@ -192,7 +193,7 @@ def run_step(c, layer, x, p, idx, dy):
 class LaunchCounter:
     """Counts the kernels this library launches: a proxy in front of the ctypes library that knows how many
     kernels each C entry point enqueues."""
-    KERNELS = {"smoe_ep_dispatch": 1, "smoe_ep_return": 1, "smoe_sort_count": 3, "smoe_sort_count_static": 3, "smoe_offsets_from_sorted": 1,
+    KERNELS = {"smoe_ep_dispatch": 1, "smoe_ep_return": 1, "smoe_ep_barrier": 1, "smoe_sort_count": 3, "smoe_sort_count_static": 3, "smoe_offsets_from_sorted": 1,
                "smoe_scatter2scatter": 1, "smoe_group_bwd_w": 1, "smoe_group": 1, "smoe_topk_reduce": 1,
                "smoe_gate_grad": 1, "smoe_activation_forward": 1, "smoe_activation_backward": 1}
 
@@ -336,6 +337,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--exchange", default="nvlink", choices=["nvlink", "nccl"],
                     help="expert-parallel row exchange for N > 1: peer-memory kernels over NVLink, or NCCL all-to-all-v")
+    ap.add_argument("--chunks", type=int, default=1,
+                    help="pipeline chunks of the NVLink exchange (each chunk's transfers overlap the other's GEMMs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-triton-ref", action="store_true")
     args = ap.parse_args()
@@ -384,7 +387,7 @@ def main():
     import scattermoe_b200 as sm
     peaks = load_peaks()
     layer, host = build_layer(name, c, tokens_local, device, seed=rank, ep_world=world if ep else 1,
-                             exchange=args.exchange)
+                             exchange=args.exchange, chunks=args.chunks)
     dev_in = {n: t.to(device) for n, t in host.items()}
 
     def barrier():
@@ -437,9 +440,9 @@ def main():
     timer.remove()
     ksum = timer.summary()
     mod = layer.get("module")
-    if getattr(mod, "last_rows_dev", None) is not None:
+    if hasattr(mod, "live_row_fraction"):
         # peer-memory expert parallelism launches its GEMMs over worst-case-sized buffers; count the live rows only
-        live = float(mod.last_rows_dev.item()) / mod.buffers.capacity
+        live = mod.live_row_fraction()
         for d_ in ksum.values():
             d_["flops"] *= live
     tensor_core = sm.kernels.ops.last_path_was_tensor_core()

@@ -186,6 +186,13 @@ int smoe_ep_dispatch(const void* X, int64_t x_rows, int64_t stride_xm, const int
 int smoe_ep_return(const void* Y, int64_t stride_ym, const int64_t* return_addr, const int64_t* live_rows,
                    int64_t capacity_rows, void* const* peer_slot_bufs, int64_t peer_stride_rows, int64_t peer_rows,
                    int32_t K, int32_t world, int32_t dtype, void* stream);
+/* Stream-ordered barrier across the ranks through peer memory: `peer_flags[w]` is rank w's int32[world] flag array
+ * (zeroed once, before the first barrier, with the ranks synchronised by other means). Call with epoch = 1, 2, 3,
+ * ... in the same order on every rank. Work enqueued after it on a rank runs after everything every rank
+ * enqueued before its own call with the same epoch, including its peer stores. The wait inside is bounded
+ * (about one second): on expiry `status` gets (2, 100, silent rank, epoch) and the kernel returns. */
+int smoe_ep_barrier(void* const* peer_flags, int32_t my_rank, int32_t world, int32_t epoch, int32_t* status,
+                    void* stream);
 
 #ifdef __cplusplus
 }

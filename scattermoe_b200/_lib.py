@@ -64,6 +64,7 @@ SIGNATURES = {
     "smoe_ep_dispatch": ([_P, _I64, _I64, _P, _P, _P, _P, _P, _I32, _P, _I64, _I64, _P, _I32, _I64, _I32, _I32, _I32, _I32,
                           _P], c_int32),
     "smoe_ep_return": ([_P, _I64, _P, _P, _I64, _P, _I64, _I64, _I32, _I32, _I32, _P], c_int32),
+    "smoe_ep_barrier": ([_P, _I32, _I32, _I32, _P, _P], c_int32),
 }
 
 

@@ -97,6 +97,39 @@ ep_return_kernel(const T* __restrict__ Y, int64_t sym, const int64_t* __restrict
   }
 }
 
+// Barrier across the ranks through peer memory. Every rank owns an int32 slot per peer; rank r announces epoch
+// n by storing n into slot r of every rank's array (release, system scope, after a system fence so that the
+// rows this rank pushed earlier on the stream are visible first) and then waits until all of its own slots have
+// reached n (acquire, system scope). Epochs only grow, so a fast peer that is already one barrier ahead is
+// fine. The wait is bounded: after ~1 s of SM clocks it records (2, 100, peer, epoch) in `status` and returns, so
+// a lost rank can never hang this GPU. One block of 32 threads, thread w talks to rank w.
+constexpr long long EP_BARRIER_LIMIT_CYCLES = 2000000000LL;
+
+__global__ void __launch_bounds__(32)
+ep_barrier_kernel(PeerPtrs flags, int my_rank, int world, int epoch, int32_t* status) {
+  const int w = threadIdx.x;
+  if (w >= world) return;
+  __threadfence_system();
+  int* remote = reinterpret_cast<int*>(flags.p[w]) + my_rank;
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(remote), "r"(epoch) : "memory");
+  const int* mine = reinterpret_cast<const int*>(flags.p[my_rank]) + w;
+  const long long t0 = clock64();
+  while (true) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if (v >= epoch) break;
+    if (clock64() - t0 > EP_BARRIER_LIMIT_CYCLES) {
+      if (status && atomicCAS(status, 0, 2) == 0) {
+        status[1] = 100;
+        status[2] = w;
+        status[3] = epoch;
+      }
+      break;
+    }
+    __nanosleep(64);
+  }
+}
+
 static bool a16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 static int fill_peers(PeerPtrs* pp, void* const* peer_bufs, int world, const char* who, bool* all_aligned) {
@@ -209,4 +242,16 @@ extern "C" int smoe_ep_return(const void* Y, int64_t stride_ym, const int64_t* r
   }
   set_error("ep_return: unknown dtype %d", dtype);
   return SMOE_ERR_BAD_ARG;
+}
+
+extern "C" int smoe_ep_barrier(void* const* peer_flags, int32_t my_rank, int32_t world, int32_t epoch, int32_t* status,
+                               void* stream) {
+  SMOE_CHECK_ARG(peer_flags != nullptr, "ep_barrier: null pointer");
+  SMOE_CHECK_ARG(my_rank >= 0 && my_rank < world && epoch > 0, "ep_barrier: rank %d of %d, epoch %d", my_rank, world, epoch);
+  PeerPtrs pp;
+  bool aligned;
+  if (int rc = fill_peers(&pp, peer_flags, world, "ep_barrier", &aligned)) return rc;
+  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp, my_rank, world, epoch, status);
+  SMOE_LAUNCH_CHECK();
+  return SMOE_OK;
 }

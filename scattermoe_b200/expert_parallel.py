@@ -226,12 +226,29 @@ class PeerRowBuffers:
             hdl = symm.rendezvous(t, self.group)
             self.local[name] = t
             self.ptrs[name] = (ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs])
+        # flag array of the peer-memory barrier: zeroed here, and no rank may signal before every rank has zeroed
+        flags = symm.empty((max(self.world, 8),), dtype=torch.int32, device=device)
+        hdl = symm.rendezvous(flags, self.group)
+        flags.zero_()
+        self.local["flags"] = flags
+        self.ptrs["flags"] = (ctypes.c_void_p * self.world)(*[int(p) for p in hdl.buffer_ptrs])
+        self.epoch = 0
+        self.device = device
         self._token = torch.zeros(1, dtype=torch.int32, device=device)
+        torch.cuda.synchronize(device)
+        dist.all_reduce(self._token, group=self.group)
+        torch.cuda.synchronize(device)
 
     def barrier(self):
-        """Stream-ordered barrier across the ranks: kernels enqueued after it on any rank run after the kernels
-        enqueued before it on every rank. (One tiny NCCL all-reduce; no host synchronisation.)"""
-        dist.all_reduce(self._token, group=self.group)
+        """Stream-ordered barrier across the ranks on the current stream: kernels enqueued after it on any rank run
+        after the kernels (and their peer stores) enqueued before it on every rank. A 32-thread kernel that
+        exchanges an epoch number through peer memory; its wait is bounded and reports through the status word.
+        (An 8-rank NCCL all-reduce used here first cost ~0.3 ms per barrier, four times per step.)"""
+        from . import _lib
+        self.epoch += 1
+        with torch.cuda.device(self.device):
+            _ep_call("smoe_ep_barrier", self.ptrs["flags"], self.rank, self.world, self.epoch,
+                     _lib.status_word(self.device).data_ptr(), _lib.stream_ptr(self.device))
 
 
 def _ep_call(name, *args):
@@ -343,28 +360,16 @@ class _PeerExchangeMLP(torch.autograd.Function):
         return dx, d_gates, None, d_w_up.permute(0, 2, 1), d_w_down.permute(0, 2, 1), None
 
 
-class PeerExpertParallelGLUMLP(ExpertParallelGLUMLP):
-    """Same layer and parameters as `ExpertParallelGLUMLP`, with the two all-to-all-v exchanges replaced by
-    kernels that write the peers' row buffers directly over NVLink (csrc/ep.cu): the dispatched rows land
-    expert-grouped at the owner, results are pushed back to their slots, and nothing is read back to the host.
-    16-bit dtypes, input and hidden sizes that are multiples of 8, SiLU / GELU / ReLU gate activations.
+class _PeerChunk:
+    """State of one pipeline chunk of a peer-memory layer: its own buffers (so chunks never touch each other's
+    rows or flags), its stream, and the bits of layer configuration the autograd function needs."""
 
-    The buffers belong to the layer and are reused by every step: run one forward (+ backward) at a time per
-    layer, with the same number of steps and the same number of local tokens per step on every call.
-    """
-
-    def __init__(self, input_size, hidden_size, num_experts, top_k, group=None, activation=nn.SiLU(),
-                 capacity_rows=None, global_tokens=None):
-        super().__init__(input_size, hidden_size, num_experts, top_k, group=group, activation=activation)
-        self.act_code = _act.resolve_activation(activation)
-        if self.act_code is None:
-            raise AssertionError("PeerExpertParallelGLUMLP needs an activation this library fuses (SiLU, GELU, ReLU)")
-        if input_size % 8 or hidden_size % 8:
-            raise AssertionError("input_size and hidden_size must be multiples of 8")
-        self._capacity_arg, self._global_tokens = capacity_rows, global_tokens
+    def __init__(self, num_experts, act_code):
+        self.num_experts, self.act_code = num_experts, act_code
         self.buffers: Optional[PeerRowBuffers] = None
-        self._dummy = None
+        self.stream = None
         self.last_rows_dev = None
+        self._dummy = None
 
     def dummy_index(self, n, device):
         """Index tensors are not read when both sides of a grouped GEMM are in expert order; the operator's
@@ -373,26 +378,80 @@ class PeerExpertParallelGLUMLP(ExpertParallelGLUMLP):
             self._dummy = torch.zeros(n, dtype=torch.int64, device=device)
         return self._dummy
 
-    def _ensure_buffers(self, x, local_rows):
-        if self.buffers is not None:
-            if self.buffers.slot_rows != local_rows:
-                raise AssertionError("this layer's peer buffers were sized for %d local (token, slot) rows, got %d"
-                                     % (self.buffers.slot_rows, local_rows))
-            return
+
+class PeerExpertParallelGLUMLP(ExpertParallelGLUMLP):
+    """Same layer and parameters as `ExpertParallelGLUMLP`, with the two all-to-all-v exchanges replaced by
+    kernels that write the peers' row buffers directly over NVLink (csrc/ep.cu): the dispatched rows land
+    expert-grouped at the owner, results are pushed back to their slots, and nothing is read back to the host.
+    16-bit dtypes, input and hidden sizes that are multiples of 8, SiLU / GELU / ReLU gate activations.
+
+    `chunks` > 1 splits the local tokens into that many independent pipelines on their own streams and buffers:
+    while one chunk's rows cross NVLink the other chunk's grouped GEMMs run, in forward and (because autograd
+    replays every node on the stream of its forward) in backward. Weight gradients of the chunks are summed by
+    autograd.
+
+    The buffers belong to the layer and are reused by every step: run one forward (+ backward) at a time per
+    layer, with the same number of steps and the same number of local tokens per step on every rank.
+    """
+
+    def __init__(self, input_size, hidden_size, num_experts, top_k, group=None, activation=nn.SiLU(),
+                 capacity_rows=None, global_tokens=None, chunks=1):
+        super().__init__(input_size, hidden_size, num_experts, top_k, group=group, activation=activation)
+        self.act_code = _act.resolve_activation(activation)
+        if self.act_code is None:
+            raise AssertionError("PeerExpertParallelGLUMLP needs an activation this library fuses (SiLU, GELU, ReLU)")
+        if input_size % 8 or hidden_size % 8:
+            raise AssertionError("input_size and hidden_size must be multiples of 8")
+        self._capacity_arg, self._global_tokens = capacity_rows, global_tokens
+        self.chunks = max(1, int(chunks))
+        self._chunk_state = [_PeerChunk(num_experts, self.act_code) for _ in range(self.chunks)]
+
+    def live_row_fraction(self) -> float:
+        """Live rows / capacity of the local receive buffers in the last step (reads device scalars)."""
+        live = sum(float(c.last_rows_dev.item()) for c in self._chunk_state if c.last_rows_dev is not None)
+        cap = sum(c.buffers.capacity for c in self._chunk_state if c.buffers is not None)
+        return live / cap if cap else 1.0
+
+    def _ensure_buffers(self, x, chunk_rows):
         world = dist.get_world_size(self.group)
-        cap = self._capacity_arg
-        if cap is None:
-            cap = (self._global_tokens * self.top_k) if self._global_tokens else local_rows * world
-        cap = (int(cap) + 127) // 128 * 128
-        self.buffers = PeerRowBuffers(cap, local_rows, self.input_size, x.dtype, x.device, self.group)
+        for c in self._chunk_state:
+            if c.buffers is not None:
+                if c.buffers.slot_rows != chunk_rows:
+                    raise AssertionError("this layer's peer buffers were sized for %d local (token, slot) rows per "
+                                         "chunk, got %d" % (c.buffers.slot_rows, chunk_rows))
+                continue
+            cap = self._capacity_arg
+            if cap is None:
+                cap = (self._global_tokens * self.top_k) if self._global_tokens else chunk_rows * self.chunks * world
+            cap = ((int(cap) + self.chunks - 1) // self.chunks + 127) // 128 * 128
+            c.buffers = PeerRowBuffers(cap, chunk_rows, self.input_size, x.dtype, x.device, self.group)
+            c.stream = torch.cuda.Stream(device=x.device) if self.chunks > 1 else None
 
     def forward(self, x: torch.Tensor, expert_p: torch.Tensor, expert_idxs: torch.Tensor):
         if x.dtype not in (torch.bfloat16, torch.float16):
             raise AssertionError("PeerExpertParallelGLUMLP runs in bfloat16 / float16")
         lead = x.shape[:-1]
         tokens = x.reshape(-1, x.shape[-1])
-        idx = expert_idxs.reshape(tokens.size(0), -1)
-        self._ensure_buffers(tokens, idx.numel())
-        y = _PeerExchangeMLP.apply(tokens, expert_p.reshape(tokens.size(0), -1), idx, self.experts.weight,
-                                   self.output_experts.weight, self)
+        T = tokens.size(0)
+        idx = expert_idxs.reshape(T, -1)
+        gates = expert_p.reshape(T, -1)
+        if T % self.chunks:
+            raise AssertionError("the number of local tokens (%d) must be divisible by chunks=%d" % (T, self.chunks))
+        tc = T // self.chunks
+        self._ensure_buffers(tokens, tc * idx.size(1))
+        w_up, w_down = self.experts.weight, self.output_experts.weight
+        if self.chunks == 1:
+            y = _PeerExchangeMLP.apply(tokens, gates, idx, w_up, w_down, self._chunk_state[0])
+            return y.view(*lead, y.size(-1))
+        cur = torch.cuda.current_stream(tokens.device)
+        outs = []
+        for i, c in enumerate(self._chunk_state):
+            c.stream.wait_stream(cur)
+            sl = slice(i * tc, (i + 1) * tc)
+            with torch.cuda.stream(c.stream):
+                outs.append(_PeerExchangeMLP.apply(tokens[sl], gates[sl], idx[sl], w_up, w_down, c))
+        for c, o in zip(self._chunk_state, outs):
+            cur.wait_stream(c.stream)
+            o.record_stream(cur)
+        y = torch.cat(outs, dim=0)
         return y.view(*lead, y.size(-1))

@@ -59,7 +59,7 @@ def test_single_rank_equals_glumlp():
     sm.check_device_status(dev)
 
 
-def _worker(rank, world, port, ret, peer=False):
+def _worker(rank, world, port, ret, peer=False, chunks=1):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
     dev = torch.device("cuda", rank)
@@ -73,8 +73,10 @@ def _worker(rank, world, port, ret, peer=False):
         tl, el = T // world, E // world
         ts, es = slice(rank * tl, (rank + 1) * tl), slice(rank * el, (rank + 1) * el)
         want = _reference_on(dev, x, p, idx, w1, w2, dy)
-        cls = PeerExpertParallelGLUMLP if peer else ExpertParallelGLUMLP
-        m = cls(x.size(1), w2.size(2), E, idx.size(1)).to(dev).bfloat16()
+        if peer:
+            m = PeerExpertParallelGLUMLP(x.size(1), w2.size(2), E, idx.size(1), chunks=chunks).to(dev).bfloat16()
+        else:
+            m = ExpertParallelGLUMLP(x.size(1), w2.size(2), E, idx.size(1)).to(dev).bfloat16()
         with torch.no_grad():
             m.experts.weight.copy_(w1[es])
             m.output_experts.weight.copy_(w2[es])
@@ -96,13 +98,14 @@ def _worker(rank, world, port, ret, peer=False):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("peer", [False, True], ids=["nccl_all_to_all", "nvlink_peer_memory"])
-def test_two_ranks_equal_the_single_gpu_layer(peer):
+@pytest.mark.parametrize("peer,chunks", [(False, 1), (True, 1), (True, 2)],
+                         ids=["nccl_all_to_all", "nvlink_peer_memory", "nvlink_peer_memory_2_chunks"])
+def test_two_ranks_equal_the_single_gpu_layer(peer, chunks):
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         ret = mgr.dict()
-        procs = [ctx.Process(target=_worker, args=(r, 2, port, ret, peer)) for r in range(2)]
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, ret, peer, chunks)) for r in range(2)]
         for q in procs:
             q.start()
         for q in procs:
