@@ -53,6 +53,11 @@ def load_peaks():
     return dict(hbm_gbs=6650.0, tflops_burst=1590.0, tflops_sustained=1400.0, source="fallback")
 
 
+# DRAM bytes per scatter2scatter launch (dram__bytes_read.sum + dram__bytes_write.sum, averaged over the four
+# launches of one step) from the ncu capture summarised in profiles/s2s_tc_kernel_mixtral_8x7b.md.
+NCU_TRAFFIC_PER_LAUNCH = {"mixtral_8x7b": 5.547e9}
+
+
 def layer_flops(c, tokens):
     R = tokens * c["k"]
     n1 = 2 * c["F"]
@@ -276,19 +281,41 @@ class KernelTimer:
 def time_reference_triton(name, c, host, device, iters=5, warmup=3):
     """The reference's own Triton kernels (installed copy under baseline/_ref) on the same layer and GPU."""
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    if c["kind"] == "gpt_oss" or not os.path.isdir(os.path.join(ref_dir, "scattermoe")):
+    if not os.path.isdir(os.path.join(ref_dir, "scattermoe")):
         return None
     sys.path.insert(0, ref_dir)
     try:
         import scattermoe as ref
         bf = torch.bfloat16
-        m = ref.mlp.GLUMLP(c["d"], c["F"], c["E"], c["k"]).to(device=device, dtype=bf)
+        d, F, E, k = c["d"], c["F"], c["E"], c["k"]
         x, p, idx, dy = (host[n].to(device) for n in ("x", "p", "idx", "dy"))
+        if c["kind"] == "gpt_oss":
+            # the call sequence of the reference's patched GptOssExperts.forward (utils/replace_moe.py:22-55)
+            w1 = torch.empty(E, d, 2 * F, dtype=bf, device=device).normal_(0, 0.02).requires_grad_()
+            w2 = torch.empty(E, F, d, dtype=bf, device=device).normal_(0, 0.02).requires_grad_()
+            b1 = torch.empty(E, 2 * F, dtype=bf, device=device).normal_(0, 0.02).requires_grad_()
+            b2 = torch.empty(E, d, dtype=bf, device=device).normal_(0, 0.02).requires_grad_()
+            leaves_w = [w1, w2, b1, b2]
+
+            def fwd(xx, pp):
+                routing = ref.flatten_sort_count(idx.flatten(), num_experts=E)
+                gu = ref.parallel_linear(xx, w1, k, *routing, expert_biases=b1, grouped_in=False, grouped_out=True)
+                gate, up = gu[..., ::2], gu[..., 1::2]
+                gate = gate.clamp(min=None, max=7.0)
+                up = up.clamp(min=-7.0, max=7.0)
+                h = (up + 1) * (gate * torch.sigmoid(gate * 1.702))
+                return ref.parallel_linear(h, w2, 1, *routing, expert_biases=b2, grouped_in=True, grouped_out=False,
+                                           gates=pp)
+        else:
+            m = ref.mlp.GLUMLP(d, F, E, k).to(device=device, dtype=bf)
+            leaves_w = [m.experts.weight, m.output_experts.weight]
+
+            def fwd(xx, pp):
+                return m(xx, pp, idx)
 
         def step():
             xx, pp = x.detach().requires_grad_(), p.detach().requires_grad_()
-            y = m(xx, pp, idx)
-            torch.autograd.grad(y, [xx, pp, m.experts.weight, m.output_experts.weight], dy)
+            torch.autograd.grad(fwd(xx, pp), [xx, pp] + leaves_w, dy)
         for _ in range(warmup):
             step()
         torch.cuda.synchronize()
@@ -299,7 +326,7 @@ def time_reference_triton(name, c, host, device, iters=5, warmup=3):
         z.record()
         torch.cuda.synchronize()
         ms = a.elapsed_time(z) / iters
-        del m
+        del leaves_w
         torch.cuda.empty_cache()
         return {"impl": "reference Triton kernels, same GPU, same inputs", "ms_per_step": ms,
                 "value": x.size(0) / (ms / 1e3), "unit": "tokens/s", "iters": iters}
@@ -399,15 +426,37 @@ def main():
         return run_step(c, layer, dev_in["x"].detach(), dev_in["p"].detach(), dev_in["idx"], dev_in["dy"])
 
     out_host = dict(y=torch.empty_like(host["x"]).pin_memory(), dx=torch.empty_like(host["x"]).pin_memory())
+    copy_stream = torch.cuda.Stream(device=device)
+    staged = {}
+
+    def stage_inputs():
+        """Enqueue the host->device copies of one step's inputs on the copy stream."""
+        with torch.cuda.stream(copy_stream):
+            staged["in"] = {n: host[n].to(device, non_blocking=True) for n in ("x", "p", "idx", "dy")}
+            staged["ready"] = torch.cuda.Event()
+            staged["ready"].record(copy_stream)
 
     def e2e_step():
-        x = host["x"].to(device, non_blocking=True)
-        p = host["p"].to(device, non_blocking=True)
-        idx = host["idx"].to(device, non_blocking=True)
-        dy = host["dy"].to(device, non_blocking=True)
-        y, dx = run_step(c, layer, x, p, idx, dy)
-        out_host["y"].copy_(y, non_blocking=True)
-        out_host["dx"].copy_(dx, non_blocking=True)
+        # Every step copies its own inputs from pinned host memory and its results back. The copies run on a
+        # second stream: this step's inputs were enqueued while the previous step computed, and its results
+        # travel back while the next step computes.
+        if "in" not in staged:
+            stage_inputs()
+        cur = torch.cuda.current_stream(device)
+        cur.wait_event(staged["ready"])
+        ins = staged.pop("in")
+        for t in ins.values():
+            t.record_stream(cur)
+        stage_inputs()                       # next step's inputs, overlapping this step's compute
+        y, dx = run_step(c, layer, ins["x"], ins["p"], ins["idx"], ins["dy"])
+        done = torch.cuda.Event()
+        done.record(cur)
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(done)
+            y.record_stream(copy_stream)
+            dx.record_stream(copy_stream)
+            out_host["y"].copy_(y, non_blocking=True)
+            out_host["dx"].copy_(dx, non_blocking=True)
 
     def timed(fn, steps, timer=None):
         barrier()
@@ -468,7 +517,8 @@ def main():
     roofline = {"bound": "tensor", "kernel": "s2s_tc_kernel (scatter2scatter: 2 forward + 2 input-gradient launches per step)",
                 "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "peak_source": "%s, sustained bf16 (kernel timed inside a long step)" % peaks["source"],
-                "launches": dom["launches"], "avg_launch_ms": dom["ms"] / max(dom["launches"], 1), "traffic": None}
+                "launches": dom["launches"], "avg_launch_ms": dom["ms"] / max(dom["launches"], 1),
+                "traffic": NCU_TRAFFIC_PER_LAUNCH.get(name) if world == 1 else None}
     wg = ksum.get("group_bwd_w")
     if wg and wg["ms"] > 0:
         roofline["group_bwd_w"] = {"achieved": wg["flops"] / (wg["ms"] / 1e3) / 1e12, "launches": wg["launches"],

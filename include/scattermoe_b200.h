@@ -164,6 +164,15 @@ int smoe_activation_backward(const void* U, int64_t stride_um, const void* DH, i
                              int64_t stride_dum, int64_t rows, const int64_t* rows_dev, int32_t F, int32_t layout,
                              int32_t act, float alpha, float limit, int32_t dtype, void* stream);
 
+/* ---- single-token decode ---------------------------------------------------------------------------------
+ * Replaces kernels.single.single2scatter (scattermoe/kernels/single.py:41-59, kernel :5-39): the k expert
+ * matvecs of one token, Y[j, :] = X[j or 0, :] @ W[expert_idxs[j]]; X has 1 or k rows; any strides, any K and N
+ * (the reference needs multiples of 128); fp32 accumulation. */
+int smoe_single2scatter(const void* X, int64_t x_rows, int64_t stride_xm, int64_t stride_xk, const void* W,
+                        int64_t stride_we, int64_t stride_wk, int64_t stride_wn, void* Y, int64_t stride_ym,
+                        int64_t stride_yn, const int64_t* expert_idxs, int32_t k, int32_t K, int32_t N, int32_t E,
+                        int32_t dtype, void* stream);
+
 /* ---- expert-parallel row exchange over NVLink peer memory -----------------------------------------------
  * No counterpart in the reference (it has no multi-GPU code). `peer_*` arguments are HOST arrays of `world` device
  * pointers, entry w = that buffer of rank w mapped into this process (e.g. a symmetric-memory allocation); entry

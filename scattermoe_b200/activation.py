@@ -87,6 +87,7 @@ class FusedActivation(torch.autograd.Function):
         return d_up, None, None, None, None
 
 
+@torch.compiler.disable
 def fused_activation(up: torch.Tensor, layout: int, act: int = ACT_SILU, alpha: float = 1.702,
                      limit: float = 7.0) -> torch.Tensor:
     """(rows, n_up) -> (rows, F); see include/scattermoe_b200.h for the layouts."""

@@ -173,9 +173,12 @@ class ParallelLinear(torch.autograd.Function):
         return (d_input, d_weights, None, None, None, None, d_biases, d_gates, None, None)
 
 
+@torch.compiler.disable
 def parallel_linear(inputs, expert_weights, k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
                     expert_biases=None, gates=None, grouped_in=False, grouped_out=False):
-    """parallel_experts.py:136-146. `expert_weights` is (E, in, out) in any stride order."""
+    """parallel_experts.py:136-146. `expert_weights` is (E, in, out) in any stride order.
+    Under torch.compile this call is a graph break: it runs eagerly between compiled regions (the kernel-level
+    operators in kernels/ops.py are registered custom ops for callers that trace them directly)."""
     return ParallelLinear.apply(inputs, expert_weights, k, sorted_expert_idxs, sorted_scattered_idxs,
                                 expert_offsets, expert_biases, gates, grouped_in, grouped_out)
 

@@ -232,3 +232,24 @@ def test_activation_resolution():
     assert A.resolve_activation(nn.Tanh()) is None and A.resolve_activation(lambda t: t) is None
     from transformers.activations import ACT2FN
     assert A.resolve_activation(ACT2FN["silu"]) == A.ACT_SILU
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("layout", ["n_contig", "k_contig"])
+@pytest.mark.parametrize("K,N,k,x_rows", [(128, 256, 2, 1), (256, 128, 4, 4), (100, 72, 3, 1), (1000, 520, 2, 2)])
+def test_single2scatter(K, N, k, x_rows, layout, dtype):
+    """Decode matvec against the formula of the reference kernel (kernels/single.py:5-39)."""
+    from scattermoe_b200.kernels import single
+    E = 6
+    g = torch.Generator().manual_seed(K + N + k)
+    X = torch.randn(x_rows, K, generator=g).to(dtype)
+    W = (torch.randn(E, K, N, generator=g) * 0.1).to(dtype)
+    idx = torch.randint(0, E, (1, k), generator=g)
+    Wd = W.cuda() if layout == "n_contig" else W.permute(0, 2, 1).contiguous().cuda().permute(0, 2, 1)
+    Y = single.single2scatter(X.cuda(), Wd, idx.cuda())
+    want = torch.stack([X[j if x_rows > 1 else 0].float() @ W[idx[0, j]].float() for j in range(k)])
+    assert Y.shape == (k, N) and Y.dtype == dtype
+    if dtype == torch.bfloat16:
+        torch.testing.assert_close(Y.float().cpu(), want, rtol=2e-2, atol=2e-2)
+    else:
+        torch.testing.assert_close(Y.cpu(), want, rtol=1e-4, atol=1e-4)
