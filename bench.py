@@ -82,8 +82,10 @@ def make_routing(cfg_name, T, E, k, seed):
 
 
 class ClockSampler:
-    """nvidia-smi sampling of SM clock and throttle reasons while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi sampling of SM clock and throttle reasons. The sampler is started before the warm-up (nvidia-smi
+    needs a moment to produce its first line) and only the samples whose timestamp falls inside the timed region
+    are kept."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
@@ -91,35 +93,50 @@ class ClockSampler:
         self.gpu = gpu_index
         self.proc = None
         self.path = None
+        self.t0 = self.t1 = None
 
     def start(self):
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
+
     def stop(self):
         if self.proc is None:
             return None
+        time.sleep(0.12)                       # let the last in-window sample reach the file
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        import datetime
+        sm, mx, reasons, outside = [], [], set(), []
         try:
             for line in open(self.path):
                 f = [x.strip() for x in line.split(",")]
                 if len(f) < 9:
                     continue
                 try:
-                    sm.append(float(f[1])); mx.append(float(f[2]))
+                    ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    clk, cmax = float(f[1]), float(f[2])
                 except ValueError:
                     continue
+                inside = self.t0 is None or (self.t0 - 0.05 <= ts <= (self.t1 or ts) + 0.05)
+                if not inside:
+                    outside.append(clk)
+                    continue
+                sm.append(clk); mx.append(cmax)
                 for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
                     if v.lower().startswith("active"):
                         reasons.add(name)
@@ -127,7 +144,8 @@ class ClockSampler:
         except Exception:
             pass
         if not sm:
-            return None
+            return {"sm_mhz": statistics.median(outside) if outside else None, "sm_max_mhz": None, "reasons": [],
+                    "samples": 0, "note": "timed region shorter than the sampling interval; median of neighbouring samples"}
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
@@ -473,6 +491,9 @@ def main():
             ms = t.item()
         return ms
 
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
     for _ in range(args.warmup):
         resident_step()
     sm.check_device_status(device)
@@ -480,10 +501,11 @@ def main():
     timer.install()
     counter = LaunchCounter()
     counter.install()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
-        sampler.start()
+        sampler.mark_begin()
     ms_total = timed(resident_step, args.steps)
+    if sampler:
+        sampler.mark_end()
     clocks = sampler.stop() if sampler else None
     counter.remove()
     timer.remove()

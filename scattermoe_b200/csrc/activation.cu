@@ -19,11 +19,18 @@ namespace smoe {
 enum { LAYOUT_PLAIN = 0, LAYOUT_GLU_SECOND = 1, LAYOUT_GLU_FIRST = 2, LAYOUT_GPT_OSS = 3 };
 enum { ACT_SILU = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_RELU = 3, ACT_IDENTITY = 4 };
 
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+// FAST (16-bit storage): hardware exp2 / reciprocal approximations, relative error ~1e-6, far below the 2^-9 of
+// the rounding to bf16 that follows; the IEEE expf + division of the exact path made these kernels ALU-bound
+// (2.7 TB/s measured on the backward pass). fp32 storage keeps the exact path.
+template <bool FAST>
+__device__ __forceinline__ float sigmoidf_(float x) {
+  return FAST ? __fdividef(1.0f, 1.0f + __expf(-x)) : 1.0f / (1.0f + expf(-x));
+}
 
+template <bool FAST>
 __device__ __forceinline__ float act_fwd(int act, float x) {
   switch (act) {
-    case ACT_SILU: return x * sigmoidf_(x);
+    case ACT_SILU: return x * sigmoidf_<FAST>(x);
     case ACT_GELU_ERF: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
     case ACT_GELU_TANH: {
       const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
@@ -34,15 +41,16 @@ __device__ __forceinline__ float act_fwd(int act, float x) {
   }
 }
 
+template <bool FAST>
 __device__ __forceinline__ float act_bwd(int act, float x) {   // d act(x) / dx
   switch (act) {
     case ACT_SILU: {
-      const float s = sigmoidf_(x);
+      const float s = sigmoidf_<FAST>(x);
       return s * (1.0f + x * (1.0f - s));
     }
     case ACT_GELU_ERF: {
       const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752f));
-      const float pdf = 0.3989422804014327f * expf(-0.5f * x * x);
+      const float pdf = 0.3989422804014327f * (FAST ? __expf(-0.5f * x * x) : expf(-0.5f * x * x));
       return cdf + x * pdf;
     }
     case ACT_GELU_TANH: {
@@ -86,11 +94,14 @@ template <typename T, int LAYOUT, int V>
 __global__ void __launch_bounds__(256)
 act_forward_kernel(const T* __restrict__ U, int64_t su, T* __restrict__ H, int64_t sh, int64_t rows,
                    const int64_t* __restrict__ rows_dev, int F, int act, float alpha, float limit) {
+  constexpr bool FAST = sizeof(T) == 2;
   const int vec_per_row = F / V;
   if (rows_dev) rows = min(rows, *rows_dev);     // live row count known only on the device
   for (int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; gid < rows * vec_per_row;
        gid += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-  const int64_t r = gid / vec_per_row;
+  // 32-bit division when the index fits (a 64-bit division per thread costs more than the rest of the body)
+  const int64_t r = (gid >> 32) == 0 ? static_cast<int64_t>(static_cast<uint32_t>(gid) / static_cast<uint32_t>(vec_per_row))
+                                     : gid / vec_per_row;
   const int j = static_cast<int>(gid - r * vec_per_row) * V;
   const T* u = U + r * su;
   float out[V];
@@ -98,7 +109,7 @@ act_forward_kernel(const T* __restrict__ U, int64_t su, T* __restrict__ H, int64
     float a[V];
     load_vec<T, V>(u + j, a);
 #pragma unroll
-    for (int i = 0; i < V; ++i) out[i] = act_fwd(act, a[i]);
+    for (int i = 0; i < V; ++i) out[i] = act_fwd<FAST>(act, a[i]);
   } else if (LAYOUT == LAYOUT_GPT_OSS) {
     float a[V], b[V];
     load_vec<T, V>(u + 2 * j, a);
@@ -109,14 +120,14 @@ act_forward_kernel(const T* __restrict__ U, int64_t su, T* __restrict__ H, int64
       const float u0 = (2 * i + 1 < V) ? a[(2 * i + 1) % V] : b[(2 * i + 1) % V];
       const float g = fminf(g0, limit);
       const float uc = fminf(fmaxf(u0, -limit), limit);
-      out[i] = (uc + 1.0f) * (g * sigmoidf_(alpha * g));
+      out[i] = (uc + 1.0f) * (g * sigmoidf_<FAST>(alpha * g));
     }
   } else {
     float lin[V], gate[V];
     load_vec<T, V>(u + (LAYOUT == LAYOUT_GLU_SECOND ? j : F + j), lin);
     load_vec<T, V>(u + (LAYOUT == LAYOUT_GLU_SECOND ? F + j : j), gate);
 #pragma unroll
-    for (int i = 0; i < V; ++i) out[i] = act_fwd(act, gate[i]) * lin[i];
+    for (int i = 0; i < V; ++i) out[i] = act_fwd<FAST>(act, gate[i]) * lin[i];
   }
   store_vec<T, V>(H + r * sh + j, out);
   }
@@ -127,11 +138,14 @@ __global__ void __launch_bounds__(256)
 act_backward_kernel(const T* __restrict__ U, int64_t su, const T* __restrict__ DH, int64_t sdh, T* __restrict__ DU,
                     int64_t sdu, int64_t rows, const int64_t* __restrict__ rows_dev, int F, int act, float alpha,
                     float limit) {
+  constexpr bool FAST = sizeof(T) == 2;
   const int vec_per_row = F / V;
   if (rows_dev) rows = min(rows, *rows_dev);
   for (int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; gid < rows * vec_per_row;
        gid += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-  const int64_t r = gid / vec_per_row;
+  // 32-bit division when the index fits (a 64-bit division per thread costs more than the rest of the body)
+  const int64_t r = (gid >> 32) == 0 ? static_cast<int64_t>(static_cast<uint32_t>(gid) / static_cast<uint32_t>(vec_per_row))
+                                     : gid / vec_per_row;
   const int j = static_cast<int>(gid - r * vec_per_row) * V;
   const T* u = U + r * su;
   T* du = DU + r * sdu;
@@ -141,7 +155,7 @@ act_backward_kernel(const T* __restrict__ U, int64_t su, const T* __restrict__ D
     float a[V], o[V];
     load_vec<T, V>(u + j, a);
 #pragma unroll
-    for (int i = 0; i < V; ++i) o[i] = dh[i] * act_bwd(act, a[i]);
+    for (int i = 0; i < V; ++i) o[i] = dh[i] * act_bwd<FAST>(act, a[i]);
     store_vec<T, V>(du + j, o);
   } else if (LAYOUT == LAYOUT_GPT_OSS) {
     float a[V], b[V], oa[V], ob[V];
@@ -153,7 +167,7 @@ act_backward_kernel(const T* __restrict__ U, int64_t su, const T* __restrict__ D
       const float u0 = (2 * i + 1 < V) ? a[(2 * i + 1) % V] : b[(2 * i + 1) % V];
       const float g = fminf(g0, limit);
       const float uc = fminf(fmaxf(u0, -limit), limit);
-      const float s = sigmoidf_(alpha * g);
+      const float s = sigmoidf_<FAST>(alpha * g);
       const float glu = g * s;
       const float d_u = (u0 >= -limit && u0 <= limit) ? dh[i] * glu : 0.f;
       const float d_glu = dh[i] * (uc + 1.0f);
@@ -171,8 +185,8 @@ act_backward_kernel(const T* __restrict__ U, int64_t su, const T* __restrict__ D
     load_vec<T, V>(u + gate_off, gate);
 #pragma unroll
     for (int i = 0; i < V; ++i) {
-      dl[i] = dh[i] * act_fwd(act, gate[i]);
-      dg[i] = dh[i] * lin[i] * act_bwd(act, gate[i]);
+      dl[i] = dh[i] * act_fwd<FAST>(act, gate[i]);
+      dg[i] = dh[i] * lin[i] * act_bwd<FAST>(act, gate[i]);
     }
     store_vec<T, V>(du + lin_off, dl);
     store_vec<T, V>(du + gate_off, dg);

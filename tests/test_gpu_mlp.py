@@ -261,3 +261,23 @@ def test_bf16_layers_against_fp32_dense_loop(name, T, d, F, E, k, kind, bias):
     if bias:
         cmp("db1", grads[4], want["d_b1"])
         cmp("db2", grads[5], want["d_b2"])
+
+
+def test_module_runs_under_torch_compile():
+    """The reference advertises its layer as usable inside torch.compile (README changelog 0.2.0). Here the
+    expert linears are graph breaks that run eagerly between compiled regions; results must not change."""
+    import scattermoe_b200 as sm
+    torch.manual_seed(0)
+    m = sm.mlp.GLUMLP(256, 128, 8, 2).cuda().bfloat16()
+    x = torch.randn(300, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    p, idx = torch.topk(torch.softmax(torch.randn(300, 8, device="cuda"), -1), 2)
+    p = p.bfloat16().requires_grad_()
+    leaves = [x, p, m.experts.weight, m.output_experts.weight]
+    y0 = m(x, p, idx)
+    g0 = torch.autograd.grad(y0, leaves, torch.ones_like(y0))
+    compiled = torch.compile(m)
+    y1 = compiled(x, p, idx)
+    g1 = torch.autograd.grad(y1, leaves, torch.ones_like(y1))
+    assert torch.equal(y1, y0)
+    for a, b in zip(g1, g0):
+        assert torch.equal(a, b)
