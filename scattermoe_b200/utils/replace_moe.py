@@ -120,3 +120,43 @@ try:
         return layer_output
 except Exception:
     logging.info("Failed to replace GraniteMoeHybridMoE")
+
+
+# Blocks the reference does not patch (its Qwen3 attempt is commented out, replace_moe.py:97-208, written for
+# releases that kept experts in a ModuleList and needed a weight consolidation pass). Current transformers releases
+# store these experts as fused 3-D parameters already -- gate_up_proj (E, 2*I, H) with the activated "gate" half
+# first, down_proj (E, H, I) -- which is exactly what `parallel_linear` consumes, so the patch is the granite one
+# without a router: forward(hidden_states (T, H), top_k_index (T, k), top_k_weights (T, k)) -> (T, H).
+def _fused_glu_experts_forward(cls_name):
+    def forward(self, hidden_states: torch.Tensor, top_k_index: torch.Tensor, top_k_weights: torch.Tensor) -> torch.Tensor:
+        if not hidden_states.is_cuda:
+            return PATCHED[cls_name](self, hidden_states, top_k_index, top_k_weights)
+        shape = hidden_states.shape
+        tokens = hidden_states.reshape(-1, shape[-1])
+        k = top_k_index.shape[-1]
+        routing = flatten_sort_count(top_k_index.reshape(tokens.size(0), k), num_experts=self.num_experts)
+        up = parallel_linear(tokens, self.gate_up_proj.transpose(2, 1), k, *routing, grouped_in=False, grouped_out=True)
+        code = _act.resolve_activation(self.act_fn) if _act.FUSE else None
+        if code is None:
+            gate_half, linear_half = up.chunk(2, dim=-1)
+            hidden = self.act_fn(gate_half) * linear_half
+        else:
+            hidden = _act.fused_activation(up, _act.LAYOUT_GLU_FIRST, code)
+        out = parallel_linear(hidden, self.down_proj.transpose(2, 1), 1, *routing, grouped_in=True, grouped_out=False,
+                              gates=top_k_weights.reshape(tokens.size(0), k).to(tokens.dtype))
+        return out.view(shape)
+    forward.__name__ = "fused_glu_experts_forward_" + cls_name
+    return forward
+
+
+for _module, _cls_name in (("transformers.models.qwen3_moe.modeling_qwen3_moe", "Qwen3MoeExperts"),
+                           ("transformers.models.mixtral.modeling_mixtral", "MixtralExperts")):
+    try:
+        import importlib
+        _cls = getattr(importlib.import_module(_module), _cls_name)
+        _src = inspect.getsource(_cls)
+        if not all(word in _src for word in ("gate_up_proj", "down_proj", "top_k_index", "top_k_weights")):
+            raise ImportError("%s does not keep fused expert tensors in this transformers release" % _cls_name)
+        replace_function(cls=_cls, fun_name='forward')(_fused_glu_experts_forward(_cls_name))
+    except Exception:
+        logging.info("Failed to replace %s", _cls_name)
