@@ -601,17 +601,29 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_consta
                        v ? 16u : 0u);
           }
         }
-        cp_async_commit();
-        if (it >= A_LAG) {
-          cp_async_wait<A_LAG>();
-          fence_proxy_async_smem();
-          mbar_arrive(full_bar((it - A_LAG) % STAGES));
+        if (p.x_by_tma) {
+          // Grouped X: only ragged tail slabs carry copies of these threads. Publishing a slab as soon as its
+          // stage is free (not two slabs later, as the lagged scheme below does) keeps the gather threads off the
+          // MMA's critical path.
+          if (slab_ragged(c, m_beg, m_end)) {
+            cp_async_commit();
+            cp_async_wait<0>();
+            fence_proxy_async_smem();
+          }
+          mbar_arrive(full_bar(s));
+        } else {
+          cp_async_commit();
+          if (it >= A_LAG) {
+            cp_async_wait<A_LAG>();
+            fence_proxy_async_smem();
+            mbar_arrive(full_bar((it - A_LAG) % STAGES));
+          }
         }
       }
     }
     cp_async_wait<0>();
     fence_proxy_async_smem();
-    if (ok) {
+    if (ok && !p.x_by_tma) {
       for (int j = max(0, it - A_LAG); j < it; ++j) mbar_arrive(full_bar(j % STAGES));
     }
   } else {

@@ -65,7 +65,7 @@ def test_hf_patches_are_installed_on_import():
     rm = scattermoe.utils.replace_moe
     from transformers.models.gpt_oss.modeling_gpt_oss import GptOssExperts
     from transformers.models.granitemoehybrid.modeling_granitemoehybrid import GraniteMoeHybridMoE
-    assert set(rm.PATCHED) == {"GptOssExperts", "GraniteMoeHybridMoE"}
+    assert {"GptOssExperts", "GraniteMoeHybridMoE"} <= set(rm.PATCHED)
     assert GptOssExperts.forward is not rm.PATCHED["GptOssExperts"]
     assert GraniteMoeHybridMoE.forward is not rm.PATCHED["GraniteMoeHybridMoE"]
     assert callable(rm.gpt_oss_forward) and callable(rm.granite_moe_forward)
