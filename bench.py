@@ -201,8 +201,9 @@ def run_step(c, layer, x, p, idx, dy):
     if c["kind"] == "gpt_oss":
         from scattermoe_b200.utils.replace_moe import gpt_oss_glu
         routing = sm.flatten_sort_count(idx, c["E"])
-        up = sm.parallel_linear(x, layer["w1"], c["k"], *routing, expert_biases=layer["b1"], grouped_out=True)
-        h = gpt_oss_glu(up, 1.702, 7.0)
+        from scattermoe_b200 import activation as A
+        h = sm.parallel_linear_act(x, layer["w1"], c["k"], *routing, A.LAYOUT_GPT_OSS, A.ACT_SILU,
+                                   expert_biases=layer["b1"], alpha=1.702, limit=7.0)
         y = sm.parallel_linear(h, layer["w2"], 1, *routing, expert_biases=layer["b2"], grouped_in=True, gates=p)
         leaves = [x, p, layer["w1"], layer["w2"], layer["b1"], layer["b2"]]
     else:
@@ -216,7 +217,7 @@ def run_step(c, layer, x, p, idx, dy):
 class LaunchCounter:
     """Counts the kernels this library launches: a proxy in front of the ctypes library that knows how many
     kernels each C entry point enqueues."""
-    KERNELS = {"smoe_ep_dispatch": 1, "smoe_ep_return": 1, "smoe_ep_barrier": 1, "smoe_sort_count": 3, "smoe_sort_count_static": 3, "smoe_offsets_from_sorted": 1,
+    KERNELS = {"smoe_scatter2scatter_act": 1, "smoe_ep_dispatch": 1, "smoe_ep_return": 1, "smoe_ep_barrier": 1, "smoe_sort_count": 3, "smoe_sort_count_static": 3, "smoe_offsets_from_sorted": 1,
                "smoe_scatter2scatter": 1, "smoe_group_bwd_w": 1, "smoe_group": 1, "smoe_topk_reduce": 1,
                "smoe_gate_grad": 1, "smoe_activation_forward": 1, "smoe_activation_backward": 1}
 
@@ -264,8 +265,17 @@ class KernelTimer:
 
     def install(self):
         from scattermoe_b200.kernels import ops
-        self._s2s, self._wg = ops._scatter2scatter_impl, ops._group_bwd_w_impl
+        self._s2s, self._wg, self._s2sa = ops._scatter2scatter_impl, ops._group_bwd_w_impl, ops.scatter2scatter_act
         timer = self
+
+        def s2sa(X, W, se, ss, k, *a, **kw):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            res = timer._s2sa(X, W, se, ss, k, *a, **kw)
+            e1.record()
+            if res is not None:
+                timer.records.append(("scatter2scatter", 2.0 * se.numel() * X.size(1) * W.size(-1), e0, e1))
+            return res
 
         def s2s(output, W, X, k, se, ss, b, xg, yg, off):
             a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -280,11 +290,11 @@ class KernelTimer:
             timer._wg(E, DW, Db, DY, X, off, gi, fan)
             z.record()
             timer.records.append(("group_bwd_w", 2.0 * DY.size(0) * X.size(1) * DY.size(1), a, z))
-        ops._scatter2scatter_impl, ops._group_bwd_w_impl = s2s, wg
+        ops._scatter2scatter_impl, ops._group_bwd_w_impl, ops.scatter2scatter_act = s2s, wg, s2sa
 
     def remove(self):
         from scattermoe_b200.kernels import ops
-        ops._scatter2scatter_impl, ops._group_bwd_w_impl = self._s2s, self._wg
+        ops._scatter2scatter_impl, ops._group_bwd_w_impl, ops.scatter2scatter_act = self._s2s, self._wg, self._s2sa
 
     def summary(self):
         out = {}

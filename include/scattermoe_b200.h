@@ -164,6 +164,20 @@ int smoe_activation_backward(const void* U, int64_t stride_um, const void* DH, i
                              int64_t stride_dum, int64_t rows, const int64_t* rows_dev, int32_t F, int32_t layout,
                              int32_t act, float alpha, float limit, int32_t dtype, void* stream);
 
+/* Up-projection + activation in one kernel: smoe_scatter2scatter with grouped output (y_grouped = 1) whose
+ * epilogue also writes H = activation(Y) (layouts / functions as above; Y nullable when the up-projection itself
+ * is not needed, e.g. inference). Fuses scattermoe/mlp.py:35-41 / :76-87 (the first expert linear and the
+ * activation after it). Tensor-core kernel only: returns SMOE_ERR_UNSUPPORTED when the request does not fit it
+ * (dtype, alignment, N <= 128), and the caller runs the two separate calls instead. */
+int smoe_scatter2scatter_act(const void* X, int64_t x_rows, int64_t stride_xm, int64_t stride_xk,
+                             const void* W, int64_t stride_we, int64_t stride_wk, int64_t stride_wn,
+                             const void* bias, int64_t stride_be, int64_t stride_bn,
+                             void* Y, int64_t stride_ym, int64_t stride_yn, void* H, int64_t stride_hm,
+                             const int64_t* sorted_expert_idxs, const int64_t* sorted_scattered_idxs,
+                             const int64_t* expert_offsets, int64_t R, int32_t K, int32_t N, int32_t E,
+                             int32_t fan_out, int32_t x_grouped, int32_t dtype, int32_t flags, int32_t act_layout,
+                             int32_t act, float alpha, float limit, int32_t* status, void* stream);
+
 /* ---- single-token decode ---------------------------------------------------------------------------------
  * Replaces kernels.single.single2scatter (scattermoe/kernels/single.py:41-59, kernel :5-39): the k expert
  * matvecs of one token, Y[j, :] = X[j or 0, :] @ W[expert_idxs[j]]; X has 1 or k rows; any strides, any K and N

@@ -7,7 +7,7 @@ Same package surface as the reference's scattermoe/__init__.py:1-15; use it as
 Importing the package installs the Hugging Face MoE patches (utils.replace_moe), as importing the reference
 does (scattermoe/__init__.py:5 -> utils/__init__.py:1).
 """
-from .parallel_experts import flatten_sort_count, parallel_linear, ParallelExperts
+from .parallel_experts import flatten_sort_count, parallel_linear, parallel_linear_act, ParallelExperts
 from . import parallel_experts
 from . import kernels
 from . import mlp
@@ -17,6 +17,7 @@ from ._lib import check_device_status, library_path
 __all__ = [
     "flatten_sort_count",
     "parallel_linear",
+    "parallel_linear_act",
     "ParallelExperts",
     "parallel_experts",
     "kernels",

@@ -61,6 +61,9 @@ SIGNATURES = {
     "smoe_activation_forward": ([_P, _I64, _P, _I64, _I64, _P, _I32, _I32, _I32, c_float, c_float, _I32, _P], c_int32),
     "smoe_activation_backward": ([_P, _I64, _P, _I64, _P, _I64, _I64, _P, _I32, _I32, _I32, c_float, c_float, _I32, _P],
                                  c_int32),
+    "smoe_scatter2scatter_act": ([_P, _I64, _I64, _I64, _P, _I64, _I64, _I64, _P, _I64, _I64, _P, _I64, _I64, _P, _I64,
+                                  _P, _P, _P, _I64, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, c_float, c_float,
+                                  _P, _P], c_int32),
     "smoe_single2scatter": ([_P, _I64, _I64, _I64, _P, _I64, _I64, _I64, _P, _I64, _I64, _P, _I32, _I32, _I32, _I32, _I32, _P],
                             c_int32),
     "smoe_ep_dispatch": ([_P, _I64, _I64, _P, _P, _P, _P, _P, _I32, _P, _I64, _I64, _P, _I32, _I64, _I32, _I32, _I32, _I32,

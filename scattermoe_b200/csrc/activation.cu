@@ -12,58 +12,10 @@
 //   GLU_FIRST   n_up = 2F    H[j] = act(U[j]) * U[F+j]                           (granite, replace_moe.py:76-83)
 //   GPT_OSS     n_up = 2F    g = min(U[2j], limit), u = clamp(U[2j+1], +-limit),
 //                            H[j] = (u + 1) * g * sigmoid(alpha * g)             (gpt-oss, replace_moe.py:39-43)
+#include "act_math.cuh"
 #include "smoe_common.cuh"
 
 namespace smoe {
-
-enum { LAYOUT_PLAIN = 0, LAYOUT_GLU_SECOND = 1, LAYOUT_GLU_FIRST = 2, LAYOUT_GPT_OSS = 3 };
-enum { ACT_SILU = 0, ACT_GELU_ERF = 1, ACT_GELU_TANH = 2, ACT_RELU = 3, ACT_IDENTITY = 4 };
-
-// FAST (16-bit storage): hardware exp2 / reciprocal approximations, relative error ~1e-6, far below the 2^-9 of
-// the rounding to bf16 that follows; the IEEE expf + division of the exact path made these kernels ALU-bound
-// (2.7 TB/s measured on the backward pass). fp32 storage keeps the exact path.
-template <bool FAST>
-__device__ __forceinline__ float sigmoidf_(float x) {
-  return FAST ? __fdividef(1.0f, 1.0f + __expf(-x)) : 1.0f / (1.0f + expf(-x));
-}
-
-template <bool FAST>
-__device__ __forceinline__ float act_fwd(int act, float x) {
-  switch (act) {
-    case ACT_SILU: return x * sigmoidf_<FAST>(x);
-    case ACT_GELU_ERF: return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f));
-    case ACT_GELU_TANH: {
-      const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-      return 0.5f * x * (1.0f + tanhf(u));
-    }
-    case ACT_RELU: return x > 0.f ? x : 0.f;
-    default: return x;
-  }
-}
-
-template <bool FAST>
-__device__ __forceinline__ float act_bwd(int act, float x) {   // d act(x) / dx
-  switch (act) {
-    case ACT_SILU: {
-      const float s = sigmoidf_<FAST>(x);
-      return s * (1.0f + x * (1.0f - s));
-    }
-    case ACT_GELU_ERF: {
-      const float cdf = 0.5f * (1.0f + erff(x * 0.70710678118654752f));
-      const float pdf = 0.3989422804014327f * (FAST ? __expf(-0.5f * x * x) : expf(-0.5f * x * x));
-      return cdf + x * pdf;
-    }
-    case ACT_GELU_TANH: {
-      const float x2 = x * x;
-      const float u = 0.7978845608028654f * (x + 0.044715f * x * x2);
-      const float t = tanhf(u);
-      const float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x2);
-      return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
-    }
-    case ACT_RELU: return x > 0.f ? 1.f : 0.f;
-    default: return 1.f;
-  }
-}
 
 template <typename T, int V> struct alignas(sizeof(T) * V) Pack { T v[V]; };
 
@@ -108,8 +60,7 @@ act_forward_kernel(const T* __restrict__ U, int64_t su, T* __restrict__ H, int64
   if (LAYOUT == LAYOUT_PLAIN) {
     float a[V];
     load_vec<T, V>(u + j, a);
-#pragma unroll
-    for (int i = 0; i < V; ++i) out[i] = act_fwd<FAST>(act, a[i]);
+    SMOE_ACT_SWITCH(act, _Pragma("unroll") for (int i = 0; i < V; ++i) out[i] = act_fwd<ACT_, FAST>(a[i]);)
   } else if (LAYOUT == LAYOUT_GPT_OSS) {
     float a[V], b[V];
     load_vec<T, V>(u + 2 * j, a);
@@ -126,8 +77,7 @@ act_forward_kernel(const T* __restrict__ U, int64_t su, T* __restrict__ H, int64
     float lin[V], gate[V];
     load_vec<T, V>(u + (LAYOUT == LAYOUT_GLU_SECOND ? j : F + j), lin);
     load_vec<T, V>(u + (LAYOUT == LAYOUT_GLU_SECOND ? F + j : j), gate);
-#pragma unroll
-    for (int i = 0; i < V; ++i) out[i] = act_fwd<FAST>(act, gate[i]) * lin[i];
+    SMOE_ACT_SWITCH(act, _Pragma("unroll") for (int i = 0; i < V; ++i) out[i] = act_fwd<ACT_, FAST>(gate[i]) * lin[i];)
   }
   store_vec<T, V>(H + r * sh + j, out);
   }
@@ -154,8 +104,7 @@ act_backward_kernel(const T* __restrict__ U, int64_t su, const T* __restrict__ D
   if (LAYOUT == LAYOUT_PLAIN) {
     float a[V], o[V];
     load_vec<T, V>(u + j, a);
-#pragma unroll
-    for (int i = 0; i < V; ++i) o[i] = dh[i] * act_bwd<FAST>(act, a[i]);
+    SMOE_ACT_SWITCH(act, _Pragma("unroll") for (int i = 0; i < V; ++i) o[i] = dh[i] * act_bwd<ACT_, FAST>(a[i]);)
     store_vec<T, V>(du + j, o);
   } else if (LAYOUT == LAYOUT_GPT_OSS) {
     float a[V], b[V], oa[V], ob[V];
@@ -183,11 +132,10 @@ act_backward_kernel(const T* __restrict__ U, int64_t su, const T* __restrict__ D
     float lin[V], gate[V], dl[V], dg[V];
     load_vec<T, V>(u + lin_off, lin);
     load_vec<T, V>(u + gate_off, gate);
-#pragma unroll
-    for (int i = 0; i < V; ++i) {
-      dl[i] = dh[i] * act_fwd<FAST>(act, gate[i]);
-      dg[i] = dh[i] * lin[i] * act_bwd<FAST>(act, gate[i]);
-    }
+    SMOE_ACT_SWITCH(act, _Pragma("unroll") for (int i = 0; i < V; ++i) {
+      dl[i] = dh[i] * act_fwd<ACT_, FAST>(gate[i]);
+      dg[i] = dh[i] * lin[i] * act_bwd<ACT_, FAST>(gate[i]);
+    })
     store_vec<T, V>(du + lin_off, dl);
     store_vec<T, V>(du + gate_off, dg);
   }

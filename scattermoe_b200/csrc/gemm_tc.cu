@@ -21,6 +21,7 @@
 
 #include <mutex>
 
+#include "act_math.cuh"
 #include "ptx.cuh"
 #include "smoe_common.cuh"
 
@@ -54,6 +55,11 @@ struct S2SParams {
   int64_t R;
   int K, N, E, fan_out, x_grouped, y_grouped, is_bf16, bias_vec;
   int a_by_tma;        // X is grouped and TMA-addressable: the row tiles come by TMA, the gather warps stay idle
+  // fused activation epilogue (EPI != 0): H (rows, F) receives the hidden activations, Y (nullable) the
+  // up-projection itself; see act_math.cuh for layouts and functions
+  uint8_t* H; int64_t h_row_bytes;
+  int F, glu_first, act;
+  float alpha, limit;
   uint32_t idesc;
   int32_t* status;
 };
@@ -112,7 +118,52 @@ __device__ __forceinline__ Tile decode_tile(int t, const int32_t* tile_prefix, c
   return tl;
 }
 
-template <int BN, bool B_KMAJOR>
+// EPI: 0 plain linear; 1 H = act(Y); 2 gated halves, H[j] = act(gate) * lin with the halves F columns apart (a tile then
+// holds 128 columns of EACH half: accumulator columns [0,128) and [128,256)); 3 gpt-oss interleaved clamped SwiGLU.
+enum { EPI_NONE = 0, EPI_ACT = 1, EPI_GLU_HALVES = 2, EPI_GPT_OSS = 3 };
+
+__device__ __forceinline__ void add_bias8(const uint8_t* brow, int col, int is_bf16, int bias_vec, float (&v)[8]) {
+  if (!brow) return;
+  if (bias_vec) {
+    const uint4 bv = __ldg(reinterpret_cast<const uint4*>(brow + col * 2));
+    const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float lo, hi;
+      if (is_bf16) {
+        const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&bw[j]);
+        lo = __low2float(h); hi = __high2float(h);
+      } else {
+        const __half2 h = *reinterpret_cast<const __half2*>(&bw[j]);
+        lo = __low2float(h); hi = __high2float(h);
+      }
+      v[2 * j] += lo; v[2 * j + 1] += hi;
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint16_t raw = __ldg(reinterpret_cast<const uint16_t*>(brow + (col + j) * 2));
+      v[j] += is_bf16 ? __bfloat162float(__ushort_as_bfloat16(raw)) : __half2float(__ushort_as_half(raw));
+    }
+  }
+}
+
+__device__ __forceinline__ void store8(uint8_t* dst, const float (&v)[8], int is_bf16) {
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (is_bf16) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+      o[j] = *reinterpret_cast<const uint32_t*>(&h);
+    } else {
+      const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+      o[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  }
+  *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+template <int BN, bool B_KMAJOR, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
               const S2SParams p) {
@@ -135,7 +186,9 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
   int32_t* tile_prefix = seg_start + (MAX_E + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n_tiles = (p.N + BN - 1) / BN;
+  // columns of the output a tile advances by: with gated halves a tile owns TN = BN/2 columns of each half
+  constexpr int TN = (EPI == EPI_GLU_HALVES) ? BN / 2 : BN;
+  const int n_tiles = ((EPI == EPI_GLU_HALVES ? p.F : p.N) + TN - 1) / TN;
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (tid == 0) {
@@ -168,7 +221,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, BN);
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN);
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
@@ -177,7 +230,19 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
           mbar_arrive_expect_tx(full_bar(s), C::B_STAGE_BYTES + (p.a_by_tma ? A_STAGE_BYTES : 0));
           if (p.a_by_tma) tma_load_2d(smem_u32(sA + s * A_STAGE_BYTES), &tmap_x, full_bar(s), kb * BK, tl.m0);
           const uint32_t dst = smem_u32(sB + s * C::B_STAGE_BYTES);
-          if (B_KMAJOR) {
+          if (EPI == EPI_GLU_HALVES) {
+            // weight rows of the two halves: [n0, n0+TN) and [F+n0, F+n0+TN)
+            if (B_KMAJOR) {
+              tma_load_3d(dst, &tmap_w, full_bar(s), kb * BK, tl.n0, tl.e);
+              tma_load_3d(dst + TN * BK * 2, &tmap_w, full_bar(s), kb * BK, p.F + tl.n0, tl.e);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) {
+                const int col = (j < BN / 128) ? tl.n0 + j * 64 : p.F + tl.n0 + (j - BN / 128) * 64;
+                tma_load_3d(dst + j * (64 * BK * 2), &tmap_w, full_bar(s), col, kb * BK, tl.e);
+              }
+            }
+          } else if (B_KMAJOR) {
             tma_load_3d(dst, &tmap_w, full_bar(s), kb * BK, tl.n0, tl.e);
           } else {
 #pragma unroll
@@ -234,7 +299,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, BN);
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN);
       const uint8_t* rowptr[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -278,7 +343,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     int tile_iter = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
-      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, BN);
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN);
       const int buf = tile_iter & 1;
       const uint32_t tph = (tile_iter >> 1) & 1;
       bool valid = r < tl.rows;
@@ -293,57 +358,94 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
       if (!mbar_wait_warp(tfull_bar(buf), tph, abort_flag, p.status, 5)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+      uint8_t* hrow = (EPI != EPI_NONE) ? p.H + out_row * p.h_row_bytes : nullptr;
+      if (EPI == EPI_GLU_HALVES) {
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int n = tl.n0 + c * 32;
-        if (n >= p.N) break;
-        uint32_t acc[32];
-        tmem_ld_32x32b_x32(taddr + c * 32, acc);
-        tmem_ld_wait();
-        if (valid) {
+        for (int c = 0; c < TN / 32; ++c) {
+          const int n = tl.n0 + c * 32;            // column inside one half
+          if (n >= p.F) break;
+          uint32_t acc_a[32], acc_b[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, acc_a);
+          tmem_ld_32x32b_x32(taddr + TN + c * 32, acc_b);
+          tmem_ld_wait();
+          if (valid) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int nn = n + g * 8;
-            if (nn < p.N) {
-              float v[8];
+            for (int g = 0; g < 4; ++g) {
+              const int nn = n + g * 8;
+              if (nn < p.F) {
+                float a[8], b[8], h[8];
 #pragma unroll
-              for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(acc[g * 8 + j]);
-              if (brow) {
-                if (p.bias_vec) {
-                  const uint4 bv = __ldg(reinterpret_cast<const uint4*>(brow + nn * 2));
-                  const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+                for (int jj = 0; jj < 8; ++jj) {
+                  a[jj] = __uint_as_float(acc_a[g * 8 + jj]);
+                  b[jj] = __uint_as_float(acc_b[g * 8 + jj]);
+                }
+                add_bias8(brow, nn, p.is_bf16, p.bias_vec, a);
+                add_bias8(brow, p.F + nn, p.is_bf16, p.bias_vec, b);
+                if (p.Y) {
+                  store8(yrow + nn * 2, a, p.is_bf16);
+                  store8(yrow + (p.F + nn) * 2, b, p.is_bf16);
+                }
+                SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj)
+                  h[jj] = p.glu_first ? act_fwd<ACT_, true>(a[jj]) * b[jj] : act_fwd<ACT_, true>(b[jj]) * a[jj];)
+                store8(hrow + nn * 2, h, p.is_bf16);
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int n = tl.n0 + c * 32;
+          if (n >= p.N) break;
+          uint32_t acc[32];
+          tmem_ld_32x32b_x32(taddr + c * 32, acc);
+          tmem_ld_wait();
+          if (valid) {
+            if (EPI == EPI_GPT_OSS) {
 #pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    float lo, hi;
-                    if (p.is_bf16) {
-                      const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&bw[j]);
-                      lo = __low2float(h); hi = __high2float(h);
-                    } else {
-                      const __half2 h = *reinterpret_cast<const __half2*>(&bw[j]);
-                      lo = __low2float(h); hi = __high2float(h);
-                    }
-                    v[2 * j] += lo; v[2 * j + 1] += hi;
+              for (int gg = 0; gg < 2; ++gg) {           // 16 accumulator columns -> 8 hidden columns
+                const int nn = n + gg * 16;
+                if (nn < p.N) {
+                  float v0[8], v1[8], h[8];
+#pragma unroll
+                  for (int jj = 0; jj < 8; ++jj) {
+                    v0[jj] = __uint_as_float(acc[gg * 16 + jj]);
+                    v1[jj] = __uint_as_float(acc[gg * 16 + 8 + jj]);
                   }
-                } else {
+                  add_bias8(brow, nn, p.is_bf16, p.bias_vec, v0);
+                  add_bias8(brow, nn + 8, p.is_bf16, p.bias_vec, v1);
+                  if (p.Y) {
+                    store8(yrow + nn * 2, v0, p.is_bf16);
+                    store8(yrow + (nn + 8) * 2, v1, p.is_bf16);
+                  }
 #pragma unroll
-                  for (int j = 0; j < 8; ++j) {
-                    const uint16_t raw = __ldg(reinterpret_cast<const uint16_t*>(brow + (nn + j) * 2));
-                    v[j] += p.is_bf16 ? __bfloat162float(__ushort_as_bfloat16(raw)) : __half2float(__ushort_as_half(raw));
+                  for (int jj = 0; jj < 8; ++jj) {
+                    const float g0 = (jj < 4) ? v0[2 * jj] : v1[2 * jj - 8];
+                    const float u0 = (jj < 4) ? v0[2 * jj + 1] : v1[2 * jj - 7];
+                    const float gc = fminf(g0, p.limit);
+                    const float uc = fminf(fmaxf(u0, -p.limit), p.limit);
+                    h[jj] = (uc + 1.0f) * (gc * sigmoidf_<true>(p.alpha * gc));
+                  }
+                  store8(hrow + (nn / 2) * 2, h, p.is_bf16);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                const int nn = n + g * 8;
+                if (nn < p.N) {
+                  float v[8];
+#pragma unroll
+                  for (int jj = 0; jj < 8; ++jj) v[jj] = __uint_as_float(acc[g * 8 + jj]);
+                  add_bias8(brow, nn, p.is_bf16, p.bias_vec, v);
+                  if (EPI == EPI_NONE || p.Y) store8(yrow + nn * 2, v, p.is_bf16);
+                  if (EPI == EPI_ACT) {
+                    float h[8];
+                    SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj) h[jj] = act_fwd<ACT_, true>(v[jj]);)
+                    store8(hrow + nn * 2, h, p.is_bf16);
                   }
                 }
               }
-              uint32_t o[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                if (p.is_bf16) {
-                  const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                  o[j] = *reinterpret_cast<const uint32_t*>(&h);
-                } else {
-                  const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-                  o[j] = *reinterpret_cast<const uint32_t*>(&h);
-                }
-              }
-              *reinterpret_cast<uint4*>(yrow + nn * 2) = make_uint4(o[0], o[1], o[2], o[3]);
             }
           }
         }
@@ -767,7 +869,7 @@ static bool encode_map3(CUtensorMap* map, bool bf16, const void* base, uint64_t 
 
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-template <int BN, bool B_KMAJOR>
+template <int BN, bool B_KMAJOR, int EPI = EPI_NONE>
 static int launch_s2s_cfg(const CUtensorMap& map, const CUtensorMap& map_x, const S2SParams& p, int grid,
                           cudaStream_t stream) {
   static std::mutex mu;
@@ -777,12 +879,12 @@ static int launch_s2s_cfg(const CUtensorMap& map, const CUtensorMap& map_x, cons
   {
     std::lock_guard<std::mutex> lock(mu);
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-      SMOE_CUDA(cudaFuncSetAttribute(s2s_tc_kernel<BN, B_KMAJOR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      SMOE_CUDA(cudaFuncSetAttribute(s2s_tc_kernel<BN, B_KMAJOR, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      Cfg<BN>::SMEM_BYTES));
       if (dev >= 0 && dev < 64) configured[dev] = true;
     }
   }
-  s2s_tc_kernel<BN, B_KMAJOR><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(map, map_x, p);
+  s2s_tc_kernel<BN, B_KMAJOR, EPI><<<grid, NUM_THREADS, Cfg<BN>::SMEM_BYTES, stream>>>(map, map_x, p);
   SMOE_LAUNCH_CHECK();
   return SMOE_OK;
 }
@@ -841,12 +943,22 @@ int launch_s2s_tc(const S2SArgs& a) {
   if (di.cc_major != 10) return SMOE_ERR_UNSUPPORTED;
 
   const bool bf16 = a.dtype == SMOE_BF16;
+  // fused activation epilogue: which kernel variant, and what it needs
+  int epi = EPI_NONE, F = 0;
+  if (a.act_layout >= 0) {
+    if (a.N <= 128 || a.H == nullptr || a.shm % 8 || !al16(a.H)) return SMOE_ERR_UNSUPPORTED;
+    if (a.act_layout == LAYOUT_PLAIN) { epi = EPI_ACT; F = a.N; }
+    else if (a.act_layout == LAYOUT_GPT_OSS) { epi = EPI_GPT_OSS; F = a.N / 2; if (a.N % 16) return SMOE_ERR_UNSUPPORTED; }
+    else { epi = EPI_GLU_HALVES; F = a.N / 2; if (a.N % 16) return SMOE_ERR_UNSUPPORTED; }
+    if (a.Y && (a.syn != 1 || a.sym % 8 || !al16(a.Y))) return SMOE_ERR_UNSUPPORTED;
+  }
   const int BN = a.N > 128 ? 256 : 128;
   CUtensorMap map;
   const uint64_t e_stride = (a.E > 1 ? static_cast<uint64_t>(a.swe) : static_cast<uint64_t>(a.K) * a.N) * 2;
   bool ok;
   if (k_major)
-    ok = encode_map3(&map, bf16, a.W, a.K, a.N, a.E, static_cast<uint64_t>(a.swn) * 2, e_stride, BK, BN);
+    ok = encode_map3(&map, bf16, a.W, a.K, a.N, a.E, static_cast<uint64_t>(a.swn) * 2, e_stride, BK,
+                     epi == EPI_GLU_HALVES ? BN / 2 : BN);
   else
     ok = encode_map3(&map, bf16, a.W, a.N, a.K, a.E, static_cast<uint64_t>(a.swk) * 2, e_stride, 64, BK);
   if (!ok) return SMOE_ERR_UNSUPPORTED;
@@ -861,13 +973,28 @@ int launch_s2s_tc(const S2SArgs& a) {
   p.bias_vec = (a.bias && al16(a.bias) && a.sbe % 8 == 0) ? 1 : 0;
   p.idesc = make_idesc_f16(bf16, false, !k_major, BM, BN);
   p.status = a.status;
+  p.H = static_cast<uint8_t*>(a.H); p.h_row_bytes = a.shm * 2;
+  p.F = F; p.glu_first = a.act_layout == LAYOUT_GLU_FIRST ? 1 : 0; p.act = a.act; p.alpha = a.alpha; p.limit = a.limit;
 
   CUtensorMap map_x = map;   // placeholder when the rows are gathered: the kernel then never touches it
   p.a_by_tma = (a.x_grouped && !(a.flags & SMOE_FLAG_GATHER_ROWS) && a.sxm >= a.K &&
                 encode_map2(&map_x, bf16, a.X, a.K, a.x_rows, static_cast<uint64_t>(a.sxm) * 2, 64, BM)) ? 1 : 0;
 
-  const int64_t max_tiles = (cdiv64(a.R, BM) + a.E) * cdiv(a.N, BN);
+  const int tile_cols = epi == EPI_GLU_HALVES ? BN / 2 : BN;
+  const int64_t max_tiles = (cdiv64(a.R, BM) + a.E) * cdiv(epi == EPI_GLU_HALVES ? F : a.N, tile_cols);
   const int grid = static_cast<int>(max_tiles < di.sm_count ? max_tiles : di.sm_count);
+  switch (epi) {
+    case EPI_ACT:
+      return k_major ? launch_s2s_cfg<256, true, EPI_ACT>(map, map_x, p, grid, a.stream)
+                     : launch_s2s_cfg<256, false, EPI_ACT>(map, map_x, p, grid, a.stream);
+    case EPI_GLU_HALVES:
+      return k_major ? launch_s2s_cfg<256, true, EPI_GLU_HALVES>(map, map_x, p, grid, a.stream)
+                     : launch_s2s_cfg<256, false, EPI_GLU_HALVES>(map, map_x, p, grid, a.stream);
+    case EPI_GPT_OSS:
+      return k_major ? launch_s2s_cfg<256, true, EPI_GPT_OSS>(map, map_x, p, grid, a.stream)
+                     : launch_s2s_cfg<256, false, EPI_GPT_OSS>(map, map_x, p, grid, a.stream);
+    default: break;
+  }
   if (BN == 256)
     return k_major ? launch_s2s_cfg<256, true>(map, map_x, p, grid, a.stream)
                    : launch_s2s_cfg<256, false>(map, map_x, p, grid, a.stream);

@@ -71,6 +71,10 @@ struct S2SArgs {
   int64_t R; int K, N, E, fan_out, x_grouped, y_grouped, dtype, flags, epilogue;
   int32_t* status;
   cudaStream_t stream;
+  // fused activation epilogue (tensor-core kernel only): act_layout < 0 = none, else a LAYOUT_* of act_math.cuh
+  void* H = nullptr; int64_t shm = 0;
+  int act_layout = -1, act = 0;
+  float alpha = 0.f, limit = 0.f;
 };
 
 struct WGradArgs {

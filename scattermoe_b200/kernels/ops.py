@@ -128,6 +128,41 @@ def scatter2scatter(X, W, sorted_expert_idxs, sorted_scattered_idxs, k, b=None, 
     return output
 
 
+def scatter2scatter_act(X, W, sorted_expert_idxs, sorted_scattered_idxs, k, act_layout, act, b=None, x_grouped=False,
+                        expert_offsets=None, alpha=1.702, limit=7.0, need_up=True):
+    """Up-projection into expert order with the activation fused into the kernel's epilogue (the first expert
+    linear and the activation of scattermoe/mlp.py:35-41 / :76-87 in one launch). Returns (up, hidden), `up` None
+    when `need_up` is False; returns None when the request does not fit the tensor-core kernel (the caller then
+    uses `scatter2scatter` and the activation kernel). Layout / function codes: scattermoe_b200.activation."""
+    _lib.require_cuda(X, "X")
+    assert sorted_scattered_idxs.size(0) == sorted_expert_idxs.size(0)
+    assert sorted_scattered_idxs.size(0) == X.size(0) * k
+    if FORCE_PATH == "simt" or X.dtype not in (torch.bfloat16, torch.float16) or W.dtype != X.dtype:
+        return None
+    se, ss = _i64(sorted_expert_idxs), _i64(sorted_scattered_idxs)
+    E, N = W.size(0), W.size(-1)
+    R = se.numel()
+    off = _i64(expert_offsets if expert_offsets is not None else offsets_from_sorted(se, E))
+    F = N if act_layout == 0 else N // 2
+    up = torch.empty((R, N), device=X.device, dtype=X.dtype) if need_up else None
+    hidden = torch.empty((R, F), device=X.device, dtype=X.dtype)
+    sb = (b.stride(0), b.stride(1)) if b is not None else (0, 0)
+    with torch.cuda.device(X.device):
+        rc = _lib.load().smoe_scatter2scatter_act(
+            X.data_ptr(), X.size(0), X.stride(0), X.stride(1),
+            W.data_ptr(), W.stride(0), W.stride(1), W.stride(2),
+            _ptr(b), sb[0], sb[1],
+            _ptr(up), up.stride(0) if need_up else 0, 1, hidden.data_ptr(), hidden.stride(0),
+            se.data_ptr(), ss.data_ptr(), off.data_ptr(),
+            R, X.size(1), N, E, k, int(x_grouped), _dtype_code(X), _flags() & ~_lib.FLAG_FORCE_TC,
+            act_layout, act, float(alpha), float(limit),
+            _lib.status_word(X.device).data_ptr(), _lib.stream_ptr(X.device))
+    if rc == _lib.SMOE_ERR_UNSUPPORTED:
+        return None
+    _lib.check(rc, "smoe_scatter2scatter_act")
+    return up, hidden
+
+
 # --------------------------------------------------------------------------------------------------
 # group_bwd_W
 # --------------------------------------------------------------------------------------------------

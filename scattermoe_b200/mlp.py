@@ -9,7 +9,7 @@ import torch
 from torch import nn
 
 from . import activation as _act
-from .parallel_experts import ParallelExperts, flatten_sort_count
+from .parallel_experts import ParallelExperts, flatten_sort_count, parallel_linear_act
 
 
 class _ExpertMLPBase(nn.Module):
@@ -17,6 +17,7 @@ class _ExpertMLPBase(nn.Module):
     to token order with the top-k gate-weighted sum."""
 
     up_factor = 1  # width of the first projection in units of hidden_size
+    act_layout = _act.LAYOUT_PLAIN
 
     def __init__(self, input_size, hidden_size, num_experts, top_k, bias, activation):
         super().__init__()
@@ -38,8 +39,15 @@ class _ExpertMLPBase(nn.Module):
         lead = x.shape[:-1]
         tokens = x.view(-1, x.shape[-1])            # any leading shape, restored on return (mlp.py:30-31, :48)
         routing = flatten_sort_count(expert_idxs, num_experts=self.num_experts)
-        up = self.experts(tokens, self.top_k, *routing, grouped_out=True)
-        hidden = self._activate(up)
+        code = _act.resolve_activation(self.activation) if _act.FUSE else None
+        if code is not None and tokens.is_cuda:
+            # up-projection and activation as one autograd node (activation in the GEMM epilogue when the tensor-core
+            # kernel applies, a separate one-pass kernel otherwise)
+            hidden = parallel_linear_act(tokens, self.experts.weight.permute(0, 2, 1), self.top_k, *routing,
+                                         self.act_layout, code, expert_biases=self.experts.bias)
+        else:
+            up = self.experts(tokens, self.top_k, *routing, grouped_out=True)
+            hidden = self._activate(up)
         y = self.output_experts(hidden, 1, *routing, grouped_in=True, gates=expert_p)
         return y.view(*lead, y.size(-1))
 
@@ -65,6 +73,7 @@ class GLUMLP(_ExpertMLPBase):
     `h, gates = chunk(2)`, `act(gates) * h` (mlp.py:81-87)."""
 
     up_factor = 2
+    act_layout = _act.LAYOUT_GLU_SECOND
 
     def __init__(self, input_size, hidden_size, num_experts, top_k, bias=False, activation=nn.SiLU()):
         super().__init__(input_size, hidden_size, num_experts, top_k, bias, activation)

@@ -173,6 +173,72 @@ class ParallelLinear(torch.autograd.Function):
         return (d_input, d_weights, None, None, None, None, d_biases, d_gates, None, None)
 
 
+class ParallelLinearAct(torch.autograd.Function):
+    """Up-projection into expert order followed by the activation, forward in ONE kernel (the activation runs in
+    the epilogue of the tensor-core grouped GEMM); the reference runs `ParallelLinear` (grouped_out=True) and
+    then PyTorch elementwise ops (scattermoe/mlp.py:35-41, :76-87). Backward: one activation-gradient kernel,
+    then exactly the backward of `ParallelLinear`."""
+
+    @staticmethod
+    def forward(ctx, x, expert_weights, k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, expert_biases,
+                act_layout, act, alpha, limit):
+        from . import activation as _act
+        x = _rowmajor(x)
+        x_src, kk, grouped = x, k, False
+        if GROUP_INPUT_COPY and x.size(1) % 8 == 0 and x.dtype in (torch.bfloat16, torch.float16):
+            x_src, kk, grouped = kernels.ops.group(x, sorted_scattered_idxs, fan_out=k), 1, True
+        res = kernels.ops.scatter2scatter_act(x_src, expert_weights, sorted_expert_idxs, sorted_scattered_idxs, kk,
+                                              act_layout, act, b=expert_biases, x_grouped=grouped,
+                                              expert_offsets=expert_offsets, alpha=alpha, limit=limit)
+        if res is None:     # not a tensor-core case: the two separate kernels
+            up = kernels.ops.scatter2scatter(x_src, expert_weights, sorted_expert_idxs, sorted_scattered_idxs, kk,
+                                             b=expert_biases, x_grouped=grouped, y_grouped=True,
+                                             expert_offsets=expert_offsets)
+            F = up.size(1) if act_layout == _act.LAYOUT_PLAIN else up.size(1) // 2
+            hidden = torch.empty((up.size(0), F), dtype=up.dtype, device=up.device)
+            _act._call(False, up, None, hidden, F, act_layout, act, alpha, limit)
+        else:
+            up, hidden = res
+        ctx.save_for_backward(x, expert_weights, expert_biases, sorted_expert_idxs, sorted_scattered_idxs,
+                              expert_offsets, up, x_src if grouped else None)
+        ctx.cfg = (k, act_layout, act, alpha, limit)
+        return hidden
+
+    @staticmethod
+    def backward(ctx, d_hidden):
+        from . import activation as _act
+        (x, expert_weights, expert_biases, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, up,
+         x_in_expert_order) = ctx.saved_tensors
+        k, act_layout, act, alpha, limit = ctx.cfg
+        d_hidden = _rowmajor(d_hidden)
+        if d_hidden.dtype != up.dtype:
+            d_hidden = d_hidden.to(up.dtype)
+        d_up = torch.empty_like(up)
+        _act._call(True, up, d_hidden, d_up, d_hidden.size(1), act_layout, act, alpha, limit)
+        d_input = d_weights = d_biases = None
+        if ctx.needs_input_grad[1] or (expert_biases is not None and ctx.needs_input_grad[6]):
+            grouped = x_in_expert_order is not None
+            d_weights, d_biases = kernels.ops.group_bwd_W(
+                DY=d_up, X=x_in_expert_order if grouped else x, expert_offsets=expert_offsets,
+                E=expert_weights.size(0), has_bias=expert_biases is not None,
+                x_gather_idx=None if grouped else sorted_scattered_idxs, fan_out=1 if grouped else k)
+        if ctx.needs_input_grad[0]:
+            d_expanded = kernels.ops.scatter2scatter(
+                X=d_up, x_grouped=True, W=expert_weights.permute(0, 2, 1), sorted_expert_idxs=sorted_expert_idxs,
+                sorted_scattered_idxs=sorted_scattered_idxs, k=1, y_grouped=False, expert_offsets=expert_offsets)
+            d_input = d_expanded if k == 1 else kernels.ops.topk_reduce(d_expanded, None, x.size(0), k)
+        return (d_input, d_weights, None, None, None, None, d_biases, None, None, None, None)
+
+
+@torch.compiler.disable
+def parallel_linear_act(inputs, expert_weights, k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
+                        act_layout, act, expert_biases=None, alpha=1.702, limit=7.0):
+    """`parallel_linear(..., grouped_out=True)` followed by the activation, as one autograd node (an addition to the
+    reference's surface; `scattermoe_b200.activation` has the layout / function codes). Input in token order, 16-bit."""
+    return ParallelLinearAct.apply(inputs, expert_weights, k, sorted_expert_idxs, sorted_scattered_idxs,
+                                   expert_offsets, expert_biases, act_layout, act, float(alpha), float(limit))
+
+
 @torch.compiler.disable
 def parallel_linear(inputs, expert_weights, k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
                     expert_biases=None, gates=None, grouped_in=False, grouped_out=False):

@@ -20,7 +20,7 @@ import torch
 from torch.nn import functional as F
 
 from .. import activation as _act
-from ..parallel_experts import flatten_sort_count, parallel_linear
+from ..parallel_experts import flatten_sort_count, parallel_linear, parallel_linear_act
 
 PATCHED = {}      # class name -> original forward
 
@@ -67,9 +67,13 @@ try:
         else:
             selected = routing_weights                                                  # already (T, k)
         routing = flatten_sort_count(router_indices.flatten(), num_experts=self.num_experts)
-        gate_up = parallel_linear(tokens, self.gate_up_proj, k, *routing,
-                                  expert_biases=self.gate_up_proj_bias, grouped_in=False, grouped_out=True)
-        gated = gpt_oss_glu(gate_up, self.alpha, self.limit)
+        if _act.FUSE:
+            gated = parallel_linear_act(tokens, self.gate_up_proj, k, *routing, _act.LAYOUT_GPT_OSS, _act.ACT_SILU,
+                                        expert_biases=self.gate_up_proj_bias, alpha=self.alpha, limit=self.limit)
+        else:
+            gate_up = parallel_linear(tokens, self.gate_up_proj, k, *routing,
+                                      expert_biases=self.gate_up_proj_bias, grouped_in=False, grouped_out=True)
+            gated = gpt_oss_glu(gate_up, self.alpha, self.limit)
         out = parallel_linear(gated, self.down_proj, 1, *routing,
                               expert_biases=self.down_proj_bias, grouped_in=True, grouped_out=False,
                               gates=selected.to(tokens.dtype))
@@ -104,14 +108,15 @@ try:
         probs = probs.to(tokens.dtype)
         routing = flatten_sort_count(selected_experts, num_experts=self.router.num_experts)
         # experts: the FIRST half of the up-projection is the activated one here (replace_moe.py:76-83)
-        up = parallel_linear(tokens, self.input_linear.weight.transpose(2, 1), self.router.top_k, *routing,
-                             grouped_in=False, grouped_out=True)
         code = _act.resolve_activation(self.activation) if _act.FUSE else None
         if code is None:
+            up = parallel_linear(tokens, self.input_linear.weight.transpose(2, 1), self.router.top_k, *routing,
+                                 grouped_in=False, grouped_out=True)
             gate_half, linear_half = up.chunk(2, dim=-1)
             hidden = self.activation(gate_half) * linear_half
         else:
-            hidden = _act.fused_activation(up, _act.LAYOUT_GLU_FIRST, code)
+            hidden = parallel_linear_act(tokens, self.input_linear.weight.transpose(2, 1), self.router.top_k, *routing,
+                                         _act.LAYOUT_GLU_FIRST, code)
         layer_output = parallel_linear(hidden, self.output_linear.weight.transpose(2, 1), 1, *routing,
                                        grouped_in=True, grouped_out=False, gates=probs)
         layer_output = layer_output.view(bsz, length, emb_size)
@@ -135,13 +140,14 @@ def _fused_glu_experts_forward(cls_name):
         tokens = hidden_states.reshape(-1, shape[-1])
         k = top_k_index.shape[-1]
         routing = flatten_sort_count(top_k_index.reshape(tokens.size(0), k), num_experts=self.num_experts)
-        up = parallel_linear(tokens, self.gate_up_proj.transpose(2, 1), k, *routing, grouped_in=False, grouped_out=True)
         code = _act.resolve_activation(self.act_fn) if _act.FUSE else None
         if code is None:
+            up = parallel_linear(tokens, self.gate_up_proj.transpose(2, 1), k, *routing, grouped_in=False, grouped_out=True)
             gate_half, linear_half = up.chunk(2, dim=-1)
             hidden = self.act_fn(gate_half) * linear_half
         else:
-            hidden = _act.fused_activation(up, _act.LAYOUT_GLU_FIRST, code)
+            hidden = parallel_linear_act(tokens, self.gate_up_proj.transpose(2, 1), k, *routing, _act.LAYOUT_GLU_FIRST,
+                                         code)
         out = parallel_linear(hidden, self.down_proj.transpose(2, 1), 1, *routing, grouped_in=True, grouped_out=False,
                               gates=top_k_weights.reshape(tokens.size(0), k).to(tokens.dtype))
         return out.view(shape)

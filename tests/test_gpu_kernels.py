@@ -253,3 +253,58 @@ def test_single2scatter(K, N, k, x_rows, layout, dtype):
         torch.testing.assert_close(Y.float().cpu(), want, rtol=2e-2, atol=2e-2)
     else:
         torch.testing.assert_close(Y.cpu(), want, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("w_layout", ["k_contig", "n_contig"])
+@pytest.mark.parametrize("layout,act,bias", [("plain", "gelu", True), ("glu_second", "silu", False), ("glu_first", "silu", True),
+                                             ("gpt_oss", None, True)])
+@pytest.mark.parametrize("T,E,k,K,F", [(300, 4, 2, 64, 136), (513, 8, 3, 320, 200), (1000, 8, 2, 256, 384)])
+def test_fused_up_projection_and_activation(T, E, k, K, F, layout, act, bias, w_layout):
+    """The activation fused into the epilogue of the tensor-core grouped GEMM (one launch) against the oracle's
+    scatter2scatter followed by the PyTorch formulas; both outputs (up-projection and hidden) are checked."""
+    from scattermoe_b200 import activation as A
+    from scattermoe_b200.kernels import ops
+    dtype = torch.bfloat16
+    N = F if layout == "plain" else 2 * F
+    _, idx, g = _routing(T, E, k, seed=T + K + F, skew=True)
+    se, ss, off = oracle.flatten_sort_count(idx, E)
+    X = torch.randn(T, K, generator=g).to(dtype)
+    if w_layout == "n_contig":
+        W = (torch.randn(E, K, N, generator=g) * 0.1).to(dtype)
+    else:
+        W = (torch.randn(E, N, K, generator=g) * 0.1).to(dtype).permute(0, 2, 1)
+    b = (torch.randn(E, N, generator=g) * 0.5).to(dtype) if bias else None
+    lay = {"plain": A.LAYOUT_PLAIN, "glu_second": A.LAYOUT_GLU_SECOND, "glu_first": A.LAYOUT_GLU_FIRST,
+           "gpt_oss": A.LAYOUT_GPT_OSS}[layout]
+    code = {"gelu": A.ACT_GELU_ERF, "silu": A.ACT_SILU, None: A.ACT_SILU}[act]
+    res = ops.scatter2scatter_act(_dev(X), _dev(W), _dev(se), _dev(ss), k, lay, code, b=_dev(b), expert_offsets=_dev(off))
+    assert res is not None, "this shape must take the fused tensor-core kernel"
+    up, hidden = res
+    want_up = oracle.scatter2scatter(X.float(), W.float(), se, ss, k, b=None if b is None else b.float(), y_grouped=True)
+    fn = {"gelu": torch.nn.functional.gelu, "silu": torch.nn.functional.silu, None: None}[act]
+    if layout == "plain":
+        want_h = fn(want_up)
+    elif layout == "glu_second":
+        want_h = oracle.act_glu_second_half(want_up, fn)
+    elif layout == "glu_first":
+        want_h = oracle.act_glu_first_half(want_up, fn)
+    else:
+        want_h = oracle.act_gpt_oss(want_up)
+    assert_close("up", up, want_up, True)
+    assert_close("hidden", hidden, want_h, True, atol_scale=max(1.0, want_h.abs().max().item() / 4))
+    # without the up-projection output (inference)
+    res2 = ops.scatter2scatter_act(_dev(X), _dev(W), _dev(se), _dev(ss), k, lay, code, b=_dev(b), expert_offsets=_dev(off),
+                                   need_up=False)
+    assert res2[0] is None and torch.equal(res2[1], hidden)
+
+
+def test_fused_up_projection_declines_what_it_cannot_do():
+    from scattermoe_b200 import activation as A
+    from scattermoe_b200.kernels import ops
+    idx = torch.zeros(8, dtype=torch.int64, device="cuda")
+    se, ss = idx, torch.arange(8, device="cuda")
+    X32 = torch.zeros(8, 64, device="cuda")
+    assert ops.scatter2scatter_act(X32, torch.zeros(1, 64, 256, device="cuda"), se, ss, 1, A.LAYOUT_PLAIN, A.ACT_SILU) is None
+    Xb = X32.bfloat16()
+    assert ops.scatter2scatter_act(Xb, torch.zeros(1, 64, 64, device="cuda", dtype=torch.bfloat16), se, ss, 1,
+                                   A.LAYOUT_PLAIN, A.ACT_SILU) is None          # N <= 128
