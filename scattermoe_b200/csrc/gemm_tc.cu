@@ -43,8 +43,11 @@ template <int BN> struct Cfg {
   static constexpr int B_STAGE_BYTES = BN * BK * 2;
   static constexpr int TMEM_COLS = 2 * BN;
   static constexpr int BAR_BYTES = 256;
+  static constexpr int TABLE_BYTES = ((2 * (MAX_E + 1) * 4 + 15) / 16) * 16;
+  static constexpr int STAGE_ROW_BYTES = 80;                       // 64 payload + 16 pad: conflict-free 16-byte accesses
+  static constexpr int EPI_STAGING_BYTES = 4 * 32 * STAGE_ROW_BYTES;   // one 32-row slab per epilogue warp
   static constexpr int SMEM_BYTES =
-      1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + BAR_BYTES + 2 * (MAX_E + 1) * 4;
+      1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + BAR_BYTES + TABLE_BYTES + EPI_STAGING_BYTES;
 };
 
 struct S2SParams {
@@ -163,6 +166,47 @@ __device__ __forceinline__ void store8(uint8_t* dst, const float (&v)[8], int is
   *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+__device__ __forceinline__ uint4 pack8(const float (&v)[8], int is_bf16) {
+  uint32_t o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (is_bf16) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+      o[j] = *reinterpret_cast<const uint32_t*>(&h);
+    } else {
+      const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
+      o[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// Whole-warp call. Lane l holds NCH 16-byte pieces (8 columns each, starting at column `col0`) of ITS output row
+// `rowptr` (row valid or not). The pieces go through a padded shared-memory slab so that every store instruction
+// writes 32/NCH rows x NCH*16 contiguous bytes instead of 32 rows x 16 bytes: 4-8x fewer memory transactions for
+// the scattered / grouped row stores of the epilogue. Columns at or beyond `col_limit` are not written.
+template <int NCH>
+__device__ __forceinline__ void flush_rows(uint8_t* slab, int lane, const uint4 (&mine)[NCH], uint8_t* rowptr, bool valid,
+                                           int col0, int col_limit) {
+  constexpr int ROW = 80;
+#pragma unroll
+  for (int g = 0; g < NCH; ++g) *reinterpret_cast<uint4*>(slab + lane * ROW + g * 16) = mine[g];
+  __syncwarp();
+  const unsigned long long mine_ptr = reinterpret_cast<unsigned long long>(rowptr);
+  constexpr int ROWS_PER_STORE = 32 / NCH;
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    const int row = i * ROWS_PER_STORE + lane / NCH;
+    const int ck = lane % NCH;
+    const uint4 v = *reinterpret_cast<const uint4*>(slab + row * ROW + ck * 16);
+    const unsigned long long ptr = __shfl_sync(0xffffffffu, mine_ptr, row);
+    const int ok = __shfl_sync(0xffffffffu, valid ? 1 : 0, row);
+    const int col = col0 + ck * 8;
+    if (ok && col < col_limit) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(ptr) + col * 2) = v;
+  }
+  __syncwarp();
+}
+
 template <int BN, bool B_KMAJOR, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
@@ -184,6 +228,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   int32_t* seg_start = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(bars) + C::BAR_BYTES);
   int32_t* tile_prefix = seg_start + (MAX_E + 1);
+  uint8_t* epi_staging = reinterpret_cast<uint8_t*>(bars) + C::BAR_BYTES + C::TABLE_BYTES;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // columns of the output a tile advances by: with gated halves a tile owns TN = BN/2 columns of each half
@@ -359,6 +404,10 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
       uint8_t* hrow = (EPI != EPI_NONE) ? p.H + out_row * p.h_row_bytes : nullptr;
+      uint8_t* slab = epi_staging + q * (32 * C::STAGE_ROW_BYTES);
+      const bool write_y = (EPI == EPI_NONE) || p.Y != nullptr;
+      // every lane runs the arithmetic (rows past the segment end hold finite leftovers of other rows' tiles or
+      // zeros and are never stored): the stores below are whole-warp operations
       if (EPI == EPI_GLU_HALVES) {
 #pragma unroll 1
         for (int c = 0; c < TN / 32; ++c) {
@@ -368,29 +417,29 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
           tmem_ld_32x32b_x32(taddr + c * 32, acc_a);
           tmem_ld_32x32b_x32(taddr + TN + c * 32, acc_b);
           tmem_ld_wait();
-          if (valid) {
+          uint4 pa[4], pb[4], ph[4];
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int nn = n + g * 8;
-              if (nn < p.F) {
-                float a[8], b[8], h[8];
+          for (int g = 0; g < 4; ++g) {
+            const int nn = min(n + g * 8, p.F - 8);      // clamped for the bias reads; the flush masks the columns
+            float a[8], b[8], h[8];
 #pragma unroll
-                for (int jj = 0; jj < 8; ++jj) {
-                  a[jj] = __uint_as_float(acc_a[g * 8 + jj]);
-                  b[jj] = __uint_as_float(acc_b[g * 8 + jj]);
-                }
-                add_bias8(brow, nn, p.is_bf16, p.bias_vec, a);
-                add_bias8(brow, p.F + nn, p.is_bf16, p.bias_vec, b);
-                if (p.Y) {
-                  store8(yrow + nn * 2, a, p.is_bf16);
-                  store8(yrow + (p.F + nn) * 2, b, p.is_bf16);
-                }
-                SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj)
-                  h[jj] = p.glu_first ? act_fwd<ACT_, true>(a[jj]) * b[jj] : act_fwd<ACT_, true>(b[jj]) * a[jj];)
-                store8(hrow + nn * 2, h, p.is_bf16);
-              }
+            for (int jj = 0; jj < 8; ++jj) {
+              a[jj] = __uint_as_float(acc_a[g * 8 + jj]);
+              b[jj] = __uint_as_float(acc_b[g * 8 + jj]);
             }
+            add_bias8(brow, nn, p.is_bf16, p.bias_vec, a);
+            add_bias8(brow, p.F + nn, p.is_bf16, p.bias_vec, b);
+            SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj)
+              h[jj] = p.glu_first ? act_fwd<ACT_, true>(a[jj]) * b[jj] : act_fwd<ACT_, true>(b[jj]) * a[jj];)
+            pa[g] = pack8(a, p.is_bf16);
+            pb[g] = pack8(b, p.is_bf16);
+            ph[g] = pack8(h, p.is_bf16);
           }
+          if (write_y) {
+            flush_rows<4>(slab, lane, pa, yrow, valid, n, p.F);
+            flush_rows<4>(slab, lane, pb, yrow + static_cast<int64_t>(p.F) * 2, valid, n, p.F);
+          }
+          flush_rows<4>(slab, lane, ph, hrow, valid, n, p.F);
         }
       } else {
 #pragma unroll 1
@@ -400,53 +449,52 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
           uint32_t acc[32];
           tmem_ld_32x32b_x32(taddr + c * 32, acc);
           tmem_ld_wait();
-          if (valid) {
-            if (EPI == EPI_GPT_OSS) {
+          uint4 py[4];
+          if (EPI == EPI_GPT_OSS) {
+            uint4 ph[2];
 #pragma unroll
-              for (int gg = 0; gg < 2; ++gg) {           // 16 accumulator columns -> 8 hidden columns
-                const int nn = n + gg * 16;
-                if (nn < p.N) {
-                  float v0[8], v1[8], h[8];
+            for (int gg = 0; gg < 2; ++gg) {           // 16 accumulator columns -> 8 hidden columns
+              const int nn = min(n + gg * 16, p.N - 16);
+              float v0[8], v1[8], h[8];
 #pragma unroll
-                  for (int jj = 0; jj < 8; ++jj) {
-                    v0[jj] = __uint_as_float(acc[gg * 16 + jj]);
-                    v1[jj] = __uint_as_float(acc[gg * 16 + 8 + jj]);
-                  }
-                  add_bias8(brow, nn, p.is_bf16, p.bias_vec, v0);
-                  add_bias8(brow, nn + 8, p.is_bf16, p.bias_vec, v1);
-                  if (p.Y) {
-                    store8(yrow + nn * 2, v0, p.is_bf16);
-                    store8(yrow + (nn + 8) * 2, v1, p.is_bf16);
-                  }
-#pragma unroll
-                  for (int jj = 0; jj < 8; ++jj) {
-                    const float g0 = (jj < 4) ? v0[2 * jj] : v1[2 * jj - 8];
-                    const float u0 = (jj < 4) ? v0[2 * jj + 1] : v1[2 * jj - 7];
-                    const float gc = fminf(g0, p.limit);
-                    const float uc = fminf(fmaxf(u0, -p.limit), p.limit);
-                    h[jj] = (uc + 1.0f) * (gc * sigmoidf_<true>(p.alpha * gc));
-                  }
-                  store8(hrow + (nn / 2) * 2, h, p.is_bf16);
-                }
+              for (int jj = 0; jj < 8; ++jj) {
+                v0[jj] = __uint_as_float(acc[gg * 16 + jj]);
+                v1[jj] = __uint_as_float(acc[gg * 16 + 8 + jj]);
               }
-            } else {
+              add_bias8(brow, nn, p.is_bf16, p.bias_vec, v0);
+              add_bias8(brow, nn + 8, p.is_bf16, p.bias_vec, v1);
 #pragma unroll
-              for (int g = 0; g < 4; ++g) {
-                const int nn = n + g * 8;
-                if (nn < p.N) {
-                  float v[8];
+              for (int jj = 0; jj < 8; ++jj) {
+                const float g0 = (jj < 4) ? v0[2 * jj] : v1[2 * jj - 8];
+                const float u0 = (jj < 4) ? v0[2 * jj + 1] : v1[2 * jj - 7];
+                const float gc = fminf(g0, p.limit);
+                const float uc = fminf(fmaxf(u0, -p.limit), p.limit);
+                h[jj] = (uc + 1.0f) * (gc * sigmoidf_<true>(p.alpha * gc));
+              }
+              py[2 * gg] = pack8(v0, p.is_bf16);
+              py[2 * gg + 1] = pack8(v1, p.is_bf16);
+              ph[gg] = pack8(h, p.is_bf16);
+            }
+            if (write_y) flush_rows<4>(slab, lane, py, yrow, valid, n, p.N);
+            flush_rows<2>(slab, lane, ph, hrow, valid, n / 2, p.N / 2);
+          } else {
+            uint4 ph[4];
 #pragma unroll
-                  for (int jj = 0; jj < 8; ++jj) v[jj] = __uint_as_float(acc[g * 8 + jj]);
-                  add_bias8(brow, nn, p.is_bf16, p.bias_vec, v);
-                  if (EPI == EPI_NONE || p.Y) store8(yrow + nn * 2, v, p.is_bf16);
-                  if (EPI == EPI_ACT) {
-                    float h[8];
-                    SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj) h[jj] = act_fwd<ACT_, true>(v[jj]);)
-                    store8(hrow + nn * 2, h, p.is_bf16);
-                  }
-                }
+            for (int g = 0; g < 4; ++g) {
+              const int nn = min(n + g * 8, p.N - 8);
+              float v[8];
+#pragma unroll
+              for (int jj = 0; jj < 8; ++jj) v[jj] = __uint_as_float(acc[g * 8 + jj]);
+              add_bias8(brow, nn, p.is_bf16, p.bias_vec, v);
+              py[g] = pack8(v, p.is_bf16);
+              if (EPI == EPI_ACT) {
+                float h[8];
+                SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj) h[jj] = act_fwd<ACT_, true>(v[jj]);)
+                ph[g] = pack8(h, p.is_bf16);
               }
             }
+            if (write_y) flush_rows<4>(slab, lane, py, yrow, valid, n, p.N);
+            if (EPI == EPI_ACT) flush_rows<4>(slab, lane, ph, hrow, valid, n, p.N);
           }
         }
       }
@@ -505,6 +553,7 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_consta
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
   int32_t* seg_start = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(bars) + C::BAR_BYTES);
+  uint8_t* epi_staging = reinterpret_cast<uint8_t*>(bars) + C::BAR_BYTES + C::TABLE_BYTES;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_tiles = (p.N + BM - 1) / BM;
@@ -732,6 +781,7 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_consta
     // ---------------- epilogue: rows = DY features, columns = X features -----------------------------------
     const int q = warp & 3;
     const int r = q * 32 + lane;
+    uint8_t* slab = epi_staging + q * (32 * C::STAGE_ROW_BYTES);
     int tile_iter = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -759,27 +809,15 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_consta
         uint32_t acc[32];
         tmem_ld_32x32b_x32(taddr + c * 32, acc);
         tmem_ld_wait();
-        if (valid) {
+        uint4 pk[4];
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int kk = kk0 + g * 8;
-            if (kk < p.K) {
-              uint32_t o[4];
+        for (int g = 0; g < 4; ++g) {
+          float v[8];
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float lo = __uint_as_float(acc[g * 8 + 2 * j]), hi = __uint_as_float(acc[g * 8 + 2 * j + 1]);
-                if (p.is_bf16) {
-                  const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-                  o[j] = *reinterpret_cast<const uint32_t*>(&h);
-                } else {
-                  const __half2 h = __floats2half2_rn(lo, hi);
-                  o[j] = *reinterpret_cast<const uint32_t*>(&h);
-                }
-              }
-              *reinterpret_cast<uint4*>(drow + kk * 2) = make_uint4(o[0], o[1], o[2], o[3]);
-            }
-          }
+          for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(acc[g * 8 + j]);
+          pk[g] = pack8(v, p.is_bf16);
         }
+        flush_rows<4>(slab, lane, pk, drow, valid, kk0, p.K);
       }
       tc_fence_before_sync();
       mbar_arrive(tempty_bar(buf));
