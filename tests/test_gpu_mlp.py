@@ -319,3 +319,68 @@ def test_hf_fused_expert_blocks(family):
     got = run(copy.deepcopy(ex).cuda(), "cuda")
     for name, a, b in zip(("y", "dx", "dw", "d_gate_up", "d_down"), got, want):
         assert_close(name, a, b, False)
+
+
+def _glu_reference(x, p, idx, w1, w2, dy):
+    return oracle.moe_mlp_forward_backward(x, p, idx, w1.permute(0, 2, 1), w2.permute(0, 2, 1), None, None,
+                                           oracle.act_glu_second_half, dy, compute_dtype=torch.float32)
+
+
+@pytest.mark.parametrize("case", ["one_expert_takes_all", "fp16", "strided_input", "more_experts_than_the_tc_table"])
+def test_edge_cases_against_the_dense_loop(case):
+    """Ragged extremes and input layouts the reference's masks handle implicitly: every token to one expert (all
+    other segments empty), fp16, an input that is a strided view, and an expert count beyond the tensor-core
+    kernel's segment table (the CUDA-core kernels take over)."""
+    import scattermoe_b200 as sm
+    dtype = torch.float16 if case == "fp16" else torch.bfloat16
+    T, d, F, k = 200, 128, 72, 2
+    E = 1100 if case == "more_experts_than_the_tc_table" else 8
+    g = torch.Generator().manual_seed(len(case))
+    x = torch.randn(T, d, generator=g).to(dtype)
+    if case == "one_expert_takes_all":
+        idx = torch.full((T, k), 5, dtype=torch.int64)
+        idx[:, 1] = 2
+        idx[:, 0] = 5
+        idx[:, 1] = 5        # both slots of every token go to expert 5
+    else:
+        idx = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)])
+    p = torch.rand(T, k, generator=g).to(dtype)
+    w1 = (torch.randn(E, 2 * F, d, generator=g) * 0.05).to(dtype)
+    w2 = (torch.randn(E, d, F, generator=g) * 0.05).to(dtype)
+    dy = torch.randn(T, d, generator=g).to(dtype)
+    want = _glu_reference(x, p, idx, w1, w2, dy)
+    m = sm.mlp.GLUMLP(d, F, E, k).cuda().to(dtype)
+    with torch.no_grad():
+        m.experts.weight.copy_(w1)
+        m.output_experts.weight.copy_(w2)
+    if case == "strided_input":
+        wide = torch.zeros(T, 2 * d, dtype=dtype, device="cuda")
+        wide[:, ::2] = x.cuda()
+        xd = wide[:, ::2].requires_grad_()          # inner stride 2
+    else:
+        xd = x.cuda().requires_grad_()
+    pd = p.cuda().requires_grad_()
+    y = m(xd, pd, idx.cuda())
+    grads = torch.autograd.grad(y, [xd, pd, m.experts.weight, m.output_experts.weight], dy.cuda())
+
+    def cmp(name, got, ref):
+        s = max(1.0, ref.abs().max().item() / 4)
+        assert_close(name, got.float().cpu() / s, ref / s, True)
+    cmp("y", y, want["y"]); cmp("dx", grads[0], want["d_x"]); cmp("dp", grads[1], want["d_expert_p"])
+    cmp("dw1", grads[2], want["d_w1"].permute(0, 2, 1)); cmp("dw2", grads[3], want["d_w2"].permute(0, 2, 1))
+    if case == "one_expert_takes_all":
+        untouched = [e for e in range(E) if e != 5]
+        assert bool((grads[2][untouched] == 0).all()) and bool((grads[3][untouched] == 0).all())
+
+
+def test_no_tokens_at_all():
+    """T = 0: outputs are empty, weight gradients exact zeros, nothing is launched out of bounds."""
+    import scattermoe_b200 as sm
+    m = sm.mlp.GLUMLP(64, 48, 4, 2).cuda().bfloat16()
+    x = torch.zeros(0, 64, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    p = torch.zeros(0, 2, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    idx = torch.zeros(0, 2, device="cuda", dtype=torch.int64)
+    y = m(x, p, idx)
+    assert y.shape == (0, 64)
+    gx, gw = torch.autograd.grad(y, [x, m.experts.weight], torch.zeros_like(y))
+    assert gx.shape == (0, 64) and bool((gw == 0).all())
