@@ -1,8 +1,8 @@
 """Generate the golden vectors under tests/golden/ by running the REFERENCE package.
 
-Run in a container that has the reference checked out (default /root/reference):
+Run where the reference project is checked out; pass its directory with --reference or $SCATTERMOE_REFERENCE:
 
-    TRITON_INTERPRET=1 python tests/golden/make_golden.py [--reference /root/reference]
+    TRITON_INTERPRET=1 python tests/golden/make_golden.py --reference <path to the scattermoe checkout>
 
 The reference's Triton kernels are executed on CPU tensors by the Triton interpreter, so the
 stored outputs are outputs of the reference's own code path (scatter2scatter, group,
@@ -57,7 +57,7 @@ def routing(gen, T, E, k, renorm=True, skew=False):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("SCATTERMOE_REFERENCE"), required="SCATTERMOE_REFERENCE" not in os.environ)
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     import scattermoe
