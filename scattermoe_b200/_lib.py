@@ -126,8 +126,14 @@ def check(rc: int, what: str):
     raise RuntimeError(msg)
 
 
+def on_device(t: torch.Tensor) -> bool:
+    """True for tensors the kernels can take. One predicate for every "is this a GPU tensor" branch of the package,
+    so that host-only tests can trace those branches with stand-in tensors."""
+    return t.is_cuda
+
+
 def require_cuda(t: torch.Tensor, name: str):
-    if not t.is_cuda:
+    if not on_device(t):
         raise RuntimeError(
             "scattermoe_b200: `%s` is on %s; this package runs on CUDA (sm_100a) only and has no CPU path"
             % (name, t.device))

@@ -60,6 +60,34 @@ def _call(backward, up, dh, out, F, layout, act, alpha, limit, rows_dev=None):
     _lib.check(rc, "smoe_activation_backward" if backward else "smoe_activation_forward")
 
 
+@torch.library.custom_op("scattermoe_b200::activation_forward", mutates_args={"hidden"})
+def activation_forward_compileable(up: torch.Tensor, hidden: torch.Tensor, F: int, layout: int, act: int,
+                                   alpha: float, limit: float) -> None:
+    _call(False, up, None, hidden, F, layout, act, alpha, limit)
+
+
+@torch.library.custom_op("scattermoe_b200::activation_backward", mutates_args={"d_up"})
+def activation_backward_compileable(up: torch.Tensor, d_hidden: torch.Tensor, d_up: torch.Tensor, F: int, layout: int,
+                                    act: int, alpha: float, limit: float) -> None:
+    _call(True, up, d_hidden, d_up, F, layout, act, alpha, limit)
+
+
+def activation_forward(up, hidden, F, layout, act, alpha, limit):
+    """hidden <- activation(up); the registered operator while torch.compile traces, the direct call otherwise."""
+    if torch.compiler.is_compiling():
+        activation_forward_compileable(up, hidden, F, layout, act, alpha, limit)
+    else:
+        _call(False, up, None, hidden, F, layout, act, alpha, limit)
+
+
+def activation_backward(up, d_hidden, d_up, F, layout, act, alpha, limit):
+    """d_up <- d_hidden * activation'(up), same dispatch as `activation_forward`."""
+    if torch.compiler.is_compiling():
+        activation_backward_compileable(up, d_hidden, d_up, F, layout, act, alpha, limit)
+    else:
+        _call(True, up, d_hidden, d_up, F, layout, act, alpha, limit)
+
+
 class FusedActivation(torch.autograd.Function):
     @staticmethod
     def forward(ctx, up: torch.Tensor, layout: int, act: int, alpha: float, limit: float):
@@ -71,7 +99,7 @@ class FusedActivation(torch.autograd.Function):
         if layout != LAYOUT_PLAIN and n_up % 2:
             raise AssertionError("gated activation needs an even number of up-projection columns")
         h = torch.empty((up.size(0), F), dtype=up.dtype, device=up.device)
-        _call(False, up, None, h, F, layout, act, alpha, limit)
+        activation_forward(up, h, F, layout, act, alpha, limit)
         ctx.save_for_backward(up)
         ctx.cfg = (F, layout, act, alpha, limit)
         return h
@@ -83,11 +111,10 @@ class FusedActivation(torch.autograd.Function):
         if dh.stride(-1) != 1 or dh.dtype != up.dtype:
             dh = dh.to(up.dtype).contiguous()
         d_up = torch.empty_like(up)
-        _call(True, up, dh, d_up, F, layout, act, alpha, limit)
+        activation_backward(up, dh, d_up, F, layout, act, alpha, limit)
         return d_up, None, None, None, None
 
 
-@torch.compiler.disable
 def fused_activation(up: torch.Tensor, layout: int, act: int = ACT_SILU, alpha: float = 1.702,
                      limit: float = 7.0) -> torch.Tensor:
     """(rows, n_up) -> (rows, F); see include/scattermoe_b200.h for the layouts."""

@@ -128,38 +128,71 @@ def scatter2scatter(X, W, sorted_expert_idxs, sorted_scattered_idxs, k, b=None, 
     return output
 
 
-def scatter2scatter_act(X, W, sorted_expert_idxs, sorted_scattered_idxs, k, act_layout, act, b=None, x_grouped=False,
-                        expert_offsets=None, alpha=1.702, limit=7.0, need_up=True):
-    """Up-projection into expert order with the activation fused into the kernel's epilogue (the first expert
-    linear and the activation of scattermoe/mlp.py:35-41 / :76-87 in one launch). Returns (up, hidden), `up` None
-    when `need_up` is False; returns None when the request does not fit the tensor-core kernel (the caller then
-    uses `scatter2scatter` and the activation kernel). Layout / function codes: scattermoe_b200.activation."""
+def _scatter2scatter_act_impl(up, hidden, W, X, k, sorted_expert_idxs, sorted_scattered_idxs, b, x_grouped,
+                              expert_offsets, act_layout, act, alpha, limit) -> bool:
+    """One launch writing `hidden` (and `up` unless None). False: the request does not fit the tensor-core kernel and
+    nothing was launched."""
     _lib.require_cuda(X, "X")
-    assert sorted_scattered_idxs.size(0) == sorted_expert_idxs.size(0)
-    assert sorted_scattered_idxs.size(0) == X.size(0) * k
     if FORCE_PATH == "simt" or X.dtype not in (torch.bfloat16, torch.float16) or W.dtype != X.dtype:
-        return None
+        return False
     se, ss = _i64(sorted_expert_idxs), _i64(sorted_scattered_idxs)
     E, N = W.size(0), W.size(-1)
-    R = se.numel()
     off = _i64(expert_offsets if expert_offsets is not None else offsets_from_sorted(se, E))
-    F = N if act_layout == 0 else N // 2
-    up = torch.empty((R, N), device=X.device, dtype=X.dtype) if need_up else None
-    hidden = torch.empty((R, F), device=X.device, dtype=X.dtype)
     sb = (b.stride(0), b.stride(1)) if b is not None else (0, 0)
     with torch.cuda.device(X.device):
         rc = _lib.load().smoe_scatter2scatter_act(
             X.data_ptr(), X.size(0), X.stride(0), X.stride(1),
             W.data_ptr(), W.stride(0), W.stride(1), W.stride(2),
             _ptr(b), sb[0], sb[1],
-            _ptr(up), up.stride(0) if need_up else 0, 1, hidden.data_ptr(), hidden.stride(0),
+            _ptr(up), up.stride(0) if up is not None else 0, 1, hidden.data_ptr(), hidden.stride(0),
             se.data_ptr(), ss.data_ptr(), off.data_ptr(),
-            R, X.size(1), N, E, k, int(x_grouped), _dtype_code(X), _flags() & ~_lib.FLAG_FORCE_TC,
+            se.numel(), X.size(1), N, E, k, int(x_grouped), _dtype_code(X), _flags() & ~_lib.FLAG_FORCE_TC,
             act_layout, act, float(alpha), float(limit),
             _lib.status_word(X.device).data_ptr(), _lib.stream_ptr(X.device))
     if rc == _lib.SMOE_ERR_UNSUPPORTED:
-        return None
+        return False
     _lib.check(rc, "smoe_scatter2scatter_act")
+    return True
+
+
+@torch.library.custom_op("scattermoe_b200::scatter2scatter_act", mutates_args={"up", "hidden"})
+def scatter2scatter_act_compileable(up: torch.Tensor, hidden: torch.Tensor, W: torch.Tensor, X: torch.Tensor, k: int,
+                                    sorted_expert_idxs: torch.Tensor, sorted_scattered_idxs: torch.Tensor,
+                                    b: Optional[torch.Tensor], x_grouped: bool,
+                                    expert_offsets: Optional[torch.Tensor], act_layout: int, act: int, alpha: float,
+                                    limit: float) -> None:
+    """Traceable form: always fills both outputs, by the fused kernel when it applies, else by the grouped GEMM
+    followed by the activation kernel (a traced graph cannot branch on what the library answers)."""
+    if not _scatter2scatter_act_impl(up, hidden, W, X, k, sorted_expert_idxs, sorted_scattered_idxs, b, x_grouped,
+                                     expert_offsets, act_layout, act, alpha, limit):
+        from .. import activation as _act
+        _scatter2scatter_impl(up, W, X, k, sorted_expert_idxs, sorted_scattered_idxs, b, x_grouped, True,
+                              expert_offsets)
+        _act._call(False, up, None, hidden, hidden.size(1), act_layout, act, alpha, limit)
+
+
+def scatter2scatter_act(X, W, sorted_expert_idxs, sorted_scattered_idxs, k, act_layout, act, b=None, x_grouped=False,
+                        expert_offsets=None, alpha=1.702, limit=7.0, need_up=True):
+    """Up-projection into expert order with the activation fused into the kernel's epilogue (the first expert
+    linear and the activation of scattermoe/mlp.py:35-41 / :76-87 in one launch). Returns (up, hidden), `up` None
+    when `need_up` is False; returns None when the request does not fit the tensor-core kernel (the caller then
+    uses `scatter2scatter` and the activation kernel; while torch.compile traces, that choice is made inside the
+    registered operator and the result is never None). Layout / function codes: scattermoe_b200.activation."""
+    assert sorted_scattered_idxs.size(0) == sorted_expert_idxs.size(0)
+    assert sorted_scattered_idxs.size(0) == X.size(0) * k
+    R, N = sorted_expert_idxs.size(0), W.size(-1)
+    F = N if act_layout == 0 else N // 2
+    if torch.compiler.is_compiling():
+        up = torch.empty((R, N), device=X.device, dtype=X.dtype)
+        hidden = torch.empty((R, F), device=X.device, dtype=X.dtype)
+        scatter2scatter_act_compileable(up, hidden, W, X, k, sorted_expert_idxs, sorted_scattered_idxs, b, x_grouped,
+                                        expert_offsets, act_layout, act, float(alpha), float(limit))
+        return up, hidden
+    up = torch.empty((R, N), device=X.device, dtype=X.dtype) if need_up else None
+    hidden = torch.empty((R, F), device=X.device, dtype=X.dtype)
+    if not _scatter2scatter_act_impl(up, hidden, W, X, k, sorted_expert_idxs, sorted_scattered_idxs, b, x_grouped,
+                                     expert_offsets, act_layout, act, alpha, limit):
+        return None
     return up, hidden
 
 
@@ -167,8 +200,9 @@ def scatter2scatter_act(X, W, sorted_expert_idxs, sorted_scattered_idxs, k, act_
 # group_bwd_W
 # --------------------------------------------------------------------------------------------------
 
-def _group_bwd_w_impl(E, DW, Db, DY, X, expert_offsets, x_gather_idx, fan_out):
+def _group_bwd_w_impl(E, DWt, Db, DY, X, expert_offsets, x_gather_idx, fan_out):
     _lib.require_cuda(DY, "DY")
+    DW = DWt.permute(0, 2, 1)
     if X.dtype != DY.dtype or DW.dtype != DY.dtype:
         raise RuntimeError("group_bwd_W: DY, X and DW must share one dtype")
     off = _i64(expert_offsets)
@@ -186,11 +220,12 @@ def _group_bwd_w_impl(E, DW, Db, DY, X, expert_offsets, x_gather_idx, fan_out):
     _lib.check(rc, "smoe_group_bwd_w")
 
 
-@torch.library.custom_op("scattermoe_b200::groupXtY", mutates_args={"DW", "Db"})
-def groupXtY_compileable(E: int, DW: torch.Tensor, Db: Optional[torch.Tensor], DY: torch.Tensor, X: torch.Tensor,
+@torch.library.custom_op("scattermoe_b200::groupXtY", mutates_args={"DWt", "Db"})
+def groupXtY_compileable(E: int, DWt: torch.Tensor, Db: Optional[torch.Tensor], DY: torch.Tensor, X: torch.Tensor,
                          expert_offsets: torch.Tensor, x_gather_idx: Optional[torch.Tensor], fan_out: int) -> None:
-    """Traceable form (mirrors scattermoe::groupXtY, ops.py:202; Db is declared as mutated here)."""
-    _group_bwd_w_impl(E, DW, Db, DY, X, expert_offsets, x_gather_idx, fan_out)
+    """Traceable form (mirrors scattermoe::groupXtY, ops.py:202; Db is declared as mutated here). `DWt` is the
+    (E, N, K) buffer whose (E, K, N) view is the gradient: the operator mutates a base tensor, not a view."""
+    _group_bwd_w_impl(E, DWt, Db, DY, X, expert_offsets, x_gather_idx, fan_out)
 
 
 def group_bwd_W(DY, X, expert_offsets, E, has_bias=False, x_gather_idx=None, fan_out=1):
@@ -208,9 +243,9 @@ def group_bwd_W(DY, X, expert_offsets, E, has_bias=False, x_gather_idx=None, fan
     DW = DWt.permute(0, 2, 1)
     Db = torch.empty((E, DY.size(-1)), device=DY.device, dtype=DY.dtype) if has_bias else None
     if torch.compiler.is_compiling():
-        groupXtY_compileable(E, DW, Db, DY, X, expert_offsets, x_gather_idx, fan_out)
+        groupXtY_compileable(E, DWt, Db, DY, X, expert_offsets, x_gather_idx, fan_out)
     else:
-        _group_bwd_w_impl(E, DW, Db, DY, X, expert_offsets, x_gather_idx, fan_out)
+        _group_bwd_w_impl(E, DWt, Db, DY, X, expert_offsets, x_gather_idx, fan_out)
     return DW, Db
 
 
@@ -261,8 +296,7 @@ def group(A, sorted_expert_idxs, coeff=None, fan_out=1, out=None):
 # top-k reductions (torch ops in the reference, parallel_experts.py:44-46, :79, :123)
 # --------------------------------------------------------------------------------------------------
 
-def topk_reduce(expanded: torch.Tensor, gates: Optional[torch.Tensor], T: int, k: int) -> torch.Tensor:
-    """out[t] = sum_j gates[t, j] * expanded[t*k + j]  (gates None: plain sum). `expanded` is (T*k, N)."""
+def _topk_reduce_impl(expanded: torch.Tensor, gates: Optional[torch.Tensor], T: int, k: int) -> torch.Tensor:
     _lib.require_cuda(expanded, "expanded")
     assert expanded.size(0) == T * k
     if expanded.stride(1) != 1:
@@ -282,8 +316,24 @@ def topk_reduce(expanded: torch.Tensor, gates: Optional[torch.Tensor], T: int, k
     return out
 
 
-def gate_grad(expanded: torch.Tensor, grad_out: torch.Tensor, T: int, k: int) -> torch.Tensor:
-    """d_gates[t, j] = <expanded[t*k + j], grad_out[t]>, in the dtype of `expanded`."""
+@torch.library.custom_op("scattermoe_b200::topk_reduce", mutates_args={})
+def topk_reduce_compileable(expanded: torch.Tensor, gates: Optional[torch.Tensor], T: int, k: int) -> torch.Tensor:
+    return _topk_reduce_impl(expanded, gates, T, k)
+
+
+@topk_reduce_compileable.register_fake
+def _(expanded, gates, T, k):
+    return torch.empty((T, expanded.size(1)), dtype=expanded.dtype, device=expanded.device)
+
+
+def topk_reduce(expanded: torch.Tensor, gates: Optional[torch.Tensor], T: int, k: int) -> torch.Tensor:
+    """out[t] = sum_j gates[t, j] * expanded[t*k + j]  (gates None: plain sum). `expanded` is (T*k, N)."""
+    if torch.compiler.is_compiling():
+        return topk_reduce_compileable(expanded, gates, T, k)
+    return _topk_reduce_impl(expanded, gates, T, k)
+
+
+def _gate_grad_impl(expanded: torch.Tensor, grad_out: torch.Tensor, T: int, k: int) -> torch.Tensor:
     _lib.require_cuda(expanded, "expanded")
     assert expanded.size(0) == T * k and grad_out.size(0) == T
     if expanded.stride(1) != 1:
@@ -297,3 +347,20 @@ def gate_grad(expanded: torch.Tensor, grad_out: torch.Tensor, T: int, k: int) ->
                                         expanded.size(1), _dtype_code(expanded), _lib.stream_ptr(expanded.device))
     _lib.check(rc, "smoe_gate_grad")
     return dg
+
+
+@torch.library.custom_op("scattermoe_b200::gate_grad", mutates_args={})
+def gate_grad_compileable(expanded: torch.Tensor, grad_out: torch.Tensor, T: int, k: int) -> torch.Tensor:
+    return _gate_grad_impl(expanded, grad_out, T, k)
+
+
+@gate_grad_compileable.register_fake
+def _(expanded, grad_out, T, k):
+    return torch.empty((T, k), dtype=expanded.dtype, device=expanded.device)
+
+
+def gate_grad(expanded: torch.Tensor, grad_out: torch.Tensor, T: int, k: int) -> torch.Tensor:
+    """d_gates[t, j] = <expanded[t*k + j], grad_out[t]>, in the dtype of `expanded`."""
+    if torch.compiler.is_compiling():
+        return gate_grad_compileable(expanded, grad_out, T, k)
+    return _gate_grad_impl(expanded, grad_out, T, k)

@@ -8,6 +8,7 @@ base class here.
 import torch
 from torch import nn
 
+from . import _lib
 from . import activation as _act
 from .parallel_experts import ParallelExperts, flatten_sort_count, parallel_linear_act
 
@@ -40,7 +41,7 @@ class _ExpertMLPBase(nn.Module):
         tokens = x.view(-1, x.shape[-1])            # any leading shape, restored on return (mlp.py:30-31, :48)
         routing = flatten_sort_count(expert_idxs, num_experts=self.num_experts)
         code = _act.resolve_activation(self.activation) if _act.FUSE else None
-        if code is not None and tokens.is_cuda:
+        if code is not None and _lib.on_device(tokens):
             # up-projection and activation as one autograd node (activation in the GEMM epilogue when the tensor-core
             # kernel applies, a separate one-pass kernel otherwise)
             hidden = parallel_linear_act(tokens, self.experts.weight.permute(0, 2, 1), self.top_k, *routing,

@@ -10,6 +10,7 @@ import torch
 import torch.nn as nn
 
 from . import _lib
+from . import activation as _act
 from . import kernels
 
 
@@ -96,7 +97,7 @@ class ParallelLinear(torch.autograd.Function):
         x = _rowmajor(x)
         x_in_expert_order = None
         if (not grouped_in and GROUP_INPUT_COPY and x.dtype in (torch.bfloat16, torch.float16)
-                and x.size(1) % 8 == 0 and x.is_cuda):
+                and x.size(1) % 8 == 0 and _lib.on_device(x)):
             x_in_expert_order = kernels.ops.group(x, sorted_scattered_idxs, fan_out=k)
             output = kernels.ops.scatter2scatter(
                 X=x_in_expert_order, W=expert_weights, b=expert_biases, k=1,
@@ -151,8 +152,10 @@ class ParallelLinear(torch.autograd.Function):
             if grouped_out:
                 grouped_grad_out = grad_out
             else:
-                grouped_grad_out = kernels.ops.group(grad_out, sorted_scattered_idxs, fan_out=gate_fan,
-                                                     coeff=gates_flat, out=grouped_grad_out)
+                # a traced backward must not write into a tensor saved by forward: allocate there instead of reusing
+                grouped_grad_out = kernels.ops.group(
+                    grad_out, sorted_scattered_idxs, fan_out=gate_fan, coeff=gates_flat,
+                    out=None if torch.compiler.is_compiling() else grouped_grad_out)
             if need_w or need_b:
                 x_rows_grouped = grouped_in or x_in_expert_order is not None
                 d_weights, d_biases = kernels.ops.group_bwd_W(
@@ -182,7 +185,6 @@ class ParallelLinearAct(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, expert_weights, k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, expert_biases,
                 act_layout, act, alpha, limit):
-        from . import activation as _act
         x = _rowmajor(x)
         x_src, kk, grouped = x, k, False
         if GROUP_INPUT_COPY and x.size(1) % 8 == 0 and x.dtype in (torch.bfloat16, torch.float16):
@@ -196,7 +198,7 @@ class ParallelLinearAct(torch.autograd.Function):
                                              expert_offsets=expert_offsets)
             F = up.size(1) if act_layout == _act.LAYOUT_PLAIN else up.size(1) // 2
             hidden = torch.empty((up.size(0), F), dtype=up.dtype, device=up.device)
-            _act._call(False, up, None, hidden, F, act_layout, act, alpha, limit)
+            _act.activation_forward(up, hidden, F, act_layout, act, alpha, limit)
         else:
             up, hidden = res
         ctx.save_for_backward(x, expert_weights, expert_biases, sorted_expert_idxs, sorted_scattered_idxs,
@@ -206,7 +208,6 @@ class ParallelLinearAct(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, d_hidden):
-        from . import activation as _act
         (x, expert_weights, expert_biases, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, up,
          x_in_expert_order) = ctx.saved_tensors
         k, act_layout, act, alpha, limit = ctx.cfg
@@ -214,7 +215,7 @@ class ParallelLinearAct(torch.autograd.Function):
         if d_hidden.dtype != up.dtype:
             d_hidden = d_hidden.to(up.dtype)
         d_up = torch.empty_like(up)
-        _act._call(True, up, d_hidden, d_up, d_hidden.size(1), act_layout, act, alpha, limit)
+        _act.activation_backward(up, d_hidden, d_up, d_hidden.size(1), act_layout, act, alpha, limit)
         d_input = d_weights = d_biases = None
         if ctx.needs_input_grad[1] or (expert_biases is not None and ctx.needs_input_grad[6]):
             grouped = x_in_expert_order is not None
@@ -230,7 +231,6 @@ class ParallelLinearAct(torch.autograd.Function):
         return (d_input, d_weights, None, None, None, None, d_biases, None, None, None, None)
 
 
-@torch.compiler.disable
 def parallel_linear_act(inputs, expert_weights, k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
                         act_layout, act, expert_biases=None, alpha=1.702, limit=7.0):
     """`parallel_linear(..., grouped_out=True)` followed by the activation, as one autograd node (an addition to the
@@ -239,12 +239,11 @@ def parallel_linear_act(inputs, expert_weights, k, sorted_expert_idxs, sorted_sc
                                    expert_offsets, expert_biases, act_layout, act, float(alpha), float(limit))
 
 
-@torch.compiler.disable
 def parallel_linear(inputs, expert_weights, k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
                     expert_biases=None, gates=None, grouped_in=False, grouped_out=False):
     """parallel_experts.py:136-146. `expert_weights` is (E, in, out) in any stride order.
-    Under torch.compile this call is a graph break: it runs eagerly between compiled regions (the kernel-level
-    operators in kernels/ops.py are registered custom ops for callers that trace them directly)."""
+    Traceable by torch.compile without graph breaks: every launch below this call is a registered operator
+    (`scattermoe_b200::*`) while a trace is being made, and a direct C-ABI call otherwise."""
     return ParallelLinear.apply(inputs, expert_weights, k, sorted_expert_idxs, sorted_scattered_idxs,
                                 expert_offsets, expert_biases, gates, grouped_in, grouped_out)
 

@@ -19,6 +19,7 @@ import logging
 import torch
 from torch.nn import functional as F
 
+from .. import _lib
 from .. import activation as _act
 from ..parallel_experts import flatten_sort_count, parallel_linear, parallel_linear_act
 
@@ -42,7 +43,7 @@ def replace_function(cls, fun_name):
 
 def gpt_oss_glu(gate_up: torch.Tensor, alpha: float, limit: float) -> torch.Tensor:
     """Clamped SwiGLU on interleaved gate/up columns (replace_moe.py:39-43)."""
-    if _act.FUSE and gate_up.is_cuda and gate_up.dim() == 2:
+    if _act.FUSE and _lib.on_device(gate_up) and gate_up.dim() == 2:
         return _act.fused_activation(gate_up, _act.LAYOUT_GPT_OSS, _act.ACT_SILU, alpha, limit)
     gate, up = gate_up[..., ::2], gate_up[..., 1::2]
     gate = gate.clamp(min=None, max=limit)
@@ -55,7 +56,7 @@ try:
 
     @replace_function(cls=GptOssExperts, fun_name='forward')
     def gpt_oss_forward(self, hidden_states: torch.Tensor, router_indices=None, routing_weights=None) -> torch.Tensor:
-        if not hidden_states.is_cuda:
+        if not _lib.on_device(hidden_states):
             return PATCHED['GptOssExperts'](self, hidden_states, router_indices=router_indices,
                                             routing_weights=routing_weights)
         batch_size = hidden_states.shape[0]
@@ -96,7 +97,7 @@ try:
 
     @replace_function(cls=GraniteMoeHybridMoE, fun_name='forward')
     def granite_moe_forward(self, layer_input):
-        if not layer_input.is_cuda:
+        if not _lib.on_device(layer_input):
             return PATCHED['GraniteMoeHybridMoE'](self, layer_input)
         bsz, length, emb_size = layer_input.size()
         tokens = layer_input.reshape(-1, emb_size)
@@ -134,7 +135,7 @@ except Exception:
 # without a router: forward(hidden_states (T, H), top_k_index (T, k), top_k_weights (T, k)) -> (T, H).
 def _fused_glu_experts_forward(cls_name):
     def forward(self, hidden_states: torch.Tensor, top_k_index: torch.Tensor, top_k_weights: torch.Tensor) -> torch.Tensor:
-        if not hidden_states.is_cuda:
+        if not _lib.on_device(hidden_states):
             return PATCHED[cls_name](self, hidden_states, top_k_index, top_k_weights)
         shape = hidden_states.shape
         tokens = hidden_states.reshape(-1, shape[-1])

@@ -264,8 +264,9 @@ def test_bf16_layers_against_fp32_dense_loop(name, T, d, F, E, k, kind, bias):
 
 
 def test_module_runs_under_torch_compile():
-    """The reference advertises its layer as usable inside torch.compile (README changelog 0.2.0). Here the
-    expert linears are graph breaks that run eagerly between compiled regions; results must not change."""
+    """The reference advertises its layer as usable inside torch.compile (README changelog 0.2.0). The whole layer
+    must trace as one graph (fullgraph=True raises on any graph break), forward and backward, with results
+    bit-equal to the eager ones."""
     import scattermoe_b200 as sm
     torch.manual_seed(0)
     m = sm.mlp.GLUMLP(256, 128, 8, 2).cuda().bfloat16()
@@ -275,7 +276,7 @@ def test_module_runs_under_torch_compile():
     leaves = [x, p, m.experts.weight, m.output_experts.weight]
     y0 = m(x, p, idx)
     g0 = torch.autograd.grad(y0, leaves, torch.ones_like(y0))
-    compiled = torch.compile(m)
+    compiled = torch.compile(m, fullgraph=True)
     y1 = compiled(x, p, idx)
     g1 = torch.autograd.grad(y1, leaves, torch.ones_like(y1))
     assert torch.equal(y1, y0)
