@@ -69,7 +69,8 @@ struct S2SParams {
 
 // Shared by all roles: offsets -> per-expert segment starts and the exclusive prefix of tiles per expert.
 __device__ __forceinline__ void build_tile_table(const int64_t* __restrict__ offsets, int64_t R, int E, int units_per_mtile,
-                                                 int32_t* seg_start, int32_t* tile_prefix, int tid, int nthreads) {
+                                                 int32_t* seg_start, int32_t* tile_prefix, int tid, int nthreads,
+                                                 int mtile_rows = BM) {
   for (int e = tid; e < E; e += nthreads) {
     int64_t v = offsets[e];
     v = v < 0 ? 0 : (v > R ? R : v);
@@ -83,7 +84,7 @@ __device__ __forceinline__ void build_tile_table(const int64_t* __restrict__ off
     int sum = 0;
     for (int e = beg; e < end; ++e) {
       const int cnt = max(0, seg_start[e + 1] - seg_start[e]);
-      sum += ((cnt + BM - 1) / BM) * units_per_mtile;
+      sum += ((cnt + mtile_rows - 1) / mtile_rows) * units_per_mtile;
     }
     int inc = sum;
 #pragma unroll
@@ -95,7 +96,7 @@ __device__ __forceinline__ void build_tile_table(const int64_t* __restrict__ off
     for (int e = beg; e < end; ++e) {
       tile_prefix[e] = run;
       const int cnt = max(0, seg_start[e + 1] - seg_start[e]);
-      run += ((cnt + BM - 1) / BM) * units_per_mtile;
+      run += ((cnt + mtile_rows - 1) / mtile_rows) * units_per_mtile;
     }
     if (tid == 31) tile_prefix[E] = inc;
   }
@@ -103,7 +104,8 @@ __device__ __forceinline__ void build_tile_table(const int64_t* __restrict__ off
 
 struct Tile { int e, m0, rows, n0; };
 
-__device__ __forceinline__ Tile decode_tile(int t, const int32_t* tile_prefix, const int32_t* seg_start, int E, int BN) {
+__device__ __forceinline__ Tile decode_tile(int t, const int32_t* tile_prefix, const int32_t* seg_start, int E, int BN,
+                                            int mtile_rows = BM) {
   int lo = 0, hi = E;
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
@@ -113,10 +115,10 @@ __device__ __forceinline__ Tile decode_tile(int t, const int32_t* tile_prefix, c
   tl.e = lo;
   const int local = t - tile_prefix[lo];
   const int cnt = seg_start[lo + 1] - seg_start[lo];
-  const int m_tiles = (cnt + BM - 1) / BM;
+  const int m_tiles = (cnt + mtile_rows - 1) / mtile_rows;
   const int n_tile = local / m_tiles, m_tile = local - n_tile * m_tiles;
-  tl.m0 = seg_start[lo] + m_tile * BM;
-  tl.rows = min(BM, seg_start[lo + 1] - tl.m0);
+  tl.m0 = seg_start[lo] + m_tile * mtile_rows;
+  tl.rows = min(mtile_rows, seg_start[lo + 1] - tl.m0);
   tl.n0 = n_tile * BN;
   return tl;
 }
@@ -205,6 +207,107 @@ __device__ __forceinline__ void flush_rows(uint8_t* slab, int lane, const uint4 
     if (ok && col < col_limit) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(ptr) + col * 2) = v;
   }
   __syncwarp();
+}
+
+// Epilogue of one tile for one warp: lane l owns accumulator row (TMEM lane) l of the warp's quarter. Reads the BN
+// accumulator columns at `taddr` 32 at a time, adds the bias, applies the fused activation (EPI) and stores the rows
+// through the warp's staging slab. Every lane runs the arithmetic (rows past the segment end hold finite leftovers
+// of other rows' tiles or zeros and are never stored): the stores are whole-warp operations.
+template <int BN, int EPI>
+__device__ __forceinline__ void epilogue_rows(const S2SParams& p, int n0, uint32_t taddr, uint8_t* slab, int lane,
+                                              bool valid, uint8_t* yrow, uint8_t* hrow, const uint8_t* brow) {
+  constexpr int TN = (EPI == EPI_GLU_HALVES) ? BN / 2 : BN;
+  const bool write_y = (EPI == EPI_NONE) || p.Y != nullptr;
+  if (EPI == EPI_GLU_HALVES) {
+#pragma unroll 1
+    for (int c = 0; c < TN / 32; ++c) {
+      const int n = n0 + c * 32;            // column inside one half
+      if (n >= p.F) break;
+      uint32_t acc_a[32], acc_b[32];
+      tmem_ld_32x32b_x32(taddr + c * 32, acc_a);
+      tmem_ld_32x32b_x32(taddr + TN + c * 32, acc_b);
+      tmem_ld_wait();
+      uint4 pa[4], pb[4], ph[4];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const int nn = min(n + g * 8, p.F - 8);      // clamped for the bias reads; the flush masks the columns
+        float a[8], b[8], h[8];
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          a[jj] = __uint_as_float(acc_a[g * 8 + jj]);
+          b[jj] = __uint_as_float(acc_b[g * 8 + jj]);
+        }
+        add_bias8(brow, nn, p.is_bf16, p.bias_vec, a);
+        add_bias8(brow, p.F + nn, p.is_bf16, p.bias_vec, b);
+        SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj)
+          h[jj] = p.glu_first ? act_fwd<ACT_, true>(a[jj]) * b[jj] : act_fwd<ACT_, true>(b[jj]) * a[jj];)
+        pa[g] = pack8(a, p.is_bf16);
+        pb[g] = pack8(b, p.is_bf16);
+        ph[g] = pack8(h, p.is_bf16);
+      }
+      if (write_y) {
+        flush_rows<4>(slab, lane, pa, yrow, valid, n, p.F);
+        flush_rows<4>(slab, lane, pb, yrow + static_cast<int64_t>(p.F) * 2, valid, n, p.F);
+      }
+      flush_rows<4>(slab, lane, ph, hrow, valid, n, p.F);
+    }
+  } else {
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      const int n = n0 + c * 32;
+      if (n >= p.N) break;
+      uint32_t acc[32];
+      tmem_ld_32x32b_x32(taddr + c * 32, acc);
+      tmem_ld_wait();
+      uint4 py[4];
+      if (EPI == EPI_GPT_OSS) {
+        uint4 ph[2];
+#pragma unroll
+        for (int gg = 0; gg < 2; ++gg) {           // 16 accumulator columns -> 8 hidden columns
+          const int nn = min(n + gg * 16, p.N - 16);
+          float v0[8], v1[8], h[8];
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) {
+            v0[jj] = __uint_as_float(acc[gg * 16 + jj]);
+            v1[jj] = __uint_as_float(acc[gg * 16 + 8 + jj]);
+          }
+          add_bias8(brow, nn, p.is_bf16, p.bias_vec, v0);
+          add_bias8(brow, nn + 8, p.is_bf16, p.bias_vec, v1);
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) {
+            const float g0 = (jj < 4) ? v0[2 * jj] : v1[2 * jj - 8];
+            const float u0 = (jj < 4) ? v0[2 * jj + 1] : v1[2 * jj - 7];
+            const float gc = fminf(g0, p.limit);
+            const float uc = fminf(fmaxf(u0, -p.limit), p.limit);
+            h[jj] = (uc + 1.0f) * (gc * sigmoidf_<true>(p.alpha * gc));
+          }
+          py[2 * gg] = pack8(v0, p.is_bf16);
+          py[2 * gg + 1] = pack8(v1, p.is_bf16);
+          ph[gg] = pack8(h, p.is_bf16);
+        }
+        if (write_y) flush_rows<4>(slab, lane, py, yrow, valid, n, p.N);
+        flush_rows<2>(slab, lane, ph, hrow, valid, n / 2, p.N / 2);
+      } else {
+        uint4 ph[4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int nn = min(n + g * 8, p.N - 8);
+          float v[8];
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) v[jj] = __uint_as_float(acc[g * 8 + jj]);
+          add_bias8(brow, nn, p.is_bf16, p.bias_vec, v);
+          py[g] = pack8(v, p.is_bf16);
+          if (EPI == EPI_ACT) {
+            float h[8];
+            SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj) h[jj] = act_fwd<ACT_, true>(v[jj]);)
+            ph[g] = pack8(h, p.is_bf16);
+          }
+        }
+        if (write_y) flush_rows<4>(slab, lane, py, yrow, valid, n, p.N);
+        if (EPI == EPI_ACT) flush_rows<4>(slab, lane, ph, hrow, valid, n, p.N);
+      }
+    }
+  }
 }
 
 template <int BN, bool B_KMAJOR, int EPI>
@@ -405,99 +508,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
       uint8_t* hrow = (EPI != EPI_NONE) ? p.H + out_row * p.h_row_bytes : nullptr;
       uint8_t* slab = epi_staging + q * (32 * C::STAGE_ROW_BYTES);
-      const bool write_y = (EPI == EPI_NONE) || p.Y != nullptr;
-      // every lane runs the arithmetic (rows past the segment end hold finite leftovers of other rows' tiles or
-      // zeros and are never stored): the stores below are whole-warp operations
-      if (EPI == EPI_GLU_HALVES) {
-#pragma unroll 1
-        for (int c = 0; c < TN / 32; ++c) {
-          const int n = tl.n0 + c * 32;            // column inside one half
-          if (n >= p.F) break;
-          uint32_t acc_a[32], acc_b[32];
-          tmem_ld_32x32b_x32(taddr + c * 32, acc_a);
-          tmem_ld_32x32b_x32(taddr + TN + c * 32, acc_b);
-          tmem_ld_wait();
-          uint4 pa[4], pb[4], ph[4];
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int nn = min(n + g * 8, p.F - 8);      // clamped for the bias reads; the flush masks the columns
-            float a[8], b[8], h[8];
-#pragma unroll
-            for (int jj = 0; jj < 8; ++jj) {
-              a[jj] = __uint_as_float(acc_a[g * 8 + jj]);
-              b[jj] = __uint_as_float(acc_b[g * 8 + jj]);
-            }
-            add_bias8(brow, nn, p.is_bf16, p.bias_vec, a);
-            add_bias8(brow, p.F + nn, p.is_bf16, p.bias_vec, b);
-            SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj)
-              h[jj] = p.glu_first ? act_fwd<ACT_, true>(a[jj]) * b[jj] : act_fwd<ACT_, true>(b[jj]) * a[jj];)
-            pa[g] = pack8(a, p.is_bf16);
-            pb[g] = pack8(b, p.is_bf16);
-            ph[g] = pack8(h, p.is_bf16);
-          }
-          if (write_y) {
-            flush_rows<4>(slab, lane, pa, yrow, valid, n, p.F);
-            flush_rows<4>(slab, lane, pb, yrow + static_cast<int64_t>(p.F) * 2, valid, n, p.F);
-          }
-          flush_rows<4>(slab, lane, ph, hrow, valid, n, p.F);
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int n = tl.n0 + c * 32;
-          if (n >= p.N) break;
-          uint32_t acc[32];
-          tmem_ld_32x32b_x32(taddr + c * 32, acc);
-          tmem_ld_wait();
-          uint4 py[4];
-          if (EPI == EPI_GPT_OSS) {
-            uint4 ph[2];
-#pragma unroll
-            for (int gg = 0; gg < 2; ++gg) {           // 16 accumulator columns -> 8 hidden columns
-              const int nn = min(n + gg * 16, p.N - 16);
-              float v0[8], v1[8], h[8];
-#pragma unroll
-              for (int jj = 0; jj < 8; ++jj) {
-                v0[jj] = __uint_as_float(acc[gg * 16 + jj]);
-                v1[jj] = __uint_as_float(acc[gg * 16 + 8 + jj]);
-              }
-              add_bias8(brow, nn, p.is_bf16, p.bias_vec, v0);
-              add_bias8(brow, nn + 8, p.is_bf16, p.bias_vec, v1);
-#pragma unroll
-              for (int jj = 0; jj < 8; ++jj) {
-                const float g0 = (jj < 4) ? v0[2 * jj] : v1[2 * jj - 8];
-                const float u0 = (jj < 4) ? v0[2 * jj + 1] : v1[2 * jj - 7];
-                const float gc = fminf(g0, p.limit);
-                const float uc = fminf(fmaxf(u0, -p.limit), p.limit);
-                h[jj] = (uc + 1.0f) * (gc * sigmoidf_<true>(p.alpha * gc));
-              }
-              py[2 * gg] = pack8(v0, p.is_bf16);
-              py[2 * gg + 1] = pack8(v1, p.is_bf16);
-              ph[gg] = pack8(h, p.is_bf16);
-            }
-            if (write_y) flush_rows<4>(slab, lane, py, yrow, valid, n, p.N);
-            flush_rows<2>(slab, lane, ph, hrow, valid, n / 2, p.N / 2);
-          } else {
-            uint4 ph[4];
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int nn = min(n + g * 8, p.N - 8);
-              float v[8];
-#pragma unroll
-              for (int jj = 0; jj < 8; ++jj) v[jj] = __uint_as_float(acc[g * 8 + jj]);
-              add_bias8(brow, nn, p.is_bf16, p.bias_vec, v);
-              py[g] = pack8(v, p.is_bf16);
-              if (EPI == EPI_ACT) {
-                float h[8];
-                SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj) h[jj] = act_fwd<ACT_, true>(v[jj]);)
-                ph[g] = pack8(h, p.is_bf16);
-              }
-            }
-            if (write_y) flush_rows<4>(slab, lane, py, yrow, valid, n, p.N);
-            if (EPI == EPI_ACT) flush_rows<4>(slab, lane, ph, hrow, valid, n, p.N);
-          }
-        }
-      }
+      epilogue_rows<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, hrow, brow);
       tc_fence_before_sync();
       mbar_arrive(tempty_bar(buf));
     }
@@ -509,6 +520,203 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// CTA-pair variant of the grouped GEMM (tcgen05 cta_group::2): the two CTAs of a cluster compute one tile of 256
+// sorted positions x 256 output columns. Each CTA stages its own 128 rows of A and only ITS half (128 columns) of
+// the weight tile, so a stage is 32 KB instead of 48 KB: a third less traffic from L2 into shared memory per flop
+// and a 6-deep ring instead of 4. The leader (cluster rank 0) issues the MMAs for both; every CTA keeps its 128
+// accumulator rows in its own tensor memory and runs its own epilogue. Needs both operands TMA-addressable (rows in
+// expert order); other requests take s2s_tc_kernel.
+//   full[s]   (leader's)  1 arrival (leader's expect_tx for both CTAs' bytes) + the bytes of both CTAs' copies
+//   empty[s]  (each CTA)  1 arrival: the leader's commit, sent to both CTAs
+//   tfull[b]  (each CTA)  1 arrival: the leader's commit, sent to both CTAs
+//   tempty[b] (leader's)  256 arrivals: the epilogue threads of both CTAs
+struct PairCfg {
+  static constexpr int BN = 256;
+  static constexpr int STAGES = 6;
+  static constexpr int B_HALF_BYTES = 128 * BK * 2;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int BAR_BYTES = 256;
+  static constexpr int TABLE_BYTES = ((2 * (MAX_E + 1) * 4 + 15) / 16) * 16;
+  static constexpr int STAGE_ROW_BYTES = 80;
+  static constexpr int EPI_STAGING_BYTES = 4 * 32 * STAGE_ROW_BYTES;
+  static constexpr int SMEM_BYTES =
+      1024 + STAGES * (A_STAGE_BYTES + B_HALF_BYTES) + BAR_BYTES + TABLE_BYTES + EPI_STAGING_BYTES;
+};
+constexpr int PAIR_ROWS = 2 * BM;
+constexpr bool PAIR_BY_DEFAULT = false;   // the single-CTA kernel unless SMOE_FLAG_PAIR asks for pairs
+
+template <bool B_KMAJOR, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+s2s_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                const S2SParams p) {
+  using C = PairCfg;
+  constexpr int STAGES = C::STAGES;
+  constexpr int BN = C::BN;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + C::B_HALF_BYTES));
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  int32_t* seg_start = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(bars) + C::BAR_BYTES);
+  int32_t* tile_prefix = seg_start + (MAX_E + 1);
+  uint8_t* epi_staging = reinterpret_cast<uint8_t*>(bars) + C::BAR_BYTES + C::TABLE_BYTES;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = cluster_ctarank();          // 0: leader
+  const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  constexpr int TN = (EPI == EPI_GLU_HALVES) ? BN / 2 : BN;
+  const int n_tiles = ((EPI == EPI_GLU_HALVES ? p.F : p.N) + TN - 1) / TN;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(tfull_bar(b), 1);
+      mbar_init(tempty_bar(b), 256);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_w);
+    tma_prefetch_desc(&tmap_x);
+  }
+  build_tile_table(p.offsets, p.R, p.E, n_tiles, seg_start, tile_prefix, tid, NUM_THREADS, PAIR_ROWS);
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_holder), C::TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync();                 // the peer's barriers exist before anything is sent to them
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_holder;
+  const int total_tiles = tile_prefix[p.E];
+
+  if (warp == 0) {
+    // ---------------- this CTA's rows of A and its half of the weight tile: TMA producer ------------------
+    int it = 0;
+    bool ok = true;
+    for (int t = pair_id; t < total_tiles && ok; t += num_pairs) {
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, PAIR_ROWS);
+      const int m0 = tl.m0 + static_cast<int>(rank) * BM;
+      // first weight row / column of this CTA's half of the B tile
+      const int nb = (EPI == EPI_GLU_HALVES) ? (rank == 0 ? tl.n0 : p.F + tl.n0) : tl.n0 + static_cast<int>(rank) * 128;
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1;
+        if (!mbar_wait_warp(empty_bar(s), ph ^ 1, abort_flag, p.status, 21)) { ok = false; break; }
+        if (lane == 0) {
+          const uint32_t full_leader = mapa_shared(full_bar(s), 0);
+          if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * (A_STAGE_BYTES + C::B_HALF_BYTES));
+          tma_load_2d_pair(smem_u32(sA + s * A_STAGE_BYTES), &tmap_x, full_leader, kb * BK, m0);
+          const uint32_t dst = smem_u32(sB + s * C::B_HALF_BYTES);
+          if (B_KMAJOR) {
+            tma_load_3d_pair(dst, &tmap_w, full_leader, kb * BK, nb, tl.e);
+          } else {
+            tma_load_3d_pair(dst, &tmap_w, full_leader, nb, kb * BK, tl.e);
+            tma_load_3d_pair(dst + 64 * BK * 2, &tmap_w, full_leader, nb + 64, kb * BK, tl.e);
+          }
+        }
+        __syncwarp();
+      }
+    }
+    // the leader's last commits still arrive on this CTA's empty barriers: take them before leaving the loop
+    for (int i = 0; i < STAGES && ok; ++i, ++it) {
+      const int s = it % STAGES;
+      const uint32_t ph = (it / STAGES) & 1;
+      if (!mbar_wait_warp(empty_bar(s), ph ^ 1, abort_flag, p.status, 26)) ok = false;
+    }
+    if (!ok) {
+      for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer: leader CTA only ---------------------------------------------------------
+    if (rank == 0) {
+      int it = 0, tile_iter = 0;
+      bool ok = true;
+      for (int t = pair_id; t < total_tiles && ok; t += num_pairs, ++tile_iter) {
+        const int buf = tile_iter & 1;
+        const uint32_t tph = (tile_iter >> 1) & 1;
+        if (!mbar_wait_warp(tempty_bar(buf), tph ^ 1, abort_flag, p.status, 22)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait_warp(full_bar(s), ph, abort_flag, p.status, 23)) { ok = false; break; }
+          tc_fence_after_sync();
+          if (lane == 0) {
+            const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
+            const uint32_t b_addr = smem_u32(sB + s * C::B_HALF_BYTES);
+#pragma unroll
+            for (int j = 0; j < BK / UMMA_K; ++j) {
+              const uint64_t adesc = make_smem_desc_sw128(a_addr + j * (UMMA_K * 2), 16, 1024);
+              const uint64_t bdesc = B_KMAJOR ? make_smem_desc_sw128(b_addr + j * (UMMA_K * 2), 16, 1024)
+                                              : make_smem_desc_sw128(b_addr + j * (UMMA_K * 128), 64 * BK * 2, 1024);
+              umma_f16_pair(d_tmem, adesc, bdesc, p.idesc, (kb | j) != 0 ? 1u : 0u);
+            }
+            umma_commit_pair(empty_bar(s), 3);
+          }
+          __syncwarp();
+        }
+        if (ok && lane == 0) umma_commit_pair(tfull_bar(buf), 3);
+        __syncwarp();
+      }
+    }
+  } else if (warp < 6) {
+    // both operands come by TMA: nothing to gather
+  } else {
+    // ---------------- epilogue: this CTA's 128 rows of the pair's tile -------------------------------------
+    const int q = warp & 3;
+    const int r = q * 32 + lane;
+    int tile_iter = 0;
+    bool ok = true;
+    for (int t = pair_id; t < total_tiles && ok; t += num_pairs, ++tile_iter) {
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, PAIR_ROWS);
+      const int buf = tile_iter & 1;
+      const uint32_t tph = (tile_iter >> 1) & 1;
+      const int row_in_tile = static_cast<int>(rank) * BM + r;
+      bool valid = row_in_tile < tl.rows;
+      int64_t out_row = 0;
+      if (valid) {
+        const int64_t m = tl.m0 + row_in_tile;
+        out_row = p.y_grouped ? m : p.sorted_idx[m];
+        valid = out_row >= 0 && out_row < p.R;
+      }
+      uint8_t* yrow = p.Y + out_row * p.y_row_bytes;
+      const uint8_t* brow = p.bias ? p.bias + static_cast<int64_t>(tl.e) * p.bias_row_elems * 2 : nullptr;
+      if (!mbar_wait_warp(tfull_bar(buf), tph, abort_flag, p.status, 25)) { ok = false; break; }
+      tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+      uint8_t* hrow = (EPI != EPI_NONE) ? p.H + out_row * p.h_row_bytes : nullptr;
+      uint8_t* slab = epi_staging + q * (32 * C::STAGE_ROW_BYTES);
+      epilogue_rows<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, hrow, brow);
+      tc_fence_before_sync();
+      mbar_arrive_cluster(mapa_shared(tempty_bar(buf), 0));
+    }
+  }
+
+  // ---------------- teardown: nobody leaves while the peer may still read its memory or signal it -----------
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
   }
 }
 
@@ -927,6 +1135,39 @@ static int launch_s2s_cfg(const CUtensorMap& map, const CUtensorMap& map_x, cons
   return SMOE_OK;
 }
 
+template <bool B_KMAJOR, int EPI>
+static int launch_s2s_pair(const CUtensorMap& map, const CUtensorMap& map_x, const S2SParams& p, int64_t max_tiles,
+                           cudaStream_t stream) {
+  static std::mutex mu;
+  static int max_pairs[64] = {0};          // 0: not asked yet
+  int dev = 0;
+  SMOE_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return SMOE_ERR_UNSUPPORTED;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (max_pairs[dev] == 0) {
+      SMOE_CUDA(cudaFuncSetAttribute(s2s_pair_kernel<B_KMAJOR, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     PairCfg::SMEM_BYTES));
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2, 1, 1);
+      cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+      cfg.dynamicSmemBytes = PairCfg::SMEM_BYTES;
+      int n = 0;
+      const cudaError_t err = cudaOccupancyMaxActiveClusters(&n, s2s_pair_kernel<B_KMAJOR, EPI>, &cfg);
+      if (err != cudaSuccess) (void)cudaGetLastError();
+      DeviceInfo di;
+      if (int rc = get_device_info(&di)) return rc;
+      // resident pairs decide only how the tiles are dealt out; without an answer assume one CTA per SM
+      max_pairs[dev] = (err == cudaSuccess && n > 0) ? n : (di.sm_count / 2 > 0 ? di.sm_count / 2 : 1);
+    }
+  }
+  const int pairs = static_cast<int>(max_tiles < max_pairs[dev] ? max_tiles : max_pairs[dev]);
+  if (pairs <= 0) return SMOE_ERR_UNSUPPORTED;
+  s2s_pair_kernel<B_KMAJOR, EPI><<<2 * pairs, NUM_THREADS, PairCfg::SMEM_BYTES, stream>>>(map, map_x, p);
+  SMOE_LAUNCH_CHECK();
+  return SMOE_OK;
+}
+
 // rank-2 map over (feature, row) of 16-bit elements, box0 x box1 box (64 x 64 by default), 128-byte swizzle.
 static bool encode_map2(CUtensorMap* map, bool bf16, const void* base, uint64_t d0, uint64_t d1,
                         uint64_t stride1_bytes, uint32_t box0 = 64, uint32_t box1 = BK) {
@@ -1019,6 +1260,45 @@ int launch_s2s_tc(const S2SArgs& a) {
                 encode_map2(&map_x, bf16, a.X, a.K, a.x_rows, static_cast<uint64_t>(a.sxm) * 2, 64, BM)) ? 1 : 0;
 
   const int tile_cols = epi == EPI_GLU_HALVES ? BN / 2 : BN;
+
+  // CTA-pair kernel: rows in expert order, a full-width tile, and enough rows per expert that 256-row tiles are
+  // mostly full. SMOE_FLAG_PAIR / SMOE_FLAG_NO_PAIR override the choice.
+  const bool pair_auto = PAIR_BY_DEFAULT && a.R >= static_cast<int64_t>(a.E) * 4 * PAIR_ROWS;
+  const bool want_pair = !(a.flags & SMOE_FLAG_NO_PAIR) && ((a.flags & SMOE_FLAG_PAIR) || pair_auto);
+  if (want_pair && p.a_by_tma && BN == 256) {
+    CUtensorMap map_pair = map;
+    bool okp = true;
+    if (k_major && epi != EPI_GLU_HALVES)
+      okp = encode_map3(&map_pair, bf16, a.W, a.K, a.N, a.E, static_cast<uint64_t>(a.swn) * 2, e_stride, BK, 128);
+    if (okp) {
+      S2SParams pp = p;
+      pp.idesc = make_idesc_f16(bf16, false, !k_major, PAIR_ROWS, 256);
+      const int64_t pair_tiles = (cdiv64(a.R, PAIR_ROWS) + a.E) * cdiv(epi == EPI_GLU_HALVES ? F : a.N, tile_cols);
+      int rc = SMOE_ERR_UNSUPPORTED;
+      switch (epi) {
+        case EPI_NONE:
+          rc = k_major ? launch_s2s_pair<true, EPI_NONE>(map_pair, map_x, pp, pair_tiles, a.stream)
+                       : launch_s2s_pair<false, EPI_NONE>(map_pair, map_x, pp, pair_tiles, a.stream);
+          break;
+        case EPI_ACT:
+          rc = k_major ? launch_s2s_pair<true, EPI_ACT>(map_pair, map_x, pp, pair_tiles, a.stream)
+                       : launch_s2s_pair<false, EPI_ACT>(map_pair, map_x, pp, pair_tiles, a.stream);
+          break;
+        case EPI_GLU_HALVES:
+          rc = k_major ? launch_s2s_pair<true, EPI_GLU_HALVES>(map_pair, map_x, pp, pair_tiles, a.stream)
+                       : launch_s2s_pair<false, EPI_GLU_HALVES>(map_pair, map_x, pp, pair_tiles, a.stream);
+          break;
+        case EPI_GPT_OSS:
+          rc = k_major ? launch_s2s_pair<true, EPI_GPT_OSS>(map_pair, map_x, pp, pair_tiles, a.stream)
+                       : launch_s2s_pair<false, EPI_GPT_OSS>(map_pair, map_x, pp, pair_tiles, a.stream);
+          break;
+        default: break;
+      }
+      if (rc != SMOE_ERR_UNSUPPORTED) return rc;
+    }
+  }
+  if ((a.flags & SMOE_FLAG_PAIR) && (a.flags & SMOE_FLAG_FORCE_TC)) return SMOE_ERR_UNSUPPORTED;
+
   const int64_t max_tiles = (cdiv64(a.R, BM) + a.E) * cdiv(epi == EPI_GLU_HALVES ? F : a.N, tile_cols);
   const int grid = static_cast<int>(max_tiles < di.sm_count ? max_tiles : di.sm_count);
   switch (epi) {

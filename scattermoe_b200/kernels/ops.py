@@ -21,6 +21,7 @@ BLOCK_M = 128        # rows of the expert-sorted slot list per tensor-core tile 
 ALLOW_TF32 = True    # fp32 inputs may use reduced-precision tensor cores (ops.py:7); read at call time
 FORCE_PATH = None    # testing hook: None (automatic) | "simt" | "tc"
 GATHER_ROWS = False  # testing hook: feed grouped inputs through the cp.async row-gather path instead of TMA
+PAIR = None          # None: the library chooses | True / False: ask for / forbid the two-CTA tensor-core kernel
 
 
 def _flags() -> int:
@@ -31,6 +32,8 @@ def _flags() -> int:
         f |= _lib.FLAG_FORCE_TC
     if GATHER_ROWS:
         f |= _lib.FLAG_GATHER_ROWS
+    if PAIR is not None:
+        f |= _lib.FLAG_PAIR if PAIR else _lib.FLAG_NO_PAIR
     return f
 
 
@@ -146,7 +149,7 @@ def _scatter2scatter_act_impl(up, hidden, W, X, k, sorted_expert_idxs, sorted_sc
             _ptr(b), sb[0], sb[1],
             _ptr(up), up.stride(0) if up is not None else 0, 1, hidden.data_ptr(), hidden.stride(0),
             se.data_ptr(), ss.data_ptr(), off.data_ptr(),
-            se.numel(), X.size(1), N, E, k, int(x_grouped), _dtype_code(X), _flags() & ~_lib.FLAG_FORCE_TC,
+            se.numel(), X.size(1), N, E, k, int(x_grouped), _dtype_code(X), _flags(),
             act_layout, act, float(alpha), float(limit),
             _lib.status_word(X.device).data_ptr(), _lib.stream_ptr(X.device))
     if rc == _lib.SMOE_ERR_UNSUPPORTED:
