@@ -838,6 +838,9 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_consta
           if (slab_ragged(c, m_beg, m_end)) {
             mbar_arrive(full_bar(s));          // nothing comes by TMA for this slab
           } else {
+            // a slab that comes whole by TMA needs nothing from the 128 gather threads: their arrivals are made
+            // here in one instruction (128 same-address arrives per slab cost the shared-memory pipe the MMAs need)
+            if (x_too) mbar_arrive_count(full_bar(s), 128);
             mbar_arrive_expect_tx(full_bar(s), A_STAGE_BYTES + (x_too ? C::B_STAGE_BYTES : 0));
             const uint32_t dst = smem_u32(sA + s * A_STAGE_BYTES);
             tma_load_2d(dst, &tmap_dy, full_bar(s), n0, m_beg + c * BK);
@@ -961,15 +964,15 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_consta
           }
         }
         if (p.x_by_tma) {
-          // Grouped X: only ragged tail slabs carry copies of these threads. Publishing a slab as soon as its
-          // stage is free (not two slabs later, as the lagged scheme below does) keeps the gather threads off the
-          // MMA's critical path.
+          // Grouped X: only ragged tail slabs carry copies of these threads (published as soon as they have
+          // landed, not two slabs later as in the lagged scheme below); for whole slabs the TMA lane arrives on
+          // their behalf and these threads only follow the ring's phases.
           if (slab_ragged(c, m_beg, m_end)) {
             cp_async_commit();
             cp_async_wait<0>();
             fence_proxy_async_smem();
+            mbar_arrive(full_bar(s));
           }
-          mbar_arrive(full_bar(s));
         } else {
           cp_async_commit();
           if (it >= A_LAG) {
