@@ -760,6 +760,9 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_consta
   auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  // go[s]: "stage s is free for the ragged tail slab", TMA lane -> gather threads (grouped X only)
+  auto go_bar = [&](int s) { return bar0 + 8u * (2 * STAGES + 5 + s); };
+  static_assert((3 * STAGES + 5) * 8 <= C::BAR_BYTES, "barrier area too small");
   int32_t* seg_start = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(bars) + C::BAR_BYTES);
   uint8_t* epi_staging = reinterpret_cast<uint8_t*>(bars) + C::BAR_BYTES + C::TABLE_BYTES;
 
@@ -773,6 +776,7 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_consta
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1 + 128);
       mbar_init(empty_bar(s), 1);
+      mbar_init(go_bar(s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(tfull_bar(b), 1);
@@ -836,7 +840,8 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_consta
         if (lane == 0) {
           const bool x_too = slab_by_tma(c, m_beg, m_end);
           if (slab_ragged(c, m_beg, m_end)) {
-            mbar_arrive(full_bar(s));          // nothing comes by TMA for this slab
+            if (p.x_by_tma) mbar_arrive(go_bar(s));   // the gather threads may now fill this stage
+            mbar_arrive(full_bar(s));                  // nothing comes by TMA for this slab
           } else {
             // a slab that comes whole by TMA needs nothing from the 128 gather threads: their arrivals are made
             // here in one instruction (128 same-address arrives per slab cost the shared-memory pipe the MMAs need)
@@ -894,6 +899,61 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_consta
       if (ok && lane == 0) umma_commit(tfull_bar(buf));
       __syncwarp();
       ++tile_iter;
+    }
+  } else if (warp < 6 && p.x_by_tma) {
+    // ---------------- grouped X: only the ragged tail slab of a tile is copied by these threads ------------
+    // Whole slabs need nothing from them (the TMA lane makes their 128 arrivals in one instruction), and they do
+    // not follow the ring: they wait on go[s], which the TMA lane signals once per ragged use of stage s and
+    // which cannot complete a second time before all of them have arrived for the first (the MMA needs their
+    // arrivals to free the stage), so its parity can never run ahead of a waiting thread.
+    const int ptid = tid - 64;
+    const int chunk = ptid % CPR;
+    const int row_base = ptid / CPR;
+    const uint32_t box_off = (chunk >> 3) * (64 * BK * 2);
+    const int a_chunk = ptid & 15, a_row0 = ptid >> 4;
+    uint32_t go_parity = 0;            // bit s: parity of the next go[s] phase
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int e, n0, k0, m_beg, m_end;
+      decode(t, e, n0, k0, m_beg, m_end);
+      const int nchunks = (m_end - m_beg + BK - 1) / BK;
+      if (nchunks == 0) continue;
+      const int c = nchunks - 1;
+      if (slab_ragged(c, m_beg, m_end)) {
+        const int s = (it + c) % STAGES;
+        if (!mbar_wait_warp(go_bar(s), (go_parity >> s) & 1u, abort_flag, p.status, 16)) { ok = false; break; }
+        go_parity ^= 1u << s;
+        const int64_t m0 = static_cast<int64_t>(m_beg) + c * BK;
+        // DY slab: 64 rows x 128 features = 1024 16-byte chunks, 8 per thread
+        const bool n_ok = (n0 + a_chunk * 8) < p.N;
+        const uint32_t dsta = smem_u32(sA + s * A_STAGE_BYTES) + (a_chunk >> 3) * (64 * BK * 2);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int row = a_row0 + 8 * i;
+          const int64_t m = m0 + row;
+          const bool v = n_ok && m < m_end;
+          cp_async16(dsta + row * 128 + (((a_chunk & 7) ^ (row & 7)) << 4),
+                     v ? p.DY + m * p.dy_row_bytes + static_cast<int64_t>(n0 + a_chunk * 8) * 2 : p.DY, v ? 16u : 0u);
+        }
+        // X slab: 64 rows x BNW features
+        const bool k_ok = (k0 + chunk * 8) < p.K;
+        const int64_t col_bytes = static_cast<int64_t>(k0 + chunk * 8) * 2;
+        const uint32_t dstb = smem_u32(sB + s * C::B_STAGE_BYTES) + box_off;
+#pragma unroll
+        for (int i = 0; i < NI; ++i) {
+          const int row = row_base + RPP * i;
+          const int64_t m = m0 + row;
+          const bool v = k_ok && m < m_end && m < p.x_rows;
+          cp_async16(dstb + row * 128 + (((chunk & 7) ^ (row & 7)) << 4), v ? p.X + m * p.x_row_bytes + col_bytes : p.X,
+                     v ? 16u : 0u);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        fence_proxy_async_smem();
+        mbar_arrive(full_bar(s));
+      }
+      it += nchunks;
     }
   } else if (warp < 6) {
     // ---------------- X slabs: cp.async row gather (zero-fill past the segment end) ----------------------
@@ -964,9 +1024,7 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_consta
           }
         }
         if (p.x_by_tma) {
-          // Grouped X: only ragged tail slabs carry copies of these threads (published as soon as they have
-          // landed, not two slabs later as in the lagged scheme below); for whole slabs the TMA lane arrives on
-          // their behalf and these threads only follow the ring's phases.
+          // not reached: grouped X takes the branch above (p.x_by_tma is uniform for the launch)
           if (slab_ragged(c, m_beg, m_end)) {
             cp_async_commit();
             cp_async_wait<0>();
