@@ -173,6 +173,22 @@ def parallel_linear_backward(grad_out, x, expert_weights, k, sorted_expert_idxs,
 
 
 # --------------------------------------------------------------------------------------
+# single-token path
+# --------------------------------------------------------------------------------------
+
+def single2scatter(X, W, expert_idxs):
+    """scattermoe/kernels/single.py:41-60 (_single2scatter :6-39): one token routed to k experts.
+    Y[j] = X[j if X has k rows else 0] @ W[expert_idxs[0, j]], fp32 accumulation, output in X's dtype."""
+    k = expert_idxs.size(1)
+    assert X.size(0) == k or X.size(0) == 1
+    rows = []
+    for j in range(k):
+        x = X[j if X.size(0) == k else 0].to(torch.float32)
+        rows.append(x @ W[int(expert_idxs[0, j])].to(torch.float32))
+    return torch.stack(rows).to(X.dtype)
+
+
+# --------------------------------------------------------------------------------------
 # activations placed between the two expert linears
 # --------------------------------------------------------------------------------------
 

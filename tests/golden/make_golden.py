@@ -58,12 +58,27 @@ def routing(gen, T, E, k, renorm=True, skew=False):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=os.environ.get("SCATTERMOE_REFERENCE"), required="SCATTERMOE_REFERENCE" not in os.environ)
+    ap.add_argument("--only", choices=["single"], default=None,
+                    help="regenerate one group of fixtures instead of all of them")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
     import scattermoe
     from scattermoe.kernels import ops
     from scattermoe.mlp import MLP, GLUMLP
     ops.ALLOW_TF32 = False
+
+    # ---- single-token kernel (kernels/single.py:41): one or k input rows, both weight orientations --------
+    from scattermoe.kernels.single import single2scatter
+    for i, (E, k, K, N, x_rows, n_major) in enumerate([(4, 2, 128, 256, 1, True), (8, 4, 256, 128, 4, False),
+                                                       (8, 3, 384, 256, 1, False)]):
+        gen = torch.Generator().manual_seed(700 + i)
+        X = torch.randn(x_rows, K, generator=gen)
+        W = torch.randn(E, K, N, generator=gen) * 0.1 if n_major else (torch.randn(E, N, K, generator=gen) * 0.1).permute(0, 2, 1)
+        idx = torch.randperm(E, generator=gen)[:k].view(1, k)
+        Y = single2scatter(X, W, idx)
+        save(f"single_{i}", X=npy(X), W=npy(W.contiguous()), expert_idxs=npy(idx), w_n_contiguous=np.bool_(n_major), Y=npy(Y))
+    if args.only == "single":
+        return
 
     # ---- routing bookkeeping -----------------------------------------------------------
     gen = torch.Generator().manual_seed(0)

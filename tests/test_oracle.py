@@ -139,3 +139,11 @@ def test_hf_granite_golden():
     assert_close("Y", out["y"].reshape(x.shape), g["Y"], False)
     assert_close("dW1", out["d_w1"].permute(0, 2, 1), g["grad.input_linear.weight"], False)
     assert_close("dW2", out["d_w2"].permute(0, 2, 1), g["grad.output_linear.weight"], False)
+
+
+@pytest.mark.parametrize("name", golden_names("single_"))
+def test_single2scatter(name):
+    """The single-token kernel (kernels/single.py) as run by the reference itself."""
+    g = load_golden(name)
+    y = oracle.single2scatter(g["X"], g["W"], g["expert_idxs"])     # W stored as (E, K, N) values
+    assert_close(name, y, g["Y"], False)
