@@ -153,21 +153,6 @@ __device__ __forceinline__ void add_bias8(const uint8_t* brow, int col, int is_b
   }
 }
 
-__device__ __forceinline__ void store8(uint8_t* dst, const float (&v)[8], int is_bf16) {
-  uint32_t o[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    if (is_bf16) {
-      const __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-      o[j] = *reinterpret_cast<const uint32_t*>(&h);
-    } else {
-      const __half2 h = __floats2half2_rn(v[2 * j], v[2 * j + 1]);
-      o[j] = *reinterpret_cast<const uint32_t*>(&h);
-    }
-  }
-  *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
-}
-
 __device__ __forceinline__ uint4 pack8(const float (&v)[8], int is_bf16) {
   uint32_t o[4];
 #pragma unroll
