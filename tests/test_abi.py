@@ -90,3 +90,19 @@ def test_reference_arm_of_the_benchmark_runs_on_the_host():
         assert key in line, key
     assert line["impl"] == "reference" and line["cpu_baseline"]["kind"] == "port" and line["value"] > 0
     assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["d2h_bytes_per_step"] == 0
+
+
+def test_python_constants_match_the_header():
+    """Status codes, dtype codes and flag bits are copied by value into the ctypes binding: they must not drift."""
+    import re
+    import torch
+    from scattermoe_b200 import _lib
+    text = open(os.path.join(ROOT, "include", "scattermoe_b200.h")).read()
+    enum = {m.group(1): int(m.group(2)) for m in re.finditer(r"\b(SMOE_[A-Z0-9_]+)\s*=\s*(\d+)", text)}
+    assert enum["SMOE_OK"] == _lib.SMOE_OK and enum["SMOE_ERR_BAD_ARG"] == _lib.SMOE_ERR_BAD_ARG
+    assert enum["SMOE_ERR_UNSUPPORTED"] == _lib.SMOE_ERR_UNSUPPORTED
+    for name in ("ALLOW_TF32", "FORCE_SIMT", "FORCE_TC", "GATHER_ROWS", "PAIR", "NO_PAIR"):
+        assert enum["SMOE_FLAG_" + name] == getattr(_lib, "FLAG_" + name), name
+    assert {torch.float32: enum["SMOE_F32"], torch.bfloat16: enum["SMOE_BF16"], torch.float16: enum["SMOE_F16"]} == _lib.DTYPE_CODE
+    flags = [v for k, v in enum.items() if k.startswith("SMOE_FLAG_")]
+    assert len(set(flags)) == len(flags) and all(v & (v - 1) == 0 for v in flags), "flags are distinct single bits"
