@@ -4,21 +4,27 @@
 
 One "step" = routing bookkeeping (flatten_sort_count) + forward + backward (gradients w.r.t. the input, the
 gates and both expert weight tensors) of the layer on one batch of seeded synthetic tokens. Prints ONE JSON
-line. `value` is device-timed with the inputs resident in HBM; `e2e` repeats the measurement with the
-step's inputs copied from pinned host memory and its results copied back inside the timed region.
+line. `value` is device-timed with the inputs resident in HBM; `e2e` repeats the measurement with every step's
+inputs copied from pinned host memory and its results copied back inside the timed region; `forward` is the
+forward pass alone. `parity` compares, outside the timed regions, the outputs and gradients of one full-size step
+with the reference's own Triton kernels on the same GPU, weights and inputs, and a sample of token rows with an
+fp32 dense per-expert loop. `other_configs` (N = 1) carries short measurements of the remaining single-GPU
+workloads; `ep_config5` the expert-parallel workload at this N.
 
 N > 1 (launched by torch.distributed.run, one rank per GPU): expert parallel, strong scaling. The layer's experts
-are partitioned across the ranks, the workload's tokens are split evenly, and every step exchanges rows with two
-NCCL all-to-all-v's each way (scattermoe_b200.expert_parallel). Time is the max over ranks, `value` the global
-tokens per second. (The gpt-oss workload, whose block has biases and its own activation, is not expert-parallel
-here: its ranks run replicas on their own token shards, weak scaling.)
+are partitioned across the ranks, the workload's tokens are split evenly, and every step exchanges rows over
+NVLink peer memory (scattermoe_b200.expert_parallel). Time is the max over ranks, `value` the global tokens per
+second. (The gpt-oss workload, whose block has biases and its own activation, is not expert-parallel here: its
+ranks run replicas on their own token shards, weak scaling.)
 
 `--impl reference` times the reference's CPU path for the same layer (the dense per-expert PyTorch loop the
-reference's own test uses as ground truth) on the host cores, on a bounded sample of the tokens.
+reference's own test uses as ground truth) on the host cores, every step on a bounded sample of the tokens.
 """
 from __future__ import annotations
 
 import argparse
+import importlib
+import importlib.util
 import json
 import os
 import statistics
@@ -41,6 +47,17 @@ LAYERS = {
     "tiny": dict(T=256, d=128, F=256, E=8, k=2, kind="glu_silu", bias=False),
 }
 CPU_SAMPLE_TOKENS = {"mixtral_8x7b": 2048, "gpt_oss_20b": 2048, "granite_zipf": 8192, "qwen3_moe_ep": 8192, "tiny": 256}
+CPU_ARM_BUDGET_S = 240.0      # the whole `--impl reference` run (warm-up + steps) is sized to end within this
+METRIC = "moe_layer_fwd_bwd_tokens_per_s"
+
+# DRAM bytes per scatter2scatter launch (ncu: dram__bytes_read.sum + dram__bytes_write.sum, mean of the four launches
+# of one layer step). Not measured by this script: it is the figure of the last profiler capture, printed beside
+# the live numbers together with where it came from.
+NCU_TRAFFIC = {
+    "mixtral_8x7b": dict(bytes_per_launch=5.547e9,
+                         source="ncu capture of the four launches of one step at 8192 tokens, scaled to 16384 (the "
+                                "traffic grows with the rows); taken before the raster and fused-gradient changes"),
+}
 
 
 def load_peaks():
@@ -53,9 +70,41 @@ def load_peaks():
     return dict(hbm_gbs=6650.0, tflops_burst=1590.0, tflops_sustained=1400.0, source="fallback")
 
 
-# DRAM bytes per scatter2scatter launch (dram__bytes_read.sum + dram__bytes_write.sum, averaged over the four
-# launches of one step) from the ncu capture summarised in profiles/s2s_tc_kernel_mixtral_8x7b.md.
-NCU_TRAFFIC_PER_LAUNCH = {"mixtral_8x7b": 5.547e9}
+def load_reference_package():
+    """The unmodified reference, installed under baseline/_ref, imported under a name of its own
+    (`scattermoe_reference`) so that it can sit beside this repository's `scattermoe` alias package. Importing it
+    re-patches the Hugging Face MoE classes (that is what its utils/replace_moe.py does on import); the patches
+    that were in place are put back, and the reference's are kept in `PATCHED_FORWARDS` of the returned module."""
+    name = "scattermoe_reference"
+    if name in sys.modules:
+        return sys.modules[name]
+    pkg_dir = os.path.join(ROOT, "baseline", "_ref", "scattermoe")
+    init = os.path.join(pkg_dir, "__init__.py")
+    if not os.path.exists(init):
+        return None
+    hf = []
+    for modname, cls in (("transformers.models.gpt_oss.modeling_gpt_oss", "GptOssExperts"),
+                         ("transformers.models.granitemoehybrid.modeling_granitemoehybrid", "GraniteMoeHybridMoE")):
+        try:
+            c = getattr(importlib.import_module(modname), cls)
+            hf.append((c, c.forward))
+        except Exception:
+            pass
+    spec = importlib.util.spec_from_file_location(name, init, submodule_search_locations=[pkg_dir])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    try:
+        spec.loader.exec_module(mod)
+    except Exception:
+        sys.modules.pop(name, None)
+        raise
+    finally:
+        patched = {}
+        for c, fwd in hf:
+            patched[c.__name__] = c.forward
+            c.forward = fwd
+        mod.PATCHED_FORWARDS = patched
+    return mod
 
 
 def layer_flops(c, tokens):
@@ -82,9 +131,9 @@ def make_routing(cfg_name, T, E, k, seed):
 
 
 class ClockSampler:
-    """nvidia-smi sampling of SM clock and throttle reasons. The sampler is started before the warm-up (nvidia-smi
-    needs a moment to produce its first line) and only the samples whose timestamp falls inside the timed region
-    are kept."""
+    """nvidia-smi sampling of SM clock and throttle reasons (query only). The sampler is started before the warm-up
+    (nvidia-smi needs a moment to produce its first line) and only the samples whose timestamp falls inside the
+    timed region are kept."""
     Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -193,33 +242,39 @@ def build_layer(name, c, tokens, device, seed, ep_world=1, exchange="nvlink", ch
     return layer, host
 
 
-def run_step(c, layer, x, p, idx, dy):
-    """One forward + backward through the public API. Returns (y, dx)."""
+def layer_leaves(c, layer):
+    if c["kind"] == "gpt_oss":
+        return [layer["w1"], layer["w2"], layer["b1"], layer["b2"]]
+    m = layer["module"]
+    return [m.experts.weight, m.output_experts.weight]
+
+
+def forward_only(c, layer, x, p, idx):
     import scattermoe_b200 as sm
+    if c["kind"] == "gpt_oss":
+        from scattermoe_b200 import activation as A
+        routing = sm.flatten_sort_count(idx, c["E"])
+        return sm.expert_mlp(x, layer["w1"], layer["w2"], p, c["k"], *routing, A.LAYOUT_GPT_OSS, A.ACT_SILU,
+                             up_biases=layer["b1"], down_biases=layer["b2"], alpha=1.702, limit=7.0)
+    return layer["module"](x, p, idx)
+
+
+def run_step(c, layer, x, p, idx, dy):
+    """One forward + backward through the public API. Returns (y, [dx, dgates, weight / bias gradients ...])."""
     x = x.requires_grad_()
     p = p.requires_grad_()
-    if c["kind"] == "gpt_oss":
-        from scattermoe_b200.utils.replace_moe import gpt_oss_glu
-        routing = sm.flatten_sort_count(idx, c["E"])
-        from scattermoe_b200 import activation as A
-        h = sm.parallel_linear_act(x, layer["w1"], c["k"], *routing, A.LAYOUT_GPT_OSS, A.ACT_SILU,
-                                   expert_biases=layer["b1"], alpha=1.702, limit=7.0)
-        y = sm.parallel_linear(h, layer["w2"], 1, *routing, expert_biases=layer["b2"], grouped_in=True, gates=p)
-        leaves = [x, p, layer["w1"], layer["w2"], layer["b1"], layer["b2"]]
-    else:
-        m = layer["module"]
-        y = m(x, p, idx)
-        leaves = [x, p, m.experts.weight, m.output_experts.weight]
-    grads = torch.autograd.grad(y, leaves, dy)
-    return y, grads[0]
+    y = forward_only(c, layer, x, p, idx)
+    grads = torch.autograd.grad(y, [x, p] + layer_leaves(c, layer), dy)
+    return y, list(grads)
 
 
 class LaunchCounter:
     """Counts the kernels this library launches: a proxy in front of the ctypes library that knows how many
     kernels each C entry point enqueues."""
-    KERNELS = {"smoe_scatter2scatter_act": 1, "smoe_ep_dispatch": 1, "smoe_ep_return": 1, "smoe_ep_barrier": 1, "smoe_sort_count": 3, "smoe_sort_count_static": 3, "smoe_offsets_from_sorted": 1,
-               "smoe_scatter2scatter": 1, "smoe_group_bwd_w": 1, "smoe_group": 1, "smoe_topk_reduce": 1,
-               "smoe_gate_grad": 1, "smoe_activation_forward": 1, "smoe_activation_backward": 1}
+    KERNELS = {"smoe_scatter2scatter_act": 1, "smoe_scatter2scatter_act_bwd": 1, "smoe_ep_dispatch": 1,
+               "smoe_ep_return": 1, "smoe_ep_barrier": 1, "smoe_sort_count": 3, "smoe_sort_count_static": 3,
+               "smoe_offsets_from_sorted": 1, "smoe_scatter2scatter": 1, "smoe_group_bwd_w": 1, "smoe_group": 1,
+               "smoe_topk_reduce": 1, "smoe_gate_grad": 1, "smoe_activation_forward": 1, "smoe_activation_backward": 1}
 
     def __init__(self):
         from scattermoe_b200 import _lib
@@ -250,6 +305,9 @@ class LaunchCounter:
             out[name] = out.get(name, 0.0) + a.elapsed_time(z)
         return out
 
+    def reset(self):
+        self.count, self.events = 0, []
+
     def install(self):
         self._mod._lib = self
 
@@ -265,36 +323,52 @@ class KernelTimer:
 
     def install(self):
         from scattermoe_b200.kernels import ops
-        self._s2s, self._wg, self._s2sa = ops._scatter2scatter_impl, ops._group_bwd_w_impl, ops.scatter2scatter_act
+        self._saved = (ops._scatter2scatter_impl, ops._group_bwd_w_impl, ops.scatter2scatter_act,
+                       ops._scatter2scatter_act_bwd_impl)
         timer = self
+        _s2s, _wg, _s2sa, _s2sb = self._saved
+
+        def bracket():
+            return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
         def s2sa(X, W, se, ss, k, *a, **kw):
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0, e1 = bracket()
             e0.record()
-            res = timer._s2sa(X, W, se, ss, k, *a, **kw)
+            res = _s2sa(X, W, se, ss, k, *a, **kw)
             e1.record()
             if res is not None:
                 timer.records.append(("scatter2scatter", 2.0 * se.numel() * X.size(1) * W.size(-1), e0, e1))
             return res
 
+        def s2sb(d_up, DY, W, up, *a):
+            e0, e1 = bracket()
+            e0.record()
+            ok = _s2sb(d_up, DY, W, up, *a)
+            e1.record()
+            if ok:
+                timer.records.append(("scatter2scatter", 2.0 * DY.size(0) * DY.size(1) * W.size(-1), e0, e1))
+            return ok
+
         def s2s(output, W, X, k, se, ss, b, xg, yg, off):
-            a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            timer._s2s(output, W, X, k, se, ss, b, xg, yg, off)
-            z.record()
-            timer.records.append(("scatter2scatter", 2.0 * se.numel() * X.size(1) * output.size(1), a, z))
+            e0, e1 = bracket()
+            e0.record()
+            _s2s(output, W, X, k, se, ss, b, xg, yg, off)
+            e1.record()
+            timer.records.append(("scatter2scatter", 2.0 * se.numel() * X.size(1) * output.size(1), e0, e1))
 
         def wg(E, DW, Db, DY, X, off, gi, fan):
-            a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            timer._wg(E, DW, Db, DY, X, off, gi, fan)
-            z.record()
-            timer.records.append(("group_bwd_w", 2.0 * DY.size(0) * X.size(1) * DY.size(1), a, z))
+            e0, e1 = bracket()
+            e0.record()
+            _wg(E, DW, Db, DY, X, off, gi, fan)
+            e1.record()
+            timer.records.append(("group_bwd_w", 2.0 * DY.size(0) * X.size(1) * DY.size(1), e0, e1))
         ops._scatter2scatter_impl, ops._group_bwd_w_impl, ops.scatter2scatter_act = s2s, wg, s2sa
+        ops._scatter2scatter_act_bwd_impl = s2sb
 
     def remove(self):
         from scattermoe_b200.kernels import ops
-        ops._scatter2scatter_impl, ops._group_bwd_w_impl, ops.scatter2scatter_act = self._s2s, self._wg, self._s2sa
+        (ops._scatter2scatter_impl, ops._group_bwd_w_impl, ops.scatter2scatter_act,
+         ops._scatter2scatter_act_bwd_impl) = self._saved
 
     def summary(self):
         out = {}
@@ -306,24 +380,24 @@ class KernelTimer:
         return out
 
 
-def time_reference_triton(name, c, host, device, iters=5, warmup=3):
-    """The reference's own Triton kernels (installed copy under baseline/_ref) on the same layer and GPU."""
-    ref_dir = os.path.join(ROOT, "baseline", "_ref")
-    if not os.path.isdir(os.path.join(ref_dir, "scattermoe")):
-        return None
-    sys.path.insert(0, ref_dir)
-    try:
-        import scattermoe as ref
-        bf = torch.bfloat16
+# ---- the reference's own Triton kernels on the same GPU ------------------------------------------------------
+
+class TritonReference:
+    """The unmodified reference from baseline/_ref through its own public API (`GLUMLP`, or the call sequence of its
+    patched GptOssExperts.forward, utils/replace_moe.py:22-55), with THIS benchmark's weights and inputs."""
+
+    def __init__(self, name, c, layer, host, device):
+        self.ref = load_reference_package()
+        if self.ref is None:
+            raise RuntimeError("baseline/_ref holds no installed copy of the reference")
+        ref, bf = self.ref, torch.bfloat16
         d, F, E, k = c["d"], c["F"], c["E"], c["k"]
-        x, p, idx, dy = (host[n].to(device) for n in ("x", "p", "idx", "dy"))
+        self.c = c
+        self.x, self.p, self.idx, self.dy = (host[n].to(device) for n in ("x", "p", "idx", "dy"))
+        idx = self.idx
         if c["kind"] == "gpt_oss":
-            # the call sequence of the reference's patched GptOssExperts.forward (utils/replace_moe.py:22-55)
-            w1 = torch.empty(E, d, 2 * F, dtype=bf, device=device).normal_(0, 0.02).requires_grad_()
-            w2 = torch.empty(E, F, d, dtype=bf, device=device).normal_(0, 0.02).requires_grad_()
-            b1 = torch.empty(E, 2 * F, dtype=bf, device=device).normal_(0, 0.02).requires_grad_()
-            b2 = torch.empty(E, d, dtype=bf, device=device).normal_(0, 0.02).requires_grad_()
-            leaves_w = [w1, w2, b1, b2]
+            w1, w2, b1, b2 = (layer[n].detach().clone().requires_grad_() for n in ("w1", "w2", "b1", "b2"))
+            self.leaves = [w1, w2, b1, b2]
 
             def fwd(xx, pp):
                 routing = ref.flatten_sort_count(idx.flatten(), num_experts=E)
@@ -336,41 +410,245 @@ def time_reference_triton(name, c, host, device, iters=5, warmup=3):
                                            gates=pp)
         else:
             m = ref.mlp.GLUMLP(d, F, E, k).to(device=device, dtype=bf)
-            leaves_w = [m.experts.weight, m.output_experts.weight]
+            with torch.no_grad():
+                m.experts.weight.copy_(layer["module"].experts.weight)
+                m.output_experts.weight.copy_(layer["module"].output_experts.weight)
+            self.leaves = [m.experts.weight, m.output_experts.weight]
 
             def fwd(xx, pp):
                 return m(xx, pp, idx)
+        self.fwd = fwd
 
-        def step():
-            xx, pp = x.detach().requires_grad_(), p.detach().requires_grad_()
-            torch.autograd.grad(fwd(xx, pp), [xx, pp] + leaves_w, dy)
-        for _ in range(warmup):
-            step()
-        torch.cuda.synchronize()
-        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(iters):
-            step()
-        z.record()
-        torch.cuda.synchronize()
-        ms = a.elapsed_time(z) / iters
-        del leaves_w
-        torch.cuda.empty_cache()
-        return {"impl": "reference Triton kernels, same GPU, same inputs", "ms_per_step": ms,
-                "value": x.size(0) / (ms / 1e3), "unit": "tokens/s", "iters": iters}
-    except Exception as e:  # the comparison is informative; it must not break the benchmark line
-        return {"unavailable": "%s: %s" % (type(e).__name__, str(e)[:200])}
+    def forward(self):
+        return self.fwd(self.x.detach().requires_grad_(), self.p.detach().requires_grad_())
+
+    def step(self):
+        xx, pp = self.x.detach().requires_grad_(), self.p.detach().requires_grad_()
+        y = self.fwd(xx, pp)
+        return y, list(torch.autograd.grad(y, [xx, pp] + self.leaves, self.dy))
+
+    def routing(self):
+        return self.ref.flatten_sort_count(self.idx.flatten(), num_experts=self.c["E"])
+
+    def time(self, iters=5, warmup=3):
+        out = {}
+        for key, fn in (("ms_per_step", self.step), ("forward_ms", self.forward)):
+            for _ in range(warmup):
+                fn()
+            torch.cuda.synchronize()
+            a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                fn()
+            z.record()
+            torch.cuda.synchronize()
+            out[key] = a.elapsed_time(z) / iters
+        T = self.x.size(0)
+        return {"impl": "reference Triton kernels (unmodified, baseline/_ref), same GPU, same weights and inputs",
+                "ms_per_step": out["ms_per_step"], "value": T / (out["ms_per_step"] / 1e3), "unit": "tokens/s",
+                "forward_ms": out["forward_ms"], "forward_value": T / (out["forward_ms"] / 1e3), "iters": iters}
+
+
+# ---- parity, outside the timed regions ------------------------------------------------------------------------
+
+RTOL, ATOL = 2e-2, 2e-2          # the bf16 contract: outputs and gradients against the reference's own kernels
+MISMATCH_BUDGET = 1e-4           # fraction of elements allowed outside it (two bf16 runs that round intermediates at
+#                                  different places disagree by one bf16 step on a few elements next to zero)
+
+
+def _compare(got, want, scale=None):
+    """|got - want| <= ATOL + RTOL * |want| elementwise, after dividing both by `scale` (a tensor or number) when
+    the quantity is a long sum whose rounding error grows with the square root of its length."""
+    got, want = got.detach().float(), want.detach().float()
+    if scale is not None:
+        got, want = got / scale, want / scale
+    diff = (got - want).abs()
+    bad = diff > (ATOL + RTOL * want.abs())
+    n = max(diff.numel(), 1)
+    frac = float(bad.sum().item()) / n
+    return {"max_abs": float(diff.max().item()) if diff.numel() else 0.0, "mismatch_frac": frac,
+            "ok": bool(frac <= MISMATCH_BUDGET and bool(torch.isfinite(got).all()))}
+
+
+def dense_loop_rows(c, layer, x, p, idx, dy, rows):
+    """fp32 dense per-expert loop (plain PyTorch, TF32 off) for a sample of token rows: y, dx, dgates of those rows.
+    Every quantity of a token depends on that token and the weights alone, so a row sample checks the full-size
+    run. Restates the reference test's ground truth (tests/test_mlp.py:10-26) per expert."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        xs = x[rows].float().requires_grad_()
+        ps = p[rows].float().requires_grad_()
+        ids = idx[rows]
+        F = c["F"]
+        y = torch.zeros_like(xs)
+        for e in ids.unique().tolist():
+            tok, slot = (ids == e).nonzero(as_tuple=True)
+            if c["kind"] == "gpt_oss":
+                w1, w2 = layer["w1"][e].detach().float(), layer["w2"][e].detach().float()          # (in, out)
+                up = xs[tok] @ w1 + layer["b1"][e].detach().float()
+                gate, lin = up[:, ::2].clamp(max=7.0), up[:, 1::2].clamp(-7.0, 7.0)
+                h = (lin + 1) * (gate * torch.sigmoid(gate * 1.702))
+                out = h @ w2 + layer["b2"][e].detach().float()
+            else:
+                m = layer["module"]
+                up = xs[tok] @ m.experts.weight[e].detach().float().t()
+                h = torch.nn.functional.silu(up[:, F:]) * up[:, :F]              # second half activated (mlp.py:81-87)
+                out = h @ m.output_experts.weight[e].detach().float().t()
+            y = y.index_add(0, tok, out * ps[tok, slot].unsqueeze(1))
+        dx, dp = torch.autograd.grad(y, [xs, ps], dy[rows].float())
+        return y.detach(), dx, dp
     finally:
-        sys.path.remove(ref_dir)
+        torch.backends.cuda.matmul.allow_tf32 = prev
 
 
-def cpu_reference(name, c, steps, warmup):
+def parity_check(name, c, layer, dev_in, triton_ref, sample_rows=256):
+    """One more full-size step of this library, compared with (a) the reference's Triton kernels on the same
+    weights and inputs and (b) the fp32 dense loop on a sample of token rows."""
+    import scattermoe_b200 as sm
+    out = {"rtol": RTOL, "atol": ATOL, "mismatch_budget": MISMATCH_BUDGET}
+    x, p, idx, dy = dev_in["x"], dev_in["p"], dev_in["idx"], dev_in["dy"]
+    y, grads = run_step(c, layer, x.detach(), p.detach(), idx, dy)
+    sm.check_device_status(x.device)
+    T, d, E = x.size(0), c["d"], c["E"]
+    root_rows = torch.bincount(idx.flatten(), minlength=E).clamp(min=1).float().sqrt()
+    names = ["dx", "dgates", "dw1", "dw2", "db1", "db2"][:len(grads)]
+    ok = True
+    if triton_ref is not None:
+        se, ss, off = sm.flatten_sort_count(idx, E)
+        rse, rss, roff = triton_ref.routing()
+        routing = {"sorted_expert_idxs_equal": bool(torch.equal(se, rse)),
+                   "expert_offsets_equal": bool(torch.equal(off, roff)),
+                   "sorted_scattered_idxs_equal": bool(torch.equal(ss, rss))}
+        if not routing["sorted_scattered_idxs_equal"]:
+            # torch.sort without stable=True may order ties differently: then the orders must agree per expert as sets
+            same, start = True, 0
+            for end in off.tolist():
+                same = same and torch.equal(torch.sort(ss[start:end]).values, torch.sort(rss[start:end]).values)
+                start = end
+            routing["sorted_scattered_idxs_equal_per_expert_as_sets"] = bool(same)
+            ok = ok and same
+        ok = ok and routing["sorted_expert_idxs_equal"] and routing["expert_offsets_equal"]
+        ry, rgrads = triton_ref.step()
+        q = {"y": _compare(y, ry)}
+        for n, g, rg in zip(names, grads, rgrads):
+            scale = None
+            if n == "dgates":
+                scale = float(d) ** 0.5                       # a dot product of d_model bf16 products
+            elif n in ("dw1", "dw2"):
+                scale = root_rows.view(E, 1, 1)               # sums over the expert's rows
+            elif n in ("db1", "db2"):
+                scale = root_rows.view(E, 1)
+            if n in ("dw1", "dw2") and g.numel() > (1 << 28):
+                # a sample of (expert, row-band) blocks of the big weight gradients keeps the check cheap
+                sel = torch.arange(0, g.size(1), max(1, g.size(1) // 64), device=g.device)
+                q[n] = _compare(g[:, sel], rg[:, sel], scale)
+                q[n]["sampled_rows_per_expert"] = int(sel.numel())
+            else:
+                q[n] = _compare(g, rg, scale)
+        out["vs_reference_gpu"] = {"ok": all(v["ok"] for v in q.values()), "quantities": q, "routing": routing,
+                                   "scales": "dgates / sqrt(d_model); dw, db / sqrt(rows of the expert): sums of n "
+                                             "bf16-rounded products differ between two correct bf16 runs by about "
+                                             "2^-8 * sqrt(n) * rms(term); y and dx unscaled"}
+        ok = ok and out["vs_reference_gpu"]["ok"]
+        del ry, rgrads
+    else:
+        out["vs_reference_gpu"] = None
+    # (b) fp32 dense loop on sampled token rows
+    g = torch.Generator().manual_seed(1)
+    rows = torch.randperm(T, generator=g)[:min(sample_rows, T)].to(x.device)
+    ty, tdx, tdp = dense_loop_rows(c, layer, x, p, idx, dy, rows)
+
+    def rms(a, b):
+        return float((a.float() - b).pow(2).mean().sqrt().item())
+    ours = {"y": rms(y[rows], ty), "dx": rms(grads[0][rows], tdx), "dgates": rms(grads[1][rows], tdp)}
+    dl = {"tokens": int(rows.numel()), "ours_rms_err": ours,
+          "truth_rms": {"y": float(ty.pow(2).mean().sqrt()), "dx": float(tdx.pow(2).mean().sqrt()),
+                        "dgates": float(tdp.pow(2).mean().sqrt())}}
+    # an rms error within 2 % (the contract's rtol) of the rms of the quantity passes
+    dl["ok"] = all(ours[n] <= RTOL * dl["truth_rms"][n] + 1e-6 for n in ours)
+    if triton_ref is not None:
+        ry, rgrads = triton_ref.step()
+        dl["reference_rms_err"] = {"y": rms(ry[rows], ty), "dx": rms(rgrads[0][rows], tdx),
+                                   "dgates": rms(rgrads[1][rows], tdp)}
+        del ry, rgrads
+    out["vs_dense_loop"] = dl
+    ok = ok and dl["ok"]
+    mx = [v["max_abs"] for v in (out["vs_reference_gpu"] or {}).get("quantities", {}).values()]
+    out["max_abs"] = max(mx) if mx else None
+    out["ok"] = bool(ok)
+    del y, grads
+    torch.cuda.empty_cache()
+    return out
+
+
+def ep_parity_check(device, rank, world, dist, exchange, chunks):
+    """N > 1: one small seeded expert-parallel step; every rank compares its outputs and gradient slices with the
+    single-GPU layer on the gathered problem (same seed on every rank, so nothing needs gathering)."""
+    import scattermoe_b200 as sm
+    from scattermoe_b200.expert_parallel import ExpertParallelGLUMLP, PeerExpertParallelGLUMLP
+    T, d, F, E, k = 1024 * world, 512, 256, 8 * world, 4
+    g = torch.Generator().manual_seed(123)
+    bf = torch.bfloat16
+    x = torch.randn(T, d, generator=g).to(bf).to(device)
+    p, idx = torch.topk(torch.softmax(torch.randn(T, E, generator=g), -1), k)
+    p = (p / p.sum(-1, keepdim=True)).to(bf).to(device)
+    idx = idx.to(device)
+    w1 = (torch.randn(E, 2 * F, d, generator=g) * 0.05).to(bf).to(device)
+    w2 = (torch.randn(E, d, F, generator=g) * 0.05).to(bf).to(device)
+    dy = torch.randn(T, d, generator=g).to(bf).to(device)
+    single = sm.mlp.GLUMLP(d, F, E, k).to(device=device, dtype=bf)
+    with torch.no_grad():
+        single.experts.weight.copy_(w1)
+        single.output_experts.weight.copy_(w2)
+    xs, ps = x.clone().requires_grad_(), p.clone().requires_grad_()
+    want_y = single(xs, ps, idx)
+    want = [want_y] + list(torch.autograd.grad(want_y, [xs, ps, single.experts.weight, single.output_experts.weight], dy))
+    tl, el = T // world, E // world
+    ts, es = slice(rank * tl, (rank + 1) * tl), slice(rank * el, (rank + 1) * el)
+    if exchange == "nvlink":
+        m = PeerExpertParallelGLUMLP(d, F, E, k, chunks=chunks).to(device=device, dtype=bf)
+    else:
+        m = ExpertParallelGLUMLP(d, F, E, k).to(device=device, dtype=bf)
+    with torch.no_grad():
+        m.experts.weight.copy_(w1[es])
+        m.output_experts.weight.copy_(w2[es])
+    xx, pp = x[ts].clone().requires_grad_(), p[ts].clone().requires_grad_()
+    for _ in range(2):
+        y = m(xx, pp, idx[ts])
+        got = [y] + list(torch.autograd.grad(y, [xx, pp, m.experts.weight, m.output_experts.weight], dy[ts]))
+    sm.check_device_status(device)
+    rows = torch.bincount(idx.flatten(), minlength=E).clamp(min=1).float().sqrt().to(device)
+    res = {"y": _compare(got[0], want[0][ts]), "dx": _compare(got[1], want[1][ts]),
+           "dgates": _compare(got[2], want[2][ts], float(d) ** 0.5),
+           "dw1": _compare(got[3], want[3][es], rows[es].view(-1, 1, 1)),
+           "dw2": _compare(got[4], want[4][es], rows[es].view(-1, 1, 1))}
+    worst = torch.tensor([max(v["max_abs"] for v in res.values()), 0.0 if all(v["ok"] for v in res.values()) else 1.0],
+                         device=device)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    del m
+    torch.cuda.empty_cache()
+    return {"against": "single-GPU GLUMLP of this library on the gathered problem (T=%d, d=%d, F=%d, E=%d, k=%d)"
+                       % (T, d, F, E, k), "max_err": float(worst[0].item()), "ok": bool(worst[1].item() == 0.0),
+            "rtol": RTOL, "atol": ATOL, "rank0": res}
+
+
+# ---- the reference's CPU path ---------------------------------------------------------------------------------
+
+def cpu_reference(name, c, steps, warmup, budget_s=None):
+    """Dense per-expert fp32 loop on all host cores, `steps` timed steps after `warmup` on a token sample. With a
+    time budget the sample shrinks (after a first probing step) so that the whole run ends within it."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import scattermoe_oracle as oracle
     tokens = min(CPU_SAMPLE_TOKENS.get(name, 1024), c["T"])
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    b = oracle.DenseLoopBench(name if name in oracle.CONFIGS else "tiny_fp32_gelu", tokens, threads=cores)
+    cfg = name if name in oracle.CONFIGS else "tiny_fp32_gelu"
+    b = oracle.DenseLoopBench(cfg, tokens, threads=cores)
+    probe = b.step()
+    if budget_s is not None and probe * (steps + warmup) > budget_s and tokens > 256:
+        tokens = max(256, int(tokens * budget_s / (probe * (steps + warmup))) // 256 * 256)
+        b = oracle.DenseLoopBench(cfg, tokens, threads=cores)
     threads = b.threads
     times = []
     for i in range(warmup + steps):
@@ -379,8 +657,216 @@ def cpu_reference(name, c, steps, warmup):
             times.append(t)
     sec = sum(times) / len(times)
     return dict(value=tokens / sec, unit="tokens/s", cores=threads, kind="port",
-                sample="%d of %d tokens per step, fp32 dense per-expert loop, forward+backward, %.2f s/step"
-                       % (tokens, c["T"], sec)), sec
+                sample="%d of %d tokens per step, fp32 dense per-expert loop, forward+backward, %.2f s/step, %d timed "
+                       "steps" % (tokens, c["T"], sec, len(times))), sec, tokens
+
+
+# ---- one workload on this process's GPU -----------------------------------------------------------------------
+
+def measure(name, c, device, rank, world, dist, steps, warmup, with_e2e=True, sampler_gpu=None, exchange="nvlink",
+            chunks=1, keep=False):
+    """Device-timed forward+backward (and forward, and end-to-end) of one workload. Returns (fields, state)."""
+    import scattermoe_b200 as sm
+    peaks = load_peaks()
+    ep = world > 1 and c["kind"] != "gpt_oss"
+    tokens_local = c["T"] // world if ep else c["T"]
+    tokens_all = c["T"] if ep else c["T"] * world
+    layer, host = build_layer(name, c, tokens_local, device, seed=rank, ep_world=world if ep else 1, exchange=exchange,
+                             chunks=chunks)
+    dev_in = {n: t.to(device) for n, t in host.items()}
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def resident_step():
+        return run_step(c, layer, dev_in["x"].detach(), dev_in["p"].detach(), dev_in["idx"], dev_in["dy"])
+
+    def forward_step():
+        return forward_only(c, layer, dev_in["x"].detach().requires_grad_(), dev_in["p"].detach().requires_grad_(),
+                            dev_in["idx"])
+
+    out_host = dict(y=torch.empty_like(host["x"]).pin_memory(), dx=torch.empty_like(host["x"]).pin_memory())
+    copy_stream = torch.cuda.Stream(device=device)
+    staged = {}
+
+    def stage_inputs():
+        """Enqueue the host->device copies of one step's inputs on the copy stream."""
+        with torch.cuda.stream(copy_stream):
+            staged["in"] = {n: host[n].to(device, non_blocking=True) for n in ("x", "p", "idx", "dy")}
+            staged["ready"] = torch.cuda.Event()
+            staged["ready"].record(copy_stream)
+
+    def e2e_step(prefetch):
+        # Every step copies its own inputs from pinned host memory and its results back. The copies run on a
+        # second stream: the next step's inputs are enqueued while this step computes, and this step's results
+        # travel back while the next step computes.
+        cur = torch.cuda.current_stream(device)
+        cur.wait_event(staged["ready"])
+        ins = staged.pop("in")
+        for t in ins.values():
+            t.record_stream(cur)
+        if prefetch:
+            stage_inputs()
+        y, grads = run_step(c, layer, ins["x"], ins["p"], ins["idx"], ins["dy"])
+        dx = grads[0]
+        done = torch.cuda.Event()
+        done.record(cur)
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(done)
+            y.record_stream(copy_stream)
+            dx.record_stream(copy_stream)
+            out_host["y"].copy_(y, non_blocking=True)
+            out_host["dx"].copy_(dx, non_blocking=True)
+
+    def e2e_loop(n):
+        # Nothing is staged before the loop starts (the first step's host->device copy is not hidden) and the
+        # last step's device->host copy is joined before it ends: every copy lies inside the timed bracket.
+        staged.clear()
+        stage_inputs()
+        for i in range(n):
+            e2e_step(prefetch=(i + 1 < n))
+        torch.cuda.current_stream(device).wait_stream(copy_stream)
+
+    def timed(fn, n):
+        barrier()
+        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn(n)
+        z.record()
+        barrier()
+        ms = a.elapsed_time(z)
+        if dist is not None:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = t.item()
+        return ms
+
+    def loop(fn):
+        def run(n):
+            for _ in range(n):
+                fn()
+        return run
+
+    sampler = ClockSampler(sampler_gpu) if (rank == 0 and sampler_gpu is not None) else None
+    if sampler:
+        sampler.start()
+    for _ in range(warmup):
+        resident_step()
+    sm.check_device_status(device)
+    timer = KernelTimer()
+    timer.install()
+    counter = LaunchCounter()
+    counter.install()
+    BAD = {"hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown"}
+    remeasured = False
+    clocks = None
+    try:
+        while True:
+            if sampler:
+                sampler.mark_begin()
+            ms_total = timed(loop(resident_step), steps)
+            if sampler:
+                sampler.mark_end()
+            clocks = sampler.stop() if sampler else None
+            bad = bool(clocks and BAD & set(clocks.get("reasons", [])))
+            if world > 1:      # every rank must take the same decision
+                flag = torch.tensor([1 if bad else 0], device=device)
+                dist.broadcast(flag, src=0)
+                bad = bool(flag.item())
+            if not bad or remeasured or sampler_gpu is None:
+                break
+            # a thermal / hardware slowdown was active during the timed region: the number is rejected and taken once more
+            remeasured = True
+            timer.records.clear()
+            counter.reset()
+            if rank == 0:
+                sampler = ClockSampler(sampler_gpu)
+                sampler.start()
+                time.sleep(0.3)
+        if clocks is not None:
+            clocks["remeasured_after_slowdown"] = remeasured
+        launches = counter.count
+        abi_ms = {k_: round(v_ / steps, 4) for k_, v_ in sorted(counter.ms_by_entry_point().items())}
+    finally:
+        counter.remove()
+        timer.remove()
+    ksum = timer.summary()
+    mod = layer.get("module")
+    if hasattr(mod, "live_row_fraction"):
+        # peer-memory expert parallelism launches its GEMMs over worst-case-sized buffers; count the live rows only
+        live = mod.live_row_fraction()
+        for d_ in ksum.values():
+            d_["flops"] *= live
+    tensor_core = sm.kernels.ops.last_path_was_tensor_core()
+
+    for _ in range(2):
+        forward_step()
+    ms_fwd = timed(loop(forward_step), steps)
+
+    ms_e2e = None
+    if with_e2e:
+        e2e_loop(2)
+        ms_e2e = timed(e2e_loop, steps)
+    sm.check_device_status(device)
+
+    ms_step = ms_total / steps
+    fwd_flops, fb_flops = layer_flops(c, tokens_all)
+    peak = peaks["tflops_sustained"]
+    dom = ksum.get("scatter2scatter", dict(launches=0, ms=0.0, flops=0.0))
+    achieved = dom["flops"] / (dom["ms"] / 1e3) / 1e12 if dom["ms"] > 0 else 0.0
+    traffic = NCU_TRAFFIC.get(name) if world == 1 else None
+    roofline = {"bound": "tensor",
+                "kernel": "s2s_tc_kernel (scatter2scatter: 2 forward + 2 input-gradient launches per step)",
+                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_source": "%s, sustained bf16 (kernel timed inside a long step)" % peaks["source"],
+                "launches": dom["launches"], "avg_launch_ms": dom["ms"] / max(dom["launches"], 1),
+                "traffic": traffic["bytes_per_launch"] if traffic else None,
+                "traffic_source": traffic["source"] if traffic else None}
+    wg = ksum.get("group_bwd_w")
+    if wg and wg["ms"] > 0:
+        roofline["group_bwd_w"] = {"achieved": wg["flops"] / (wg["ms"] / 1e3) / 1e12, "launches": wg["launches"],
+                                   "avg_launch_ms": wg["ms"] / wg["launches"],
+                                   "frac": wg["flops"] / (wg["ms"] / 1e3) / 1e12 / peak}
+    fields = {
+        "value": tokens_all / (ms_step / 1e3), "ms_per_step": ms_step,
+        "layer_tflops": fb_flops / (ms_step / 1e3) / 1e12,
+        "layer_frac_of_bf16_peak": fb_flops / world / (ms_step / 1e3) / 1e12 / peak,
+        "tensor_core_path": bool(tensor_core),
+        "roofline": roofline,
+        "forward": {"value": tokens_all / (ms_fwd / steps / 1e3), "unit": "tokens/s", "ms_per_step": ms_fwd / steps,
+                    "frac_of_bf16_peak": fwd_flops / world / (ms_fwd / steps / 1e3) / 1e12 / peak,
+                    "what": "the training forward alone (autograd on, tensors for backward saved)"},
+        # kernels of this library launched by this rank inside the timed region (counted at the C-ABI boundary)
+        "gpu_launches": launches,
+        # device time between the events bracketing each C-ABI call, summed over the timed region, per step
+        "abi_ms_per_step": abi_ms,
+        "clocks": clocks,
+    }
+    if ms_e2e is not None:
+        h2d = sum(host[n].numel() * host[n].element_size() for n in ("x", "p", "idx", "dy"))
+        d2h = sum(t.numel() * t.element_size() for t in out_host.values())
+        fields["e2e"] = {"value": tokens_all / (ms_e2e / steps / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                         "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / steps}
+    staged.clear()
+    state = dict(tokens_all=tokens_all, tokens_local=tokens_local, ep=ep)
+    if keep:
+        state.update(layer=layer, host=host, dev_in=dev_in)
+    else:
+        del layer, host, dev_in, out_host
+        torch.cuda.empty_cache()
+    return fields, state
+
+
+def describe(name, c, world, ep, exchange, tokens_all, tokens_local):
+    return {"workload": name, "global_tokens": tokens_all, "tokens_per_gpu": tokens_local, "d_model": c["d"],
+            "d_ffn": c["F"], "experts": c["E"], "experts_per_gpu": c["E"] // world if ep else c["E"],
+            "top_k": c["k"], "activation": c["kind"], "bias": c["bias"],
+            "parallelism": ("ep%d: experts partitioned, %s dispatch/combine"
+                            % (world, "NVLink peer-memory" if exchange == "nvlink" else "NCCL all-to-all-v")) if ep
+            else ("single GPU" if world == 1 else "replicas on token shards"),
+            "l2": "weights and activations exceed L2 (126 MB) every step"}
 
 
 def main():
@@ -396,6 +882,9 @@ def main():
                     help="pipeline chunks of the NVLink exchange (each chunk's transfers overlap the other's GEMMs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-triton-ref", action="store_true")
+    ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--no-other-configs", action="store_true",
+                    help="skip the short measurements of the other workloads (other_configs / ep_config5)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -403,28 +892,23 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     name, c = args.config, LAYERS[args.config]
-    metric = "moe_layer_fwd_bwd_tokens_per_s"
     ep = world > 1 and c["kind"] != "gpt_oss"
     if ep and (c["E"] % world or c["T"] % world):
         raise SystemExit("expert parallel needs the world size to divide E=%d and T=%d" % (c["E"], c["T"]))
-    tokens_local = c["T"] // world if ep else c["T"]
-    tokens_all = c["T"] if ep else c["T"] * world
     scaling = "weak" if (world > 1 and not ep) else "strong"
-    config = {"workload": name, "global_tokens": tokens_all, "tokens_per_gpu": tokens_local, "d_model": c["d"],
-              "d_ffn": c["F"], "experts": c["E"], "experts_per_gpu": c["E"] // world if ep else c["E"],
-              "top_k": c["k"], "activation": c["kind"], "bias": c["bias"],
-              "parallelism": ("ep%d: experts partitioned, %s dispatch/combine"
-                              % (world, "NVLink peer-memory" if args.exchange == "nvlink" else "NCCL all-to-all-v")) if ep
-              else ("single GPU" if world == 1 else "replicas on token shards"),
-              "l2": "weights and activations exceed L2 (126 MB) every step"}
 
     if args.impl == "reference":
         if rank != 0:
             return
-        base, sec = cpu_reference(name, c, max(1, min(args.steps, 3)), min(args.warmup, 1))
-        line = {"impl": "reference", "metric": metric, "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
-                "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+        steps, warmup = max(1, args.steps), max(0, args.warmup)
+        base, sec, sample = cpu_reference(name, c, steps, warmup, budget_s=CPU_ARM_BUDGET_S)
+        tokens_local = c["T"] // world if ep else c["T"]
+        tokens_all = c["T"] if ep else c["T"] * world
+        line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tokens/s", "n_gpus": args.gpus,
+                "steps": steps, "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+                "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": describe(name, c, world, ep, args.exchange, tokens_all, tokens_local),
+                "sampled": sample < c["T"], "sample_tokens": sample, "full_tokens": c["T"],
                 "cpu_baseline": base,
                 "e2e": {"value": base["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
@@ -439,164 +923,88 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
 
-    import scattermoe_b200 as sm
-    peaks = load_peaks()
-    layer, host = build_layer(name, c, tokens_local, device, seed=rank, ep_world=world if ep else 1,
-                             exchange=args.exchange, chunks=args.chunks)
-    dev_in = {n: t.to(device) for n, t in host.items()}
+    fields, st = measure(name, c, device, rank, world, dist, args.steps, args.warmup, with_e2e=True,
+                         sampler_gpu=local_rank, exchange=args.exchange, chunks=args.chunks, keep=(world == 1))
+    line = {"metric": METRIC, "value": fields.pop("value"), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": fields.pop("ms_per_step"), "higher_is_better": True,
+            "scaling": scaling, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": describe(name, c, world, st["ep"], args.exchange, st["tokens_all"], st["tokens_local"])}
+    line.update(fields)
+    failed = False
 
-    def barrier():
-        if dist is not None:
-            dist.barrier()
-        torch.cuda.synchronize()
+    if world == 1:
+        triton_ref = None
+        if not args.no_triton_ref:
+            try:
+                triton_ref = TritonReference(name, c, st["layer"], st["host"], device)
+                line["reference_gpu"] = triton_ref.time()
+            except Exception as e:  # the comparison is informative; it must not break the benchmark line
+                triton_ref = None
+                line["reference_gpu"] = {"unavailable": "%s: %s" % (type(e).__name__, str(e)[:200])}
+        if not args.no_parity:
+            line["parity"] = parity_check(name, c, st["layer"], st["dev_in"], triton_ref)
+            failed = failed or not line["parity"]["ok"]
+        del triton_ref
+        st.clear()
+        torch.cuda.empty_cache()
+    elif not args.no_parity and ep:
+        line["parity"] = ep_parity_check(device, rank, world, dist, args.exchange, args.chunks)
+        failed = failed or not line["parity"]["ok"]
 
-    def resident_step():
-        return run_step(c, layer, dev_in["x"].detach(), dev_in["p"].detach(), dev_in["idx"], dev_in["dy"])
-
-    out_host = dict(y=torch.empty_like(host["x"]).pin_memory(), dx=torch.empty_like(host["x"]).pin_memory())
-    copy_stream = torch.cuda.Stream(device=device)
-    staged = {}
-
-    def stage_inputs():
-        """Enqueue the host->device copies of one step's inputs on the copy stream."""
-        with torch.cuda.stream(copy_stream):
-            staged["in"] = {n: host[n].to(device, non_blocking=True) for n in ("x", "p", "idx", "dy")}
-            staged["ready"] = torch.cuda.Event()
-            staged["ready"].record(copy_stream)
-
-    def e2e_step():
-        # Every step copies its own inputs from pinned host memory and its results back. The copies run on a
-        # second stream: this step's inputs were enqueued while the previous step computed, and its results
-        # travel back while the next step computes.
-        if "in" not in staged:
-            stage_inputs()
-        cur = torch.cuda.current_stream(device)
-        cur.wait_event(staged["ready"])
-        ins = staged.pop("in")
-        for t in ins.values():
-            t.record_stream(cur)
-        stage_inputs()                       # next step's inputs, overlapping this step's compute
-        y, dx = run_step(c, layer, ins["x"], ins["p"], ins["idx"], ins["dy"])
-        done = torch.cuda.Event()
-        done.record(cur)
-        with torch.cuda.stream(copy_stream):
-            copy_stream.wait_event(done)
-            y.record_stream(copy_stream)
-            dx.record_stream(copy_stream)
-            out_host["y"].copy_(y, non_blocking=True)
-            out_host["dx"].copy_(dx, non_blocking=True)
-
-    def timed(fn, steps, timer=None):
-        barrier()
-        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(steps):
-            fn()
-        z.record()
-        barrier()
-        ms = a.elapsed_time(z)
-        if dist is not None:
-            t = torch.tensor([ms], device=device)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = t.item()
-        return ms
-
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    if sampler:
-        sampler.start()
-    for _ in range(args.warmup):
-        resident_step()
-    sm.check_device_status(device)
-    timer = KernelTimer()
-    timer.install()
-    counter = LaunchCounter()
-    counter.install()
-    BAD = {"hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown"}
-    remeasured = False
-    while True:
-        if sampler:
-            sampler.mark_begin()
-        ms_total = timed(resident_step, args.steps)
-        if sampler:
-            sampler.mark_end()
-        clocks = sampler.stop() if sampler else None
-        bad = bool(clocks and BAD & set(clocks.get("reasons", [])))
-        if world > 1:      # every rank must take the same decision
-            flag = torch.tensor([1 if bad else 0], device=device)
-            dist.broadcast(flag, src=0)
-            bad = bool(flag.item())
-        if not bad or remeasured:
-            break
-        # a thermal / hardware slowdown was active during the timed region: the number is rejected and taken once more
-        remeasured = True
-        timer.records.clear()
-        counter.count, counter.events = 0, []
-        if sampler:
-            sampler = ClockSampler(local_rank)
-            sampler.start()
-            time.sleep(0.3)
-    if clocks is not None:
-        clocks["remeasured_after_slowdown"] = remeasured
-    counter.remove()
-    timer.remove()
-    ksum = timer.summary()
-    mod = layer.get("module")
-    if hasattr(mod, "live_row_fraction"):
-        # peer-memory expert parallelism launches its GEMMs over worst-case-sized buffers; count the live rows only
-        live = mod.live_row_fraction()
-        for d_ in ksum.values():
-            d_["flops"] *= live
-    tensor_core = sm.kernels.ops.last_path_was_tensor_core()
-
-    for _ in range(2):
-        e2e_step()
-    ms_e2e = timed(e2e_step, args.steps)
-    sm.check_device_status(device)
+    if not args.no_other_configs and name == "mixtral_8x7b":
+        # the remaining workloads, short runs, so that the record of this run holds them too
+        short_steps, short_warm = min(args.steps, 6), 3
+        others = {}
+        for other in (("gpt_oss_20b", "granite_zipf", "qwen3_moe_ep") if world == 1 else ("qwen3_moe_ep",)):
+            oc = LAYERS[other]
+            if world > 1 and (oc["E"] % world or oc["T"] % world):
+                continue
+            try:
+                f, ost = measure(other, oc, device, rank, world, dist, short_steps, short_warm, with_e2e=(world > 1),
+                                 sampler_gpu=None, exchange=args.exchange, chunks=args.chunks, keep=(world == 1))
+                entry = {"ms_per_step": f["ms_per_step"], "value": f["value"], "unit": "tokens/s", "steps": short_steps,
+                         "warmup": short_warm, "layer_frac_of_bf16_peak": f["layer_frac_of_bf16_peak"],
+                         "forward_ms": f["forward"]["ms_per_step"], "abi_ms_per_step": f["abi_ms_per_step"],
+                         "roofline_frac": f["roofline"]["frac"],
+                         "config": describe(other, oc, world, ost["ep"], args.exchange, ost["tokens_all"],
+                                            ost["tokens_local"])}
+                if "e2e" in f:
+                    entry["e2e"] = f["e2e"]
+                if world == 1:
+                    if not args.no_triton_ref:
+                        try:
+                            tr = TritonReference(other, oc, ost["layer"], ost["host"], device)
+                            entry["reference_gpu"] = tr.time(iters=3, warmup=2)
+                            if not args.no_parity:
+                                entry["parity"] = parity_check(other, oc, ost["layer"], ost["dev_in"], tr)
+                                failed = failed or not entry["parity"]["ok"]
+                            del tr
+                        except Exception as e:
+                            entry["reference_gpu"] = {"unavailable": "%s: %s" % (type(e).__name__, str(e)[:200])}
+                    ost.clear()
+                    torch.cuda.empty_cache()
+                others[other] = entry
+            except Exception as e:
+                others[other] = {"failed": "%s: %s" % (type(e).__name__, str(e)[:300])}
+                failed = True
+        if "qwen3_moe_ep" in others:
+            # BASELINE config 5 at this N (the single-GPU layer at N = 1): the expert-parallel scaling curve
+            line["ep_config5"] = others.pop("qwen3_moe_ep")
+        if others:
+            line["other_configs"] = others
 
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
-
-    ms_step = ms_total / args.steps
-    value = tokens_all / (ms_step / 1e3)
-    fwd_flops, fb_flops = layer_flops(c, tokens_all)
-    h2d = sum(host[n].numel() * host[n].element_size() for n in ("x", "p", "idx", "dy"))
-    d2h = sum(t.numel() * t.element_size() for t in out_host.values())
-    dom = ksum.get("scatter2scatter", dict(launches=0, ms=0.0, flops=0.0))
-    achieved = dom["flops"] / (dom["ms"] / 1e3) / 1e12 if dom["ms"] > 0 else 0.0
-    peak = peaks["tflops_sustained"]
-    roofline = {"bound": "tensor", "kernel": "s2s_tc_kernel (scatter2scatter: 2 forward + 2 input-gradient launches per step)",
-                "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                "peak_source": "%s, sustained bf16 (kernel timed inside a long step)" % peaks["source"],
-                "launches": dom["launches"], "avg_launch_ms": dom["ms"] / max(dom["launches"], 1),
-                "traffic": NCU_TRAFFIC_PER_LAUNCH.get(name) if world == 1 else None}
-    wg = ksum.get("group_bwd_w")
-    if wg and wg["ms"] > 0:
-        roofline["group_bwd_w"] = {"achieved": wg["flops"] / (wg["ms"] / 1e3) / 1e12, "launches": wg["launches"],
-                                   "avg_launch_ms": wg["ms"] / wg["launches"],
-                                   "frac": wg["flops"] / (wg["ms"] / 1e3) / 1e12 / peak}
-    line = {"metric": metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": scaling,
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
-            "layer_tflops": fb_flops / (ms_step / 1e3) / 1e12,
-            "layer_frac_of_bf16_peak": fb_flops / world / (ms_step / 1e3) / 1e12 / peak,
-            "tensor_core_path": bool(tensor_core),
-            "roofline": roofline,
-            "e2e": {"value": tokens_all / (ms_e2e / args.steps / 1e3), "unit": "tokens/s",
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / args.steps},
-            # kernels of this library launched by this rank inside the timed region (counted at the C-ABI boundary)
-            "gpu_launches": counter.count,
-            # device time between the events bracketing each C-ABI call, summed over the timed region, per step
-            "abi_ms_per_step": {k_: round(v_ / args.steps, 4) for k_, v_ in sorted(counter.ms_by_entry_point().items())},
-            "clocks": clocks}
-    if world == 1 and not args.no_triton_ref:
-        line["reference_gpu"] = time_reference_triton(name, c, host, device)
     if world == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"], _ = cpu_reference(name, c, 1, 0)
+        line["cpu_baseline"], _, _ = cpu_reference(name, c, 1, 0)
     print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
+    if failed:
+        print("bench.py: a parity check failed (see the `parity` keys of the line above)", file=sys.stderr)
+        sys.exit(3)
 
 
 if __name__ == "__main__":

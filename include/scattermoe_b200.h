@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define SMOE_ABI_VERSION 1
+#define SMOE_ABI_VERSION 2
 
 enum smoe_status {
   SMOE_OK = 0,
@@ -45,11 +45,6 @@ enum smoe_flags {
   SMOE_FLAG_PAIR = 16,        /* smoe_scatter2scatter(_act): use the two-CTA (cta_group::2) tensor-core kernel where it
                                  applies (rows in expert order, N > 128); with SMOE_FLAG_FORCE_TC, fail if it does not */
   SMOE_FLAG_NO_PAIR = 32      /* never use the two-CTA kernel */
-};
-
-/* fused epilogues of smoe_scatter2scatter (what sits between / after the two expert linears) */
-enum smoe_epilogue {
-  SMOE_EPI_NONE = 0
 };
 
 int smoe_version(void);
@@ -108,7 +103,7 @@ int smoe_scatter2scatter(const void* X, int64_t x_rows, int64_t stride_xm, int64
                          const int64_t* expert_offsets,
                          int64_t R, int32_t K, int32_t N, int32_t E, int32_t fan_out,
                          int32_t x_grouped, int32_t y_grouped, int32_t dtype, int32_t flags,
-                         int32_t epilogue, int32_t* status, void* stream);
+                         int32_t* status, void* stream);
 
 /* ---- per-expert weight gradient ---------------------------------------------------------------------
  * Replaces kernels.ops.group_bwd_W (scattermoe/kernels/ops.py:191-239, kernel :247-366).
@@ -181,6 +176,21 @@ int smoe_scatter2scatter_act(const void* X, int64_t x_rows, int64_t stride_xm, i
                              int32_t fan_out, int32_t x_grouped, int32_t dtype, int32_t flags, int32_t act_layout,
                              int32_t act, float alpha, float limit, int32_t* status, void* stream);
 
+/* Input gradient of the down-projection + activation gradient in one kernel. Fuses the backward of
+ * scattermoe/mlp.py:41 / :81-87 (PyTorch autograd of the activation in the reference) into the grouped GEMM that the
+ * reference runs for the down-projection's input gradient (scattermoe/parallel_experts.py:110-116):
+ *     dU = d activation(U) applied to dH,   dH = DY @ W    (never stored)
+ * DY (R, K) and U, DU (R, n_up) are in expert order, W is (E, K, F) in element strides (the transposed view of the
+ * down-projection weight), layouts / functions as for smoe_activation_backward, n_up = F (plain) or 2F.
+ * Tensor-core kernel only: returns SMOE_ERR_UNSUPPORTED when the request does not fit it (dtype, alignment,
+ * F <= 128); the caller then runs smoe_scatter2scatter and smoe_activation_backward. */
+int smoe_scatter2scatter_act_bwd(const void* DY, int64_t stride_dym, int64_t stride_dyk,
+                                 const void* W, int64_t stride_we, int64_t stride_wk, int64_t stride_wn,
+                                 const void* U, int64_t stride_um, void* DU, int64_t stride_dum,
+                                 const int64_t* expert_offsets, int64_t R, int32_t K, int32_t F, int32_t E,
+                                 int32_t dtype, int32_t flags, int32_t act_layout, int32_t act, float alpha,
+                                 float limit, int32_t* status, void* stream);
+
 /* ---- single-token decode ---------------------------------------------------------------------------------
  * Replaces kernels.single.single2scatter (scattermoe/kernels/single.py:41-59, kernel :5-39): the k expert
  * matvecs of one token, Y[j, :] = X[j or 0, :] @ W[expert_idxs[j]]; X has 1 or k rows; any strides, any K and N
@@ -203,7 +213,10 @@ int smoe_single2scatter(const void* X, int64_t x_rows, int64_t stride_xm, int64_
  *   `dst_offsets[e]` = first row reserved for this rank's rows of expert e in the owner's (capacity_rows,
  *   peer_stride_rows) buffer, chosen so that the owner's buffer ends up expert-grouped with no further copy.
  * smoe_ep_return: for every row i < min(capacity_rows, *live_rows) of the local (capacity_rows, K) result Y:
- *     (r, s) = return_addr[i];  peer_slot_bufs[r][s, :] = Y[i, :]           (peer buffers are (peer_rows, stride)) */
+ *     (r, s) = return_addr[i];  peer_slot_bufs[r][s, :] = Y[i, :]           (peer buffers are (peer_rows, stride))
+ * Both kernels walk their rows in an order rotated by the calling rank (dispatch: starting with the next rank's
+ * experts; return: starting `my_rank` (expert, sender) sub-segments in, `local_experts` = E / world), so that at any
+ * moment the ranks write to different peers instead of all to the same one. */
 int smoe_ep_dispatch(const void* X, int64_t x_rows, int64_t stride_xm, const int64_t* sorted_expert_idxs,
                      const int64_t* sorted_scattered_idxs, const int64_t* expert_offsets, const int64_t* dst_offsets,
                      const void* coeff, int32_t fan_out, void* const* peer_bufs, int64_t peer_stride_rows,
@@ -211,14 +224,19 @@ int smoe_ep_dispatch(const void* X, int64_t x_rows, int64_t stride_xm, const int
                      int32_t E, int32_t world, int32_t dtype, void* stream);
 int smoe_ep_return(const void* Y, int64_t stride_ym, const int64_t* return_addr, const int64_t* live_rows,
                    int64_t capacity_rows, void* const* peer_slot_bufs, int64_t peer_stride_rows, int64_t peer_rows,
-                   int32_t K, int32_t world, int32_t dtype, void* stream);
+                   int32_t K, int32_t world, int32_t my_rank, int32_t local_experts, int32_t dtype, void* stream);
 /* Stream-ordered barrier across the ranks through peer memory: `peer_flags[w]` is rank w's int32[world] flag array
  * (zeroed once, before the first barrier, with the ranks synchronised by other means). Call with epoch = 1, 2, 3,
  * ... in the same order on every rank. Work enqueued after it on a rank runs after everything every rank
  * enqueued before its own call with the same epoch, including its peer stores. The wait inside is bounded
- * (about one second): on expiry `status` gets (2, 100, silent rank, epoch) and the kernel returns. */
-int smoe_ep_barrier(void* const* peer_flags, int32_t my_rank, int32_t world, int32_t epoch, int32_t* status,
-                    void* stream);
+ * (`limit_cycles` SM clocks, 0 = about one second): on expiry `status` gets (2, 100, silent rank, epoch) and the kernel
+ * returns; the work enqueued after it then runs on rows that may not have arrived. */
+int smoe_ep_barrier(void* const* peer_flags, int32_t my_rank, int32_t world, int32_t epoch, int64_t limit_cycles,
+                    int32_t* status, void* stream);
+/* Makes an expired wait loud: if status[0] != 0 when the kernel runs, `buf` (bytes) is filled with 0xFF bytes, which
+ * read as NaN in fp32 / bf16 / fp16; otherwise nothing is written. Enqueue it on the results of a step after the
+ * step's last barrier. */
+int smoe_status_poison(const int32_t* status, void* buf, int64_t bytes, void* stream);
 
 #ifdef __cplusplus
 }

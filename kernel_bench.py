@@ -1,6 +1,6 @@
 """Single-launch timings of the grouped-GEMM kernels at a named layer shape.
 
-    python -m scattermoe_b200.kernel_bench --workload mixtral_8x7b --launch all --pair both
+    python kernel_bench.py --workload mixtral_8x7b --launch all
 
 times, with CUDA events around back-to-back launches on torch's current stream, the launches one layer step makes
 through `kernels.ops` (rows already in expert order, as `parallel_linear` feeds them): the up-projection with and
@@ -12,15 +12,19 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
+import sys
 
 import torch
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 WORKLOADS = {   # tokens, d_model, d_ffn, experts, top_k
     "mixtral_8x7b": (16384, 4096, 14336, 8, 2),
     "gpt_oss_20b": (8192, 2880, 2880, 32, 4),
     "qwen3_moe": (8192, 2048, 768, 128, 8),
 }
-LAUNCHES = ("gemm1", "gemm1_act", "gemm2", "dgrad2", "dgrad1", "wgrad1", "wgrad2")
+LAUNCHES = ("gemm1", "gemm1_act", "gemm2", "dgrad2", "dgrad2_act", "dgrad1", "wgrad1", "wgrad2")
 
 
 def main(argv=None):
@@ -56,6 +60,8 @@ def main(argv=None):
                       2 * R * d * 2 * F),
         "gemm2": (lambda: s2s(h, w2.permute(0, 2, 1), False), 2 * R * d * F),
         "dgrad2": (lambda: s2s(x, w2, True), 2 * R * d * F),
+        "dgrad2_act": (lambda: ops.scatter2scatter_act_bwd(x, w2, d_up, off, act.LAYOUT_GLU_SECOND, act.ACT_SILU),
+                       2 * R * d * F),
         "dgrad1": (lambda: s2s(d_up, w1, False), 2 * R * d * 2 * F),
         "wgrad1": (lambda: ops.group_bwd_W(d_up, x, off, E), 2 * R * d * 2 * F),
         "wgrad2": (lambda: ops.group_bwd_W(x, h, off, E), 2 * R * d * F),

@@ -7,7 +7,7 @@ Same package surface as the reference's scattermoe/__init__.py:1-15; use it as
 Importing the package installs the Hugging Face MoE patches (utils.replace_moe), as importing the reference
 does (scattermoe/__init__.py:5 -> utils/__init__.py:1).
 """
-from .parallel_experts import flatten_sort_count, parallel_linear, parallel_linear_act, ParallelExperts
+from .parallel_experts import expert_mlp, flatten_sort_count, parallel_linear, parallel_linear_act, ParallelExperts
 from . import parallel_experts
 from . import kernels
 from . import mlp
@@ -18,6 +18,7 @@ __all__ = [
     "flatten_sort_count",
     "parallel_linear",
     "parallel_linear_act",
+    "expert_mlp",
     "ParallelExperts",
     "parallel_experts",
     "kernels",

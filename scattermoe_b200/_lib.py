@@ -17,6 +17,8 @@ from . import build as _build
 _lock = threading.Lock()
 _lib = None
 
+ABI_VERSION = 2          # SMOE_ABI_VERSION of include/scattermoe_b200.h this binding was written against
+
 SMOE_OK = 0
 SMOE_ERR_BAD_ARG = 1
 SMOE_ERR_UNSUPPORTED = 2
@@ -48,7 +50,7 @@ SIGNATURES = {
                               _P, _I64, _I64,                # Y
                               _P, _P, _P,                    # index tensors
                               _I64, _I32, _I32, _I32, _I32,  # R K N E fan_out
-                              _I32, _I32, _I32, _I32, _I32,  # x_grouped y_grouped dtype flags epilogue
+                              _I32, _I32, _I32, _I32,        # x_grouped y_grouped dtype flags
                               _P, _P], c_int32),
     "smoe_group_bwd_w": ([_P, _I64, _I64,                    # DY
                           _P, _I64, _I64, _I64,              # X
@@ -66,12 +68,15 @@ SIGNATURES = {
     "smoe_scatter2scatter_act": ([_P, _I64, _I64, _I64, _P, _I64, _I64, _I64, _P, _I64, _I64, _P, _I64, _I64, _P, _I64,
                                   _P, _P, _P, _I64, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, c_float, c_float,
                                   _P, _P], c_int32),
+    "smoe_scatter2scatter_act_bwd": ([_P, _I64, _I64, _P, _I64, _I64, _I64, _P, _I64, _P, _I64, _P, _I64, _I32, _I32, _I32,
+                                      _I32, _I32, _I32, _I32, c_float, c_float, _P, _P], c_int32),
     "smoe_single2scatter": ([_P, _I64, _I64, _I64, _P, _I64, _I64, _I64, _P, _I64, _I64, _P, _I32, _I32, _I32, _I32, _I32, _P],
                             c_int32),
     "smoe_ep_dispatch": ([_P, _I64, _I64, _P, _P, _P, _P, _P, _I32, _P, _I64, _I64, _P, _I32, _I64, _I32, _I32, _I32, _I32,
                           _P], c_int32),
-    "smoe_ep_return": ([_P, _I64, _P, _P, _I64, _P, _I64, _I64, _I32, _I32, _I32, _P], c_int32),
-    "smoe_ep_barrier": ([_P, _I32, _I32, _I32, _P, _P], c_int32),
+    "smoe_ep_return": ([_P, _I64, _P, _P, _I64, _P, _I64, _I64, _I32, _I32, _I32, _I32, _I32, _P], c_int32),
+    "smoe_ep_barrier": ([_P, _I32, _I32, _I32, _I64, _P, _P], c_int32),
+    "smoe_status_poison": ([_P, _P, _I64, _P], c_int32),
 }
 
 
@@ -107,6 +112,9 @@ def load():
                 raise ImportError("scattermoe_b200: %s does not export %s (stale build?)" % (path, name)) from e
             fn.argtypes = argtypes
             fn.restype = restype
+        if lib.smoe_version() != ABI_VERSION:
+            raise ImportError("scattermoe_b200: %s has ABI version %d, this package needs %d (stale build: run "
+                              "`python -m scattermoe_b200.build --force`)" % (path, lib.smoe_version(), ABI_VERSION))
         _lib = lib
         return _lib
 

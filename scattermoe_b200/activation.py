@@ -21,25 +21,64 @@ ACT_SILU, ACT_GELU_ERF, ACT_GELU_TANH, ACT_RELU, ACT_IDENTITY = 0, 1, 2, 3, 4
 FUSE = True    # set False to fall back to calling the activation object with PyTorch ops
 
 
+def _hf_activation_types():
+    """Exact Hugging Face activation classes whose forward is one of the functions fused here."""
+    try:
+        import transformers.activations as hf
+    except Exception:
+        return {}
+    out = {}
+    for cls_name, code in (("SiLUActivation", ACT_SILU), ("GELUActivation", ACT_GELU_ERF), ("GELUTanh", ACT_GELU_TANH)):
+        cls = getattr(hf, cls_name, None)
+        if cls is not None:
+            out[cls] = code
+    return out
+
+
+_HF_TYPES = None
+
+
 def resolve_activation(fn) -> Optional[int]:
-    """Activation code for a module / function this library fuses, else None."""
+    """Activation code for a module / function this library fuses, else None (the callable is then simply called,
+    as the reference always does, scattermoe/mlp.py:41, :87). Matching is by identity or EXACT type, never by
+    name and never for subclasses: a user class that happens to be called `Swish`, or a subclass overriding
+    forward, keeps its own arithmetic."""
+    global _HF_TYPES
     if fn is None:
         return None
-    if isinstance(fn, nn.SiLU) or fn is torch.nn.functional.silu:
+    Fn = torch.nn.functional
+    if fn is Fn.silu:
         return ACT_SILU
-    if isinstance(fn, nn.GELU):
-        return ACT_GELU_TANH if getattr(fn, "approximate", "none") == "tanh" else ACT_GELU_ERF
-    if fn is torch.nn.functional.gelu:
+    if fn is Fn.gelu:
         return ACT_GELU_ERF
-    if isinstance(fn, nn.ReLU) or fn is torch.nn.functional.relu:
+    if fn is Fn.relu:
         return ACT_RELU
-    if isinstance(fn, nn.Identity):
-        return ACT_IDENTITY
-    name = type(fn).__name__.lower()
-    if name in ("siluactivation", "silu", "swish"):          # Hugging Face ACT2FN["silu"]
+    t = type(fn)
+    if t is nn.SiLU:
         return ACT_SILU
-    if name in ("geluactivation",):
-        return ACT_GELU_ERF
+    if t is nn.GELU:
+        return ACT_GELU_TANH if getattr(fn, "approximate", "none") == "tanh" else ACT_GELU_ERF
+    if t is nn.ReLU:
+        return ACT_RELU
+    if t is nn.Identity:
+        return ACT_IDENTITY
+    if _HF_TYPES is None:
+        _HF_TYPES = _hf_activation_types()
+    code = _HF_TYPES.get(t)
+    if code is not None:
+        # these classes pick their implementation in __init__ (`use_gelu_python` and the like): only the default,
+        # nn.functional-backed one is the function fused here (the pure-Python variants agree mathematically but
+        # the reference would run them as written)
+        act = getattr(fn, "act", None)
+        if act is None:
+            return code
+        if act is Fn.gelu and code == ACT_GELU_ERF:
+            return code
+        import functools
+        if (isinstance(act, functools.partial) and act.func is Fn.gelu and act.keywords == {"approximate": "tanh"}
+                and not act.args and code == ACT_GELU_TANH):
+            return code
+        return None
     return None
 
 

@@ -64,8 +64,8 @@ extern "C" int smoe_scatter2scatter(const void* X, int64_t x_rows, int64_t strid
                                     int64_t stride_ym, int64_t stride_yn, const int64_t* sorted_expert_idxs,
                                     const int64_t* sorted_scattered_idxs, const int64_t* expert_offsets, int64_t R,
                                     int32_t K, int32_t N, int32_t E, int32_t fan_out, int32_t x_grouped,
-                                    int32_t y_grouped, int32_t dtype, int32_t flags, int32_t epilogue,
-                                    int32_t* status, void* stream) {
+                                    int32_t y_grouped, int32_t dtype, int32_t flags, int32_t* status,
+                                    void* stream) {
   if (int rc = check_dtype("scatter2scatter", dtype)) return rc;
   SMOE_CHECK_ARG(R >= 0 && R < (int64_t(1) << 31), "scatter2scatter: R=%lld out of range [0, 2^31)", (long long)R);
   SMOE_CHECK_ARG(K >= 0 && N >= 0 && E >= 1 && fan_out >= 1, "scatter2scatter: bad sizes K=%d N=%d E=%d fan_out=%d", K,
@@ -74,13 +74,12 @@ extern "C" int smoe_scatter2scatter(const void* X, int64_t x_rows, int64_t strid
   SMOE_CHECK_ARG(x_rows * fan_out == R && (!x_grouped || fan_out == 1),
                  "scatter2scatter: %lld index entries but X has %lld rows with fan_out %d", (long long)R,
                  (long long)x_rows, fan_out);
-  SMOE_CHECK_ARG(epilogue == SMOE_EPI_NONE, "scatter2scatter: unknown epilogue %d", epilogue);
   if (R == 0 || N == 0) return SMOE_OK;
   SMOE_CHECK_ARG(X && W && Y && sorted_expert_idxs && sorted_scattered_idxs && expert_offsets,
                  "scatter2scatter: null pointer");
   S2SArgs a{X, x_rows, stride_xm, stride_xk, W, stride_we, stride_wk, stride_wn, bias, stride_be, stride_bn,
             Y, stride_ym, stride_yn, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
-            R, K, N, E, fan_out, x_grouped ? 1 : 0, y_grouped ? 1 : 0, dtype, flags, epilogue,
+            R, K, N, E, fan_out, x_grouped ? 1 : 0, y_grouped ? 1 : 0, dtype, flags,
             status, static_cast<cudaStream_t>(stream)};
   if (!(flags & SMOE_FLAG_FORCE_SIMT)) {
     const int rc = launch_s2s_tc(a);
@@ -156,9 +155,37 @@ extern "C" int smoe_scatter2scatter_act(const void* X, int64_t x_rows, int64_t s
   if (flags & SMOE_FLAG_FORCE_SIMT) return SMOE_ERR_UNSUPPORTED;
   S2SArgs a{X, x_rows, stride_xm, stride_xk, W, stride_we, stride_wk, stride_wn, bias, stride_be, stride_bn,
             Y, stride_ym, stride_yn, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
-            R, K, N, E, fan_out, x_grouped ? 1 : 0, 1, dtype, flags, 0, status, static_cast<cudaStream_t>(stream)};
+            R, K, N, E, fan_out, x_grouped ? 1 : 0, 1, dtype, flags, status, static_cast<cudaStream_t>(stream)};
   a.H = H; a.shm = stride_hm; a.act_layout = act_layout; a.act = act; a.alpha = alpha; a.limit = limit;
   if (Y == nullptr) { a.sym = 8; a.syn = 1; }
+  const int rc = launch_s2s_tc(a);
+  if (rc == SMOE_OK) set_last_path(1);
+  return rc;
+}
+
+// Input gradient of the down-projection with the activation gradient fused into the epilogue of the tensor-core
+// kernel: dU = activation'(U) applied to (DY @ W), the (rows, F) hidden gradient itself never stored. Returns
+// SMOE_ERR_UNSUPPORTED (no error text) when the request does not fit that kernel: the caller then runs
+// smoe_scatter2scatter followed by smoe_activation_backward.
+extern "C" int smoe_scatter2scatter_act_bwd(const void* DY, int64_t stride_dym, int64_t stride_dyk, const void* W,
+                                            int64_t stride_we, int64_t stride_wk, int64_t stride_wn, const void* U,
+                                            int64_t stride_um, void* DU, int64_t stride_dum,
+                                            const int64_t* expert_offsets, int64_t R, int32_t K, int32_t F, int32_t E,
+                                            int32_t dtype, int32_t flags, int32_t act_layout, int32_t act, float alpha,
+                                            float limit, int32_t* status, void* stream) {
+  if (int rc = check_dtype("scatter2scatter_act_bwd", dtype)) return rc;
+  SMOE_CHECK_ARG(R >= 0 && R < (int64_t(1) << 31), "scatter2scatter_act_bwd: R=%lld out of range", (long long)R);
+  SMOE_CHECK_ARG(K >= 0 && F >= 0 && E >= 1, "scatter2scatter_act_bwd: bad sizes K=%d F=%d E=%d", K, F, E);
+  SMOE_CHECK_ARG(act_layout >= 0 && act_layout <= 3 && act >= 0 && act <= 4,
+                 "scatter2scatter_act_bwd: layout %d / function %d", act_layout, act);
+  if (R == 0 || F == 0) return SMOE_OK;
+  SMOE_CHECK_ARG(DY && W && U && DU && expert_offsets, "scatter2scatter_act_bwd: null pointer");
+  if (flags & SMOE_FLAG_FORCE_SIMT) return SMOE_ERR_UNSUPPORTED;
+  // rows are in expert order on both sides: the index tensors are never read (the offsets stand in for them)
+  S2SArgs a{DY, R, stride_dym, stride_dyk, W, stride_we, stride_wk, stride_wn, nullptr, 0, 0,
+            DU, stride_dum, 1, expert_offsets, expert_offsets, expert_offsets,
+            R, K, F, E, 1, 1, 1, dtype, flags, status, static_cast<cudaStream_t>(stream)};
+  a.U = U; a.sum = stride_um; a.act_layout = act_layout; a.act = act; a.alpha = alpha; a.limit = limit; a.act_bwd = 1;
   const int rc = launch_s2s_tc(a);
   if (rc == SMOE_OK) set_last_path(1);
   return rc;

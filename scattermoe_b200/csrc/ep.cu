@@ -36,8 +36,18 @@ ep_dispatch_kernel(const T* __restrict__ X, int64_t x_rows, int64_t sxm, const i
                    int64_t peer_row_elems, int64_t cap_rows, PeerPtrs ret_peers, int my_rank, int64_t R, int K, int E,
                    int e_local, int world) {
   const int lane = threadIdx.x & 31;
-  const int64_t m = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  int64_t m = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (m >= R) return;
+  // Rank r starts with the rows of rank r+1's experts and wraps around: at any moment the ranks are then writing
+  // to DIFFERENT owners. In plain sorted order every rank would first write to rank 0, then all to rank 1, ...:
+  // eight senders into one receiver's NVLink ingress at a time.
+  {
+    const int first = ((my_rank + 1) % world) * e_local;
+    int64_t shift = first ? offsets[first - 1] : 0;
+    shift = shift < 0 ? 0 : (shift > R ? R : shift);
+    m += shift;
+    if (m >= R) m -= R;
+  }
   const int64_t e = sorted_e[m];
   const int64_t slot = sorted_idx[m];
   if (e < 0 || e >= E || slot < 0 || slot >= R) return;
@@ -74,12 +84,18 @@ template <typename T, bool VEC>
 __global__ void __launch_bounds__(256)
 ep_return_kernel(const T* __restrict__ Y, int64_t sym, const int64_t* __restrict__ ret_addr,
                  const int64_t* __restrict__ live_rows, int64_t cap_rows, PeerPtrs peers, int64_t peer_row_elems,
-                 int64_t peer_rows, int K, int world) {
+                 int64_t peer_rows, int K, int world, int64_t row_shift_num, int64_t row_shift_den) {
   const int lane = threadIdx.x & 31;
   const int64_t live = min(cap_rows, *live_rows);
+  // The buffer is ordered (local expert, sending rank): walked from row 0 every owner would be returning rows to
+  // the same rank at the same time. Owner r starts r sub-segments in (live * r / (local experts * world) rows) and
+  // wraps, so that the owners address different ranks at any moment (exactly so when the load is even).
+  const int64_t shift = row_shift_den > 0 ? (live * row_shift_num / row_shift_den) : 0;
   // grid-stride over the live rows: the grid is sized for the device, not for the (much larger) capacity
-  for (int64_t i = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); i < live;
-       i += static_cast<int64_t>(gridDim.x) * 8) {
+  for (int64_t j = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); j < live;
+       j += static_cast<int64_t>(gridDim.x) * 8) {
+    int64_t i = j + shift;
+    if (i >= live) i -= live;
     const int64_t d = ret_addr[i];
     const int rank = dest_rank(d);
     const int64_t slot = dest_row(d);
@@ -102,11 +118,13 @@ ep_return_kernel(const T* __restrict__ Y, int64_t sym, const int64_t* __restrict
 // rows this rank pushed earlier on the stream are visible first) and then waits until all of its own slots have
 // reached n (acquire, system scope). Epochs only grow, so a fast peer that is already one barrier ahead is
 // fine. The wait is bounded: after ~1 s of SM clocks it records (2, 100, peer, epoch) in `status` and returns, so
-// a lost rank can never hang this GPU. One block of 32 threads, thread w talks to rank w.
+// a lost rank can never hang this GPU. One block of 32 threads, thread w talks to rank w. What ran on the strength of
+// an expired barrier has read rows that had not arrived: callers follow their last barrier with
+// smoe_status_poison on their results, so that the step yields NaNs instead of plausible numbers.
 constexpr long long EP_BARRIER_LIMIT_CYCLES = 2000000000LL;
 
 __global__ void __launch_bounds__(32)
-ep_barrier_kernel(PeerPtrs flags, int my_rank, int world, int epoch, int32_t* status) {
+ep_barrier_kernel(PeerPtrs flags, int my_rank, int world, int epoch, long long limit_cycles, int32_t* status) {
   const int w = threadIdx.x;
   if (w >= world) return;
   __threadfence_system();
@@ -118,7 +136,7 @@ ep_barrier_kernel(PeerPtrs flags, int my_rank, int world, int epoch, int32_t* st
     int v;
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
     if (v >= epoch) break;
-    if (clock64() - t0 > EP_BARRIER_LIMIT_CYCLES) {
+    if (clock64() - t0 > limit_cycles) {
       if (status && atomicCAS(status, 0, 2) == 0) {
         status[1] = 100;
         status[2] = w;
@@ -173,17 +191,17 @@ static int dispatch_typed(const void* X, int64_t x_rows, int64_t sxm, const int6
 template <typename T>
 static int return_typed(const void* Y, int64_t sym, const int64_t* ret_addr, const int64_t* live_rows, int64_t cap_rows,
                         const PeerPtrs& pp, bool aligned, int64_t peer_row_elems, int64_t peer_rows, int K, int world,
-                        cudaStream_t st) {
+                        int64_t shift_num, int64_t shift_den, cudaStream_t st) {
   constexpr int V = 16 / sizeof(T);
   const bool vec = aligned && K % V == 0 && sym % V == 0 && peer_row_elems % V == 0 && a16(Y);
   const int64_t want = cdiv64(cap_rows, 8);
   const unsigned grid = static_cast<unsigned>(want < 148 * 16 ? want : 148 * 16);
   if (vec)
     ep_return_kernel<T, true><<<grid, 256, 0, st>>>((const T*)Y, sym, ret_addr, live_rows, cap_rows, pp, peer_row_elems,
-                                                    peer_rows, K, world);
+                                                    peer_rows, K, world, shift_num, shift_den);
   else
     ep_return_kernel<T, false><<<grid, 256, 0, st>>>((const T*)Y, sym, ret_addr, live_rows, cap_rows, pp, peer_row_elems,
-                                                     peer_rows, K, world);
+                                                     peer_rows, K, world, shift_num, shift_den);
   SMOE_LAUNCH_CHECK();
   return SMOE_OK;
 }
@@ -227,8 +245,12 @@ extern "C" int smoe_ep_dispatch(const void* X, int64_t x_rows, int64_t stride_xm
 
 extern "C" int smoe_ep_return(const void* Y, int64_t stride_ym, const int64_t* return_addr, const int64_t* live_rows,
                               int64_t capacity_rows, void* const* peer_slot_bufs, int64_t peer_stride_rows,
-                              int64_t peer_rows, int32_t K, int32_t world, int32_t dtype, void* stream) {
+                              int64_t peer_rows, int32_t K, int32_t world, int32_t my_rank, int32_t local_experts,
+                              int32_t dtype, void* stream) {
   SMOE_CHECK_ARG(capacity_rows >= 0 && K >= 0, "ep_return: bad sizes rows=%lld K=%d", (long long)capacity_rows, K);
+  SMOE_CHECK_ARG(my_rank >= 0 && my_rank < world && local_experts >= 1, "ep_return: rank %d of %d, %d local experts",
+                 my_rank, world, local_experts);
+  const int64_t shift_num = my_rank, shift_den = static_cast<int64_t>(local_experts) * world;
   if (capacity_rows == 0 || K == 0) return SMOE_OK;
   SMOE_CHECK_ARG(Y && return_addr && live_rows && peer_slot_bufs, "ep_return: null pointer");
   PeerPtrs pp;
@@ -236,22 +258,54 @@ extern "C" int smoe_ep_return(const void* Y, int64_t stride_ym, const int64_t* r
   if (int rc = fill_peers(&pp, peer_slot_bufs, world, "ep_return", &aligned)) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
-    case SMOE_F32: return return_typed<float>(Y, stride_ym, return_addr, live_rows, capacity_rows, pp, aligned, peer_stride_rows, peer_rows, K, world, st);
-    case SMOE_BF16: return return_typed<__nv_bfloat16>(Y, stride_ym, return_addr, live_rows, capacity_rows, pp, aligned, peer_stride_rows, peer_rows, K, world, st);
-    case SMOE_F16: return return_typed<__half>(Y, stride_ym, return_addr, live_rows, capacity_rows, pp, aligned, peer_stride_rows, peer_rows, K, world, st);
+    case SMOE_F32: return return_typed<float>(Y, stride_ym, return_addr, live_rows, capacity_rows, pp, aligned, peer_stride_rows, peer_rows, K, world, shift_num, shift_den, st);
+    case SMOE_BF16: return return_typed<__nv_bfloat16>(Y, stride_ym, return_addr, live_rows, capacity_rows, pp, aligned, peer_stride_rows, peer_rows, K, world, shift_num, shift_den, st);
+    case SMOE_F16: return return_typed<__half>(Y, stride_ym, return_addr, live_rows, capacity_rows, pp, aligned, peer_stride_rows, peer_rows, K, world, shift_num, shift_den, st);
   }
   set_error("ep_return: unknown dtype %d", dtype);
   return SMOE_ERR_BAD_ARG;
 }
 
-extern "C" int smoe_ep_barrier(void* const* peer_flags, int32_t my_rank, int32_t world, int32_t epoch, int32_t* status,
-                               void* stream) {
+extern "C" int smoe_ep_barrier(void* const* peer_flags, int32_t my_rank, int32_t world, int32_t epoch,
+                               int64_t limit_cycles, int32_t* status, void* stream) {
   SMOE_CHECK_ARG(peer_flags != nullptr, "ep_barrier: null pointer");
   SMOE_CHECK_ARG(my_rank >= 0 && my_rank < world && epoch > 0, "ep_barrier: rank %d of %d, epoch %d", my_rank, world, epoch);
   PeerPtrs pp;
   bool aligned;
   if (int rc = fill_peers(&pp, peer_flags, world, "ep_barrier", &aligned)) return rc;
-  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp, my_rank, world, epoch, status);
+  SMOE_CHECK_ARG(limit_cycles >= 0, "ep_barrier: negative wait limit");
+  const long long limit = limit_cycles > 0 ? static_cast<long long>(limit_cycles) : EP_BARRIER_LIMIT_CYCLES;
+  ep_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp, my_rank, world, epoch, limit, status);
+  SMOE_LAUNCH_CHECK();
+  return SMOE_OK;
+}
+
+// Fills `buf` with 0xFF bytes (NaN in every floating-point format this library stores) if the status word says that
+// a bounded wait ran out. Reads one int and returns otherwise.
+__global__ void __launch_bounds__(256)
+status_poison_kernel(const int32_t* __restrict__ status, uint8_t* __restrict__ buf, int64_t bytes) {
+  if (status[0] == 0) return;
+  int64_t head = (16 - static_cast<int64_t>(reinterpret_cast<uintptr_t>(buf) & 15)) & 15;
+  head = head < bytes ? head : bytes;
+  uint4* body = reinterpret_cast<uint4*>(buf + head);
+  const int64_t n16 = (bytes - head) / 16;
+  const uint4 ff = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n16;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    body[i] = ff;
+  if (blockIdx.x == 0) {
+    for (int64_t i = threadIdx.x; i < head; i += blockDim.x) buf[i] = 0xff;
+    for (int64_t i = head + n16 * 16 + threadIdx.x; i < bytes; i += blockDim.x) buf[i] = 0xff;
+  }
+}
+
+extern "C" int smoe_status_poison(const int32_t* status, void* buf, int64_t bytes, void* stream) {
+  SMOE_CHECK_ARG(bytes >= 0, "status_poison: negative size");
+  if (bytes == 0) return SMOE_OK;
+  SMOE_CHECK_ARG(status && buf, "status_poison: null pointer");
+  const int64_t want = cdiv64(bytes / 16 + 1, 256);
+  const unsigned grid = static_cast<unsigned>(want < 148 * 4 ? want : 148 * 4);
+  status_poison_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(status, static_cast<uint8_t*>(buf), bytes);
   SMOE_LAUNCH_CHECK();
   return SMOE_OK;
 }

@@ -18,6 +18,7 @@
 //     "major" bits of the UMMA descriptors.
 // Every wait is bounded (ptx.cuh): a protocol bug sets the status word and the kernel returns.
 #include <cuda.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -63,6 +64,10 @@ struct S2SParams {
   uint8_t* H; int64_t h_row_bytes;
   int F, glu_first, act;
   float alpha, limit;
+  // fused activation-gradient epilogue (EPI_BWD_*): U (rows, n_up) is the up-projection saved by forward; the GEMM's
+  // result is the hidden gradient (N = F columns, never stored) and Y receives the (rows, n_up) gradient of U
+  const uint8_t* U; int64_t u_row_bytes;
+  int group_m;         // m-tiles per raster group (see decode_tile)
   uint32_t idesc;
   int32_t* status;
 };
@@ -104,8 +109,13 @@ __device__ __forceinline__ void build_tile_table(const int64_t* __restrict__ off
 
 struct Tile { int e, m0, rows, n0; };
 
+// Tile t of the launch -> expert, row tile, column tile. Inside one expert the m-tiles are walked in groups of
+// `group_m`: all column tiles of a group before the next group, the m-tiles of the group innermost. The 148
+// tiles that run at the same time then cover about group_m x 148/group_m tiles instead of a whole column of
+// m-tiles x a few columns: with group_m chosen so that both footprints are alike, the operands a wave streams
+// from HBM (rows x K of A plus columns x K of W) are at their minimum for the number of tiles in flight.
 __device__ __forceinline__ Tile decode_tile(int t, const int32_t* tile_prefix, const int32_t* seg_start, int E, int BN,
-                                            int mtile_rows = BM) {
+                                            int mtile_rows = BM, int group_m = 1 << 30) {
   int lo = 0, hi = E;
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
@@ -116,7 +126,14 @@ __device__ __forceinline__ Tile decode_tile(int t, const int32_t* tile_prefix, c
   const int local = t - tile_prefix[lo];
   const int cnt = seg_start[lo + 1] - seg_start[lo];
   const int m_tiles = (cnt + mtile_rows - 1) / mtile_rows;
-  const int n_tile = local / m_tiles, m_tile = local - n_tile * m_tiles;
+  const int n_tiles_e = (tile_prefix[lo + 1] - tile_prefix[lo]) / m_tiles;
+  const int gm = max(1, min(group_m, m_tiles));
+  const int per_group = gm * n_tiles_e;
+  const int grp = local / per_group;
+  const int in_grp = local - grp * per_group;
+  const int gw = min(gm, m_tiles - grp * gm);
+  const int n_tile = in_grp / gw;
+  const int m_tile = grp * gm + (in_grp - n_tile * gw);
   tl.m0 = seg_start[lo] + m_tile * mtile_rows;
   tl.rows = min(mtile_rows, seg_start[lo + 1] - tl.m0);
   tl.n0 = n_tile * BN;
@@ -125,7 +142,11 @@ __device__ __forceinline__ Tile decode_tile(int t, const int32_t* tile_prefix, c
 
 // EPI: 0 plain linear; 1 H = act(Y); 2 gated halves, H[j] = act(gate) * lin with the halves F columns apart (a tile then
 // holds 128 columns of EACH half: accumulator columns [0,128) and [128,256)); 3 gpt-oss interleaved clamped SwiGLU.
-enum { EPI_NONE = 0, EPI_ACT = 1, EPI_GLU_HALVES = 2, EPI_GPT_OSS = 3 };
+// EPI_BWD_*: the GEMM's result is the gradient of the hidden activations (N = F columns); the epilogue turns it into
+// the gradient of the saved up-projection U and stores that, (rows, n_up), instead: the hidden gradient never
+// reaches memory (4 plain, 5 gated halves, 6 gpt-oss interleaved).
+enum { EPI_NONE = 0, EPI_ACT = 1, EPI_GLU_HALVES = 2, EPI_GPT_OSS = 3, EPI_BWD_PLAIN = 4, EPI_BWD_GLU = 5,
+       EPI_BWD_GPT_OSS = 6 };
 
 __device__ __forceinline__ void add_bias8(const uint8_t* brow, int col, int is_bf16, int bias_vec, float (&v)[8]) {
   if (!brow) return;
@@ -295,6 +316,104 @@ __device__ __forceinline__ void epilogue_rows(const S2SParams& p, int n0, uint32
   }
 }
 
+// Eight 16-bit values of one row as floats; zeros when the row is not valid.
+__device__ __forceinline__ void load8(const uint8_t* ptr, int is_bf16, bool ok, float (&v)[8]) {
+  const uint4 raw = ok ? __ldg(reinterpret_cast<const uint4*>(ptr)) : make_uint4(0u, 0u, 0u, 0u);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (is_bf16) {
+      const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[j]);
+      v[2 * j] = __low2float(h); v[2 * j + 1] = __high2float(h);
+    } else {
+      const __half2 h = *reinterpret_cast<const __half2*>(&w[j]);
+      v[2 * j] = __low2float(h); v[2 * j + 1] = __high2float(h);
+    }
+  }
+}
+
+// Epilogue of one tile of the fused "input gradient of the down-projection + activation gradient" launch. The
+// accumulator holds dH = dL/d(hidden) for 128 rows x BN hidden columns starting at n0; lane l owns row l of the warp's
+// quarter, reads ITS row of the saved up-projection U (`urow`) and writes the matching columns of dU (`durow`):
+//   plain       dU[j]      = dH[j] * act'(U[j])
+//   gated       dU[lin j]  = dH[j] * act(U[gate j]),   dU[gate j] = dH[j] * U[lin j] * act'(U[gate j])
+//   gpt-oss     g = U[2j], u = U[2j+1] (clamped in forward): dU[2j+1] = dH[j] * glu(g) inside the clamp, else 0;
+//               dU[2j] = dH[j] * (u_c + 1) * glu'(g) below the limit, else 0
+// (the arithmetic of act_backward_kernel in activation.cu, on fp32 accumulators instead of a rounded dH).
+template <int BN, int EPI>
+__device__ __forceinline__ void epilogue_act_bwd(const S2SParams& p, int n0, uint32_t taddr, uint8_t* slab, int lane,
+                                                 bool valid, uint8_t* durow, const uint8_t* urow) {
+  const int F = p.N;
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    const int n = n0 + c * 32;
+    if (n >= F) break;
+    uint32_t acc[32];
+    tmem_ld_32x32b_x32(taddr + c * 32, acc);
+    tmem_ld_wait();
+    if (EPI == EPI_BWD_PLAIN) {
+      uint4 pd[4];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const int nn = min(n + g * 8, F - 8);       // clamped for the loads; the flush masks the columns
+        float u[8], d[8];
+        load8(urow + nn * 2, p.is_bf16, valid, u);
+        SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj)
+          d[jj] = __uint_as_float(acc[g * 8 + jj]) * act_bwd<ACT_, true>(u[jj]);)
+        pd[g] = pack8(d, p.is_bf16);
+      }
+      flush_rows<4>(slab, lane, pd, durow, valid, n, F);
+    } else if (EPI == EPI_BWD_GLU) {
+      const int lin_off = p.glu_first ? F : 0, gate_off = p.glu_first ? 0 : F;
+      uint4 pl[4], pg[4];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const int nn = min(n + g * 8, F - 8);
+        float lin[8], gate[8], dl[8], dg[8];
+        load8(urow + static_cast<int64_t>(lin_off + nn) * 2, p.is_bf16, valid, lin);
+        load8(urow + static_cast<int64_t>(gate_off + nn) * 2, p.is_bf16, valid, gate);
+        SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj) {
+          const float dh = __uint_as_float(acc[g * 8 + jj]);
+          dl[jj] = dh * act_fwd<ACT_, true>(gate[jj]);
+          dg[jj] = dh * lin[jj] * act_bwd<ACT_, true>(gate[jj]);
+        })
+        pl[g] = pack8(dl, p.is_bf16);
+        pg[g] = pack8(dg, p.is_bf16);
+      }
+      flush_rows<4>(slab, lane, pl, durow + static_cast<int64_t>(lin_off) * 2, valid, n, F);
+      flush_rows<4>(slab, lane, pg, durow + static_cast<int64_t>(gate_off) * 2, valid, n, F);
+    } else {
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {               // 16 hidden columns -> 32 columns of U
+        uint4 po[4];
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          const int nn = min(n + hh * 16 + g * 8, F - 8);
+          float u0[8], u1[8], o0[8], o1[8];
+          load8(urow + static_cast<int64_t>(2 * nn) * 2, p.is_bf16, valid, u0);
+          load8(urow + static_cast<int64_t>(2 * nn + 8) * 2, p.is_bf16, valid, u1);
+#pragma unroll
+          for (int jj = 0; jj < 8; ++jj) {
+            const float g0 = (jj < 4) ? u0[2 * jj] : u1[2 * jj - 8];
+            const float up0 = (jj < 4) ? u0[2 * jj + 1] : u1[2 * jj - 7];
+            const float dh = __uint_as_float(acc[hh * 16 + g * 8 + jj]);
+            const float gc = fminf(g0, p.limit);
+            const float uc = fminf(fmaxf(up0, -p.limit), p.limit);
+            const float sg = sigmoidf_<true>(p.alpha * gc);
+            const float d_u = (up0 >= -p.limit && up0 <= p.limit) ? dh * (gc * sg) : 0.f;
+            const float d_g = (g0 <= p.limit) ? dh * (uc + 1.0f) * (sg + gc * p.alpha * sg * (1.0f - sg)) : 0.f;
+            if (jj < 4) { o0[2 * jj] = d_g; o0[2 * jj + 1] = d_u; }
+            else { o1[2 * jj - 8] = d_g; o1[2 * jj - 7] = d_u; }
+          }
+          po[2 * g] = pack8(o0, p.is_bf16);
+          po[2 * g + 1] = pack8(o1, p.is_bf16);
+        }
+        flush_rows<4>(slab, lane, po, durow, valid, 2 * (n + hh * 16), 2 * F);
+      }
+    }
+  }
+}
+
 template <int BN, bool B_KMAJOR, int EPI>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
@@ -354,7 +473,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN);
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, BM, p.group_m);
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
@@ -432,7 +551,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN);
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, BM, p.group_m);
       const uint8_t* rowptr[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -476,7 +595,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     int tile_iter = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
-      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN);
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, BM, p.group_m);
       const int buf = tile_iter & 1;
       const uint32_t tph = (tile_iter >> 1) & 1;
       bool valid = r < tl.rows;
@@ -491,9 +610,13 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
       if (!mbar_wait_warp(tfull_bar(buf), tph, abort_flag, p.status, 5)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-      uint8_t* hrow = (EPI != EPI_NONE) ? p.H + out_row * p.h_row_bytes : nullptr;
       uint8_t* slab = epi_staging + q * (32 * C::STAGE_ROW_BYTES);
-      epilogue_rows<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, hrow, brow);
+      if constexpr (EPI >= EPI_BWD_PLAIN) {
+        epilogue_act_bwd<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, p.U + out_row * p.u_row_bytes);
+      } else {
+        uint8_t* hrow = (EPI != EPI_NONE) ? p.H + out_row * p.h_row_bytes : nullptr;
+        epilogue_rows<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, hrow, brow);
+      }
       tc_fence_before_sync();
       mbar_arrive(tempty_bar(buf));
     }
@@ -719,6 +842,8 @@ struct WGradParams {
   int64_t R;
   int K, N, E, fan_out, is_bf16;
   int x_by_tma;        // X is grouped and TMA-addressable: whole 64-row slabs come by TMA, ragged tails by cp.async
+  int band_over_n;     // 0: bands of `band` X-feature tiles, DY-feature tiles stream through them; 1: the other way
+  int band;            // band width in tiles (see the tile order in the kernel)
   uint32_t idesc;
   int32_t* status;
 };
@@ -787,19 +912,31 @@ wgrad_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_consta
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_holder;
 
-  // tile t -> expert, DY-feature tile, X-feature tile and the expert's row segment. Inside one expert the
-  // X-feature tiles are walked in bands of KBAND: a band's X slabs (KBAND * BNW features of the expert's
-  // rows) stay in L2 while every DY-feature tile passes over them, so both operands stream from HBM about once.
-  constexpr int KBAND = 16;
+  // tile t -> expert, DY-feature tile, X-feature tile and the expert's row segment. Inside one expert the tiles are
+  // walked in bands: `band` tiles of ONE operand's feature dimension stay in L2 (band * tile width * rows of the
+  // expert) while every tile of the other operand passes over them once, so the banded operand is read from HBM
+  // once per expert and the streamed one once per band. The host picks the operand to band (the one whose whole
+  // panel, or failing that the larger share of it, fits the L2 budget) and the band width.
+  const int band_w = max(1, p.band);
   auto decode = [&](int t, int& e, int& n0, int& k0, int& m_beg, int& m_end) {
     e = t / tiles_per_e;
     const int rem = t - e * tiles_per_e;
-    const int band = rem / (n_tiles * KBAND);
-    const int in_band = rem - band * n_tiles * KBAND;
-    const int bandw = min(KBAND, k_tiles - band * KBAND);
-    const int nt = in_band / bandw;
+    int nt, kt;
+    if (p.band_over_n) {
+      const int band = rem / (k_tiles * band_w);
+      const int in_band = rem - band * k_tiles * band_w;
+      const int bw = min(band_w, n_tiles - band * band_w);
+      kt = in_band / bw;
+      nt = band * band_w + (in_band - kt * bw);
+    } else {
+      const int band = rem / (n_tiles * band_w);
+      const int in_band = rem - band * n_tiles * band_w;
+      const int bw = min(band_w, k_tiles - band * band_w);
+      nt = in_band / bw;
+      kt = band * band_w + (in_band - nt * bw);
+    }
     n0 = nt * BM;
-    k0 = (band * KBAND + (in_band - nt * bandw)) * BNW;
+    k0 = kt * BNW;
     m_beg = seg_start[e];
     m_end = max(m_beg, seg_start[e + 1]);
   };
@@ -1161,6 +1298,15 @@ static bool encode_map3(CUtensorMap* map, bool bf16, const void* base, uint64_t 
 
 static inline bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// Tuning knobs, read once: SMOE_GROUP_M (m-tiles per raster group of the grouped GEMM) and SMOE_L2_BAND_MB (bytes
+// of L2 the weight gradient plans to keep one operand's band resident in). Unset: the built-in choices.
+static int env_int(const char* name, int fallback) {
+  const char* v = getenv(name);
+  if (!v || !*v) return fallback;
+  const long x = strtol(v, nullptr, 10);
+  return x > 0 && x < (1 << 20) ? static_cast<int>(x) : fallback;
+}
+
 template <int BN, bool B_KMAJOR, int EPI = EPI_NONE>
 static int launch_s2s_cfg(const CUtensorMap& map, const CUtensorMap& map_x, const S2SParams& p, int grid,
                           cudaStream_t stream) {
@@ -1270,12 +1416,19 @@ int launch_s2s_tc(const S2SArgs& a) {
   const bool bf16 = a.dtype == SMOE_BF16;
   // fused activation epilogue: which kernel variant, and what it needs
   int epi = EPI_NONE, F = 0;
-  if (a.act_layout >= 0) {
+  if (a.act_layout >= 0 && !a.act_bwd) {
     if (a.N <= 128 || a.H == nullptr || a.shm % 8 || !al16(a.H)) return SMOE_ERR_UNSUPPORTED;
     if (a.act_layout == LAYOUT_PLAIN) { epi = EPI_ACT; F = a.N; }
     else if (a.act_layout == LAYOUT_GPT_OSS) { epi = EPI_GPT_OSS; F = a.N / 2; if (a.N % 16) return SMOE_ERR_UNSUPPORTED; }
     else { epi = EPI_GLU_HALVES; F = a.N / 2; if (a.N % 16) return SMOE_ERR_UNSUPPORTED; }
     if (a.Y && (a.syn != 1 || a.sym % 8 || !al16(a.Y))) return SMOE_ERR_UNSUPPORTED;
+  }
+  if (a.act_bwd) {
+    // fused activation gradient: N = F hidden columns, U and Y (= dU) are (rows, n_up)
+    if (a.N <= 128 || a.U == nullptr || a.sum % 8 || !al16(a.U) || !a.x_grouped || !a.y_grouped || a.bias)
+      return SMOE_ERR_UNSUPPORTED;
+    epi = a.act_layout == LAYOUT_PLAIN ? EPI_BWD_PLAIN : (a.act_layout == LAYOUT_GPT_OSS ? EPI_BWD_GPT_OSS : EPI_BWD_GLU);
+    F = a.N;
   }
   const int BN = a.N > 128 ? 256 : 128;
   CUtensorMap map;
@@ -1300,6 +1453,10 @@ int launch_s2s_tc(const S2SArgs& a) {
   p.status = a.status;
   p.H = static_cast<uint8_t*>(a.H); p.h_row_bytes = a.shm * 2;
   p.F = F; p.glu_first = a.act_layout == LAYOUT_GLU_FIRST ? 1 : 0; p.act = a.act; p.alpha = a.alpha; p.limit = a.limit;
+  p.U = static_cast<const uint8_t*>(a.U); p.u_row_bytes = a.sum * 2;
+  // raster: about sqrt(tiles in flight * tile columns / tile rows) m-tiles per group (see decode_tile)
+  static const int group_m_env = env_int("SMOE_GROUP_M", 0);
+  p.group_m = group_m_env ? group_m_env : (BN == 256 ? 16 : 12);
 
   CUtensorMap map_x = map;   // placeholder when the rows are gathered: the kernel then never touches it
   p.a_by_tma = (a.x_grouped && !(a.flags & SMOE_FLAG_GATHER_ROWS) && a.sxm >= a.K &&
@@ -1311,7 +1468,7 @@ int launch_s2s_tc(const S2SArgs& a) {
   // mostly full. SMOE_FLAG_PAIR / SMOE_FLAG_NO_PAIR override the choice.
   const bool pair_auto = PAIR_BY_DEFAULT && a.R >= static_cast<int64_t>(a.E) * 4 * PAIR_ROWS;
   const bool want_pair = !(a.flags & SMOE_FLAG_NO_PAIR) && ((a.flags & SMOE_FLAG_PAIR) || pair_auto);
-  if (want_pair && p.a_by_tma && BN == 256) {
+  if (want_pair && p.a_by_tma && BN == 256 && epi < EPI_BWD_PLAIN) {
     CUtensorMap map_pair = map;
     bool okp = true;
     if (k_major && epi != EPI_GLU_HALVES)
@@ -1357,6 +1514,15 @@ int launch_s2s_tc(const S2SArgs& a) {
     case EPI_GPT_OSS:
       return k_major ? launch_s2s_cfg<256, true, EPI_GPT_OSS>(map, map_x, p, grid, a.stream)
                      : launch_s2s_cfg<256, false, EPI_GPT_OSS>(map, map_x, p, grid, a.stream);
+    case EPI_BWD_PLAIN:
+      return k_major ? launch_s2s_cfg<256, true, EPI_BWD_PLAIN>(map, map_x, p, grid, a.stream)
+                     : launch_s2s_cfg<256, false, EPI_BWD_PLAIN>(map, map_x, p, grid, a.stream);
+    case EPI_BWD_GLU:
+      return k_major ? launch_s2s_cfg<256, true, EPI_BWD_GLU>(map, map_x, p, grid, a.stream)
+                     : launch_s2s_cfg<256, false, EPI_BWD_GLU>(map, map_x, p, grid, a.stream);
+    case EPI_BWD_GPT_OSS:
+      return k_major ? launch_s2s_cfg<256, true, EPI_BWD_GPT_OSS>(map, map_x, p, grid, a.stream)
+                     : launch_s2s_cfg<256, false, EPI_BWD_GPT_OSS>(map, map_x, p, grid, a.stream);
     default: break;
   }
   if (BN == 256)
@@ -1392,6 +1558,25 @@ int launch_wgrad_tc(const WGradArgs& a) {
   p.K = a.K; p.N = a.N; p.E = a.E; p.fan_out = a.fan_out; p.is_bf16 = bf16 ? 1 : 0;
   p.idesc = make_idesc_f16(bf16, true, true, BM, BNW);
   p.status = a.status;
+  {
+    // Which operand's band stays in L2 (see the tile order in the kernel). The row count per expert is only
+    // known on the device; the average decides. Bytes read per expert: the banded operand once, the streamed
+    // one once per band.
+    static const int budget_mb = env_int("SMOE_L2_BAND_MB", 40);
+    const double rows = static_cast<double>(a.R) / a.E, budget = budget_mb * 1e6;
+    const int n_tiles = cdiv(a.N, BM), k_tiles = cdiv(a.K, BNW);
+    auto width = [&](int tiles, int tile_cols) {
+      const int fit = static_cast<int>(budget / (tile_cols * rows * 2.0 + 1.0));
+      const int w = fit < 1 ? 1 : (fit > tiles ? tiles : fit);
+      return cdiv(tiles, cdiv(tiles, w));          // equal-sized bands
+    };
+    const int wn = width(n_tiles, BM), wk = width(k_tiles, BNW);
+    const double dy_panel = a.N * rows * 2.0, x_panel = a.K * rows * 2.0;
+    const double bytes_over_n = dy_panel + x_panel * cdiv(n_tiles, wn);
+    const double bytes_over_k = x_panel + dy_panel * cdiv(k_tiles, wk);
+    p.band_over_n = bytes_over_n < bytes_over_k ? 1 : 0;
+    p.band = p.band_over_n ? wn : wk;
+  }
   const int64_t total = static_cast<int64_t>(a.E) * cdiv(a.N, BM) * cdiv(a.K, BNW);
   const int grid = static_cast<int>(total < di.sm_count ? total : di.sm_count);
   int rc = (BNW == 256) ? launch_wgrad_cfg<256>(map, map_x, p, grid, a.stream)

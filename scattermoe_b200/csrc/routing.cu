@@ -195,26 +195,18 @@ extern "C" size_t smoe_sort_count_workspace_bytes(int64_t R, int32_t E) {
   return static_cast<size_t>(nblk) * static_cast<size_t>(E) * sizeof(int32_t) + 256;
 }
 
-extern "C" int smoe_sort_count(const int64_t* expert_idxs, int64_t R, int32_t E, int64_t* sorted_expert_idxs,
-                               int64_t* sorted_scattered_idxs, int64_t* expert_offsets, void* workspace,
-                               size_t workspace_bytes, void* stream_) {
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  SMOE_CHECK_ARG(R >= 0 && R < (int64_t(1) << 31), "sort_count: R=%lld out of range [0, 2^31)", (long long)R);
-  SMOE_CHECK_ARG(E >= 1 && E <= SC_MAX_E, "sort_count: E=%d out of range [1, %d]", E, SC_MAX_E);
-  SMOE_CHECK_ARG(expert_offsets != nullptr, "sort_count: expert_offsets is null");
+// The three launches of the sort. `block_hist` holds ceil(R / SC_CHUNK) * E ints; the caller has checked its size.
+static int sort_count_launch(const char* who, const int64_t* expert_idxs, int64_t R, int32_t E,
+                             int64_t* sorted_expert_idxs, int64_t* sorted_scattered_idxs, int64_t* expert_offsets,
+                             int32_t* block_hist, cudaStream_t stream) {
+  SMOE_CHECK_ARG(expert_offsets != nullptr, "%s: expert_offsets is null", who);
   if (R == 0) {
     zero_offsets_kernel<<<cdiv(E, 256), 256, 0, stream>>>(expert_offsets, E);
     SMOE_LAUNCH_CHECK();
     return SMOE_OK;
   }
-  SMOE_CHECK_ARG(expert_idxs && sorted_expert_idxs && sorted_scattered_idxs, "sort_count: null pointer");
-  if (workspace == nullptr || workspace_bytes < smoe_sort_count_workspace_bytes(R, E)) {
-    set_error("sort_count: workspace of %zu bytes needed, %zu given", smoe_sort_count_workspace_bytes(R, E),
-              workspace_bytes);
-    return SMOE_ERR_WORKSPACE;
-  }
+  SMOE_CHECK_ARG(expert_idxs && sorted_expert_idxs && sorted_scattered_idxs && block_hist, "%s: null pointer", who);
   const int nblk = static_cast<int>(cdiv64(R, SC_CHUNK));
-  int32_t* block_hist = static_cast<int32_t*>(workspace);
   const size_t smem = static_cast<size_t>(SC_WARPS) * E * sizeof(int32_t);
   if (smem > 48 * 1024) {
     static thread_local int configured_device = -1;
@@ -236,6 +228,20 @@ extern "C" int smoe_sort_count(const int64_t* expert_idxs, int64_t R, int32_t E,
                                                         sorted_expert_idxs, sorted_scattered_idxs);
   SMOE_LAUNCH_CHECK();
   return SMOE_OK;
+}
+
+extern "C" int smoe_sort_count(const int64_t* expert_idxs, int64_t R, int32_t E, int64_t* sorted_expert_idxs,
+                               int64_t* sorted_scattered_idxs, int64_t* expert_offsets, void* workspace,
+                               size_t workspace_bytes, void* stream_) {
+  SMOE_CHECK_ARG(R >= 0 && R < (int64_t(1) << 31), "sort_count: R=%lld out of range [0, 2^31)", (long long)R);
+  SMOE_CHECK_ARG(E >= 1 && E <= SC_MAX_E, "sort_count: E=%d out of range [1, %d]", E, SC_MAX_E);
+  if (R > 0 && (workspace == nullptr || workspace_bytes < smoe_sort_count_workspace_bytes(R, E))) {
+    set_error("sort_count: workspace of %zu bytes needed, %zu given", smoe_sort_count_workspace_bytes(R, E),
+              workspace_bytes);
+    return SMOE_ERR_WORKSPACE;
+  }
+  return sort_count_launch("sort_count", expert_idxs, R, E, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
+                           static_cast<int32_t*>(workspace), static_cast<cudaStream_t>(stream_));
 }
 
 extern "C" int smoe_offsets_from_sorted(const int64_t* sorted_expert_idxs, int64_t R, int32_t E,
@@ -266,8 +272,10 @@ extern "C" int smoe_sort_count_static(const int64_t* expert_idxs, int64_t R, int
   }
   int32_t* scratch = nullptr;
   if (int rc = static_scratch_address(&scratch)) return rc;
-  // Same kernels as smoe_sort_count. The histogram pass writes every scratch entry the later passes read, so
-  // nothing left behind by an earlier call needs clearing.
-  return smoe_sort_count(expert_idxs, R, E, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, scratch,
-                         static_cast<size_t>(SC_STATIC_INTS) * sizeof(int32_t), stream);
+  // Same kernels as smoe_sort_count, on the built-in array: its SC_STATIC_INTS entries are exactly what the capacity
+  // check above admits (the caller-workspace entry point asks for 256 spare bytes that the kernels never touch).
+  // The histogram pass writes every scratch entry the later passes read, so nothing left behind by an earlier
+  // call needs clearing.
+  return sort_count_launch("sort_count_static", expert_idxs, R, E, sorted_expert_idxs, sorted_scattered_idxs,
+                           expert_offsets, scratch, static_cast<cudaStream_t>(stream));
 }

@@ -68,13 +68,16 @@ struct S2SArgs {
   const void* bias; int64_t sbe, sbn;
   void* Y; int64_t sym, syn;
   const int64_t* sorted_e; const int64_t* sorted_idx; const int64_t* offsets;
-  int64_t R; int K, N, E, fan_out, x_grouped, y_grouped, dtype, flags, epilogue;
+  int64_t R; int K, N, E, fan_out, x_grouped, y_grouped, dtype, flags;
   int32_t* status;
   cudaStream_t stream;
   // fused activation epilogue (tensor-core kernel only): act_layout < 0 = none, else a LAYOUT_* of act_math.cuh
   void* H = nullptr; int64_t shm = 0;
   int act_layout = -1, act = 0;
   float alpha = 0.f, limit = 0.f;
+  // fused activation-gradient epilogue: U = saved up-projection (rows, n_up); Y then receives dU, N is F
+  const void* U = nullptr; int64_t sum = 0;
+  int act_bwd = 0;
 };
 
 struct WGradArgs {

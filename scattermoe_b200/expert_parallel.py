@@ -248,7 +248,24 @@ class PeerRowBuffers:
         self.epoch += 1
         with torch.cuda.device(self.device):
             _ep_call("smoe_ep_barrier", self.ptrs["flags"], self.rank, self.world, self.epoch,
-                     _lib.status_word(self.device).data_ptr(), _lib.stream_ptr(self.device))
+                     int(BARRIER_LIMIT_CYCLES), _lib.status_word(self.device).data_ptr(), _lib.stream_ptr(self.device))
+
+    def poison_if_a_wait_expired(self, *tensors):
+        """After the last barrier of a pass: results computed on the strength of a barrier that gave up waiting become
+        NaN (a kernel that reads the status word on the device; no host synchronisation). The status word itself is
+        read by `scattermoe_b200.check_device_status()`, which callers should run before `optimizer.step()`."""
+        from . import _lib
+        with torch.cuda.device(self.device):
+            for t in tensors:
+                if t is not None and t.numel():
+                    _ep_call("smoe_status_poison", _lib.status_word(self.device).data_ptr(), t.data_ptr(),
+                             t.numel() * t.element_size(), _lib.stream_ptr(self.device))
+
+
+# Wait limit of the peer-memory barrier in SM clocks (0: the library's default, about one second). A rank that is
+# late by more than this (a long host stall between forward and backward, say) makes the others' barrier give up:
+# their step then yields NaNs and sets the status word, it does not hang and it does not return plausible numbers.
+BARRIER_LIMIT_CYCLES = 0
 
 
 def _ep_call(name, *args):
@@ -298,18 +315,26 @@ class _PeerExchangeMLP(torch.autograd.Function):
         cap = bufs.capacity
         dummy = layer.dummy_index(cap, dev)
         xb = bufs.local["x"]
-        up = ops.scatter2scatter(xb, w_up.permute(0, 2, 1), dummy, dummy, 1, x_grouped=True, y_grouped=True,
-                                 expert_offsets=local_offsets)
-        hidden = torch.empty((cap, w_down.size(2)), dtype=x.dtype, device=dev)
-        _act._call(False, up, None, hidden, hidden.size(1), _act.LAYOUT_GLU_SECOND, layer.act_code, 1.702, 7.0, rows_dev)
+        fused = ops.scatter2scatter_act(xb, w_up.permute(0, 2, 1), dummy, dummy, 1, _act.LAYOUT_GLU_SECOND,
+                                        layer.act_code, x_grouped=True, expert_offsets=local_offsets)
+        if fused is None:       # not a tensor-core case: the grouped GEMM, then the activation kernel
+            up = ops.scatter2scatter(xb, w_up.permute(0, 2, 1), dummy, dummy, 1, x_grouped=True, y_grouped=True,
+                                     expert_offsets=local_offsets)
+            hidden = torch.empty((cap, w_down.size(2)), dtype=x.dtype, device=dev)
+            _act._call(False, up, None, hidden, hidden.size(1), _act.LAYOUT_GLU_SECOND, layer.act_code, 1.702, 7.0,
+                       rows_dev)
+        else:
+            up, hidden = fused
         y_rows = ops.scatter2scatter(hidden, w_down.permute(0, 2, 1), dummy, dummy, 1, x_grouped=True, y_grouped=True,
                                      expert_offsets=local_offsets)
         # 5. results go home: one row per (token, slot) into the token owner's slot-ordered buffer
         with torch.cuda.device(dev):
             _ep_call("smoe_ep_return", y_rows.data_ptr(), y_rows.stride(0), bufs.local["ret"].data_ptr(),
-                     rows_dev.data_ptr(), cap, bufs.ptrs["yslot"], bufs.width, bufs.slot_rows, d, W, code, stream)
+                     rows_dev.data_ptr(), cap, bufs.ptrs["yslot"], bufs.width, bufs.slot_rows, d, W, rank, e_local, code,
+                     stream)
         bufs.barrier()
         out = ops.topk_reduce(bufs.local["yslot"], gates, T, k)
+        bufs.poison_if_a_wait_expired(out)
         layer.last_rows_dev = rows_dev          # live rows of the local buffers (device scalar), for accounting
         ctx.layer = layer
         ctx.shape = (T, k, d)
@@ -342,20 +367,21 @@ class _PeerExchangeMLP(torch.autograd.Function):
         xb, gb = bufs.local["x"], bufs.local["g"]
         e_local = w_up.size(0)
         # input-gradient chain first, its rows start travelling home ...
-        d_hidden = ops.scatter2scatter(gb, w_down, dummy, dummy, 1, x_grouped=True, y_grouped=True,
-                                       expert_offsets=local_offsets)
-        d_up = torch.empty_like(up)
-        _act._call(True, up, d_hidden, d_up, hidden.size(1), _act.LAYOUT_GLU_SECOND, layer.act_code, 1.702, 7.0, rows_dev)
+        # (input gradient of the down-projection and the activation gradient in one launch where the tensor-core
+        # kernel applies; only the live rows, which the expert offsets delimit, are read or written)
+        d_up = ops.scatter2scatter_act_bwd(gb, w_down, up, local_offsets, _act.LAYOUT_GLU_SECOND, layer.act_code)
         dx_rows = ops.scatter2scatter(d_up, w_up, dummy, dummy, 1, x_grouped=True, y_grouped=True,
                                       expert_offsets=local_offsets)
         with torch.cuda.device(dev):
             _ep_call("smoe_ep_return", dx_rows.data_ptr(), dx_rows.stride(0), bufs.local["ret"].data_ptr(),
-                     rows_dev.data_ptr(), cap, bufs.ptrs["dxslot"], bufs.width, bufs.slot_rows, d, W, code, stream)
+                     rows_dev.data_ptr(), cap, bufs.ptrs["dxslot"], bufs.width, bufs.slot_rows, d, W, rank, e_local, code,
+                     stream)
         # ... while the two weight gradients run: the barrier that follows them finds the peers' rows already here
         d_w_down, _ = ops.group_bwd_W(gb, hidden, local_offsets, e_local)
         d_w_up, _ = ops.group_bwd_W(d_up, xb, local_offsets, e_local)
         bufs.barrier()
         dx = ops.topk_reduce(bufs.local["dxslot"], None, T, k) if k > 1 else bufs.local["dxslot"].clone()
+        bufs.poison_if_a_wait_expired(dx, d_gates, d_w_up, d_w_down)
         # weight gradients come back as (E, K, N) views of (E, N, K) buffers = the parameters' own layout
         return dx, d_gates, None, d_w_up.permute(0, 2, 1), d_w_down.permute(0, 2, 1), None
 

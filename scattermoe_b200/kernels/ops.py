@@ -94,7 +94,7 @@ def _scatter2scatter_impl(output, W, X, k, sorted_expert_idxs, sorted_scattered_
             output.data_ptr(), output.stride(0), output.stride(1),
             se.data_ptr(), ss.data_ptr(), off.data_ptr(),
             se.numel(), X.size(1), output.size(1), E, k,
-            int(x_grouped), int(y_grouped), _dtype_code(X), _flags(), 0,
+            int(x_grouped), int(y_grouped), _dtype_code(X), _flags(),
             _lib.status_word(X.device).data_ptr(), _lib.stream_ptr(X.device))
     _lib.check(rc, "smoe_scatter2scatter")
 
@@ -197,6 +197,66 @@ def scatter2scatter_act(X, W, sorted_expert_idxs, sorted_scattered_idxs, k, act_
                                      expert_offsets, act_layout, act, alpha, limit):
         return None
     return up, hidden
+
+
+def _scatter2scatter_act_bwd_impl(d_up, DY, W, up, expert_offsets, act_layout, act, alpha, limit) -> bool:
+    """One launch writing `d_up` = activation gradient of (DY @ W) with respect to the saved up-projection `up`.
+    False: the request does not fit the tensor-core kernel and nothing was launched."""
+    _lib.require_cuda(DY, "DY")
+    if FORCE_PATH == "simt" or DY.dtype not in (torch.bfloat16, torch.float16) or W.dtype != DY.dtype:
+        return False
+    if up.dtype != DY.dtype or up.stride(1) != 1 or d_up.stride(1) != 1 or d_up.shape != up.shape:
+        return False
+    off = _i64(expert_offsets)
+    with torch.cuda.device(DY.device):
+        rc = _lib.load().smoe_scatter2scatter_act_bwd(
+            DY.data_ptr(), DY.stride(0), DY.stride(1),
+            W.data_ptr(), W.stride(0), W.stride(1), W.stride(2),
+            up.data_ptr(), up.stride(0), d_up.data_ptr(), d_up.stride(0),
+            off.data_ptr(), DY.size(0), DY.size(1), W.size(-1), W.size(0), _dtype_code(DY), _flags(),
+            act_layout, act, float(alpha), float(limit),
+            _lib.status_word(DY.device).data_ptr(), _lib.stream_ptr(DY.device))
+    if rc == _lib.SMOE_ERR_UNSUPPORTED:
+        return False
+    _lib.check(rc, "smoe_scatter2scatter_act_bwd")
+    return True
+
+
+@torch.library.custom_op("scattermoe_b200::scatter2scatter_act_bwd", mutates_args={"d_up"})
+def scatter2scatter_act_bwd_compileable(d_up: torch.Tensor, DY: torch.Tensor, W: torch.Tensor, up: torch.Tensor,
+                                        expert_offsets: torch.Tensor, act_layout: int, act: int, alpha: float,
+                                        limit: float) -> None:
+    """Traceable form: always fills `d_up`, by the fused kernel when it applies, else by the grouped GEMM followed by
+    the activation-gradient kernel."""
+    _scatter2scatter_act_bwd_fill(d_up, DY, W, up, expert_offsets, act_layout, act, alpha, limit)
+
+
+def _scatter2scatter_act_bwd_fill(d_up, DY, W, up, expert_offsets, act_layout, act, alpha, limit):
+    if _scatter2scatter_act_bwd_impl(d_up, DY, W, up, expert_offsets, act_layout, act, alpha, limit):
+        return
+    from .. import activation as _act
+    R = DY.size(0)
+    d_hidden = torch.empty((R, W.size(-1)), device=DY.device, dtype=DY.dtype)
+    # rows are in expert order on both sides: the index tensors are not read
+    dummy = expert_offsets.new_zeros(R)
+    _scatter2scatter_impl(d_hidden, W, DY, 1, dummy, dummy, None, True, True, expert_offsets)
+    _act._call(True, up, d_hidden, d_up, d_hidden.size(1), act_layout, act, alpha, limit)
+
+
+def scatter2scatter_act_bwd(DY, W, up, expert_offsets, act_layout, act, alpha=1.702, limit=7.0):
+    """Gradient of the up-projection `up` (rows, n_up) given the gradient `DY` (rows, K) of the down-projection's
+    OUTPUT, rows in expert order: d_up = activation'(up) applied to DY @ W, with W the (E, K, F) transposed view of
+    the down-projection weight. One tensor-core launch whose epilogue applies the activation gradient (the
+    autograd of scattermoe/mlp.py:41 / :81-87 fused into the grouped GEMM of scattermoe/parallel_experts.py:110-116);
+    the (rows, F) hidden gradient is not materialised. Falls back to the two separate kernels when the request does
+    not fit the tensor-core kernel."""
+    d_up = torch.empty_like(up)
+    if torch.compiler.is_compiling():
+        scatter2scatter_act_bwd_compileable(d_up, DY, W, up, expert_offsets, act_layout, act, float(alpha),
+                                            float(limit))
+    else:
+        _scatter2scatter_act_bwd_fill(d_up, DY, W, up, expert_offsets, act_layout, act, alpha, limit)
+    return d_up
 
 
 # --------------------------------------------------------------------------------------------------

@@ -10,7 +10,7 @@ from torch import nn
 
 from . import _lib
 from . import activation as _act
-from .parallel_experts import ParallelExperts, flatten_sort_count, parallel_linear_act
+from .parallel_experts import ParallelExperts, expert_mlp, flatten_sort_count
 
 
 class _ExpertMLPBase(nn.Module):
@@ -41,15 +41,17 @@ class _ExpertMLPBase(nn.Module):
         tokens = x.view(-1, x.shape[-1])            # any leading shape, restored on return (mlp.py:30-31, :48)
         routing = flatten_sort_count(expert_idxs, num_experts=self.num_experts)
         code = _act.resolve_activation(self.activation) if _act.FUSE else None
-        if code is not None and _lib.on_device(tokens):
-            # up-projection and activation as one autograd node (activation in the GEMM epilogue when the tensor-core
-            # kernel applies, a separate one-pass kernel otherwise)
-            hidden = parallel_linear_act(tokens, self.experts.weight.permute(0, 2, 1), self.top_k, *routing,
-                                         self.act_layout, code, expert_biases=self.experts.bias)
+        if code is not None and expert_p is not None and _lib.on_device(tokens):
+            # the whole expert MLP as one autograd node: activation in the epilogue of the up-projection GEMM,
+            # activation gradient in the epilogue of the down-projection's input-gradient GEMM (tensor-core cases;
+            # separate one-pass kernels otherwise)
+            y = expert_mlp(tokens, self.experts.weight.permute(0, 2, 1), self.output_experts.weight.permute(0, 2, 1),
+                           expert_p.reshape(tokens.size(0), -1), self.top_k, *routing, self.act_layout, code,
+                           up_biases=self.experts.bias, down_biases=self.output_experts.bias)
         else:
             up = self.experts(tokens, self.top_k, *routing, grouped_out=True)
             hidden = self._activate(up)
-        y = self.output_experts(hidden, 1, *routing, grouped_in=True, gates=expert_p)
+            y = self.output_experts(hidden, 1, *routing, grouped_in=True, gates=expert_p)
         return y.view(*lead, y.size(-1))
 
 

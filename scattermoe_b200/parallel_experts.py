@@ -231,6 +231,91 @@ class ParallelLinearAct(torch.autograd.Function):
         return (d_input, d_weights, None, None, None, None, d_biases, None, None, None, None)
 
 
+class ExpertMLP(torch.autograd.Function):
+    """Both expert linears, the activation between them and the gate-weighted top-k sum as ONE autograd node, so that
+    backward can fuse across the two linears: the input gradient of the down-projection and the activation
+    gradient run as one tensor-core launch (`kernels.ops.scatter2scatter_act_bwd`) and the hidden gradient is never
+    written. Computes what `ParallelLinear(grouped_out=True)` -> activation -> `ParallelLinear(grouped_in=True,
+    gates=...)` compute (scattermoe/mlp.py:33-47, :74-93; scattermoe/parallel_experts.py:27-134), with the same
+    saved tensors: the up-projection, the hidden rows and the un-weighted per-slot outputs (the reference's
+    `output_expanded`, :45), whose storage backward reuses for the expert-order gradient copy as the reference
+    does (:82)."""
+
+    @staticmethod
+    def forward(ctx, x, w_up, b_up, w_down, b_down, gates, k, sorted_expert_idxs, sorted_scattered_idxs,
+                expert_offsets, act_layout, act, alpha, limit):
+        x = _rowmajor(x)
+        T = x.size(0)
+        x_src, kk, grouped = x, k, False
+        if GROUP_INPUT_COPY and x.size(1) % 8 == 0 and x.dtype in (torch.bfloat16, torch.float16):
+            x_src, kk, grouped = kernels.ops.group(x, sorted_scattered_idxs, fan_out=k), 1, True
+        res = kernels.ops.scatter2scatter_act(x_src, w_up, sorted_expert_idxs, sorted_scattered_idxs, kk, act_layout,
+                                              act, b=b_up, x_grouped=grouped, expert_offsets=expert_offsets,
+                                              alpha=alpha, limit=limit)
+        if res is None:     # not a tensor-core case: the two separate kernels
+            up = kernels.ops.scatter2scatter(x_src, w_up, sorted_expert_idxs, sorted_scattered_idxs, kk, b=b_up,
+                                             x_grouped=grouped, y_grouped=True, expert_offsets=expert_offsets)
+            F = up.size(1) if act_layout == _act.LAYOUT_PLAIN else up.size(1) // 2
+            hidden = torch.empty((up.size(0), F), dtype=up.dtype, device=up.device)
+            _act.activation_forward(up, hidden, F, act_layout, act, alpha, limit)
+        else:
+            up, hidden = res
+        per_slot = kernels.ops.scatter2scatter(hidden, w_down, sorted_expert_idxs, sorted_scattered_idxs, 1, b=b_down,
+                                               x_grouped=True, y_grouped=False, expert_offsets=expert_offsets)
+        out = kernels.ops.topk_reduce(per_slot, gates, T, k)
+        ctx.save_for_backward(x, w_up, b_up, w_down, b_down, gates, sorted_expert_idxs, sorted_scattered_idxs,
+                              expert_offsets, up, hidden, per_slot, x_src if grouped else None)
+        ctx.cfg = (k, act_layout, act, alpha, limit)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        (x, w_up, b_up, w_down, b_down, gates, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, up, hidden,
+         per_slot, x_in_expert_order) = ctx.saved_tensors
+        k, act_layout, act, alpha, limit = ctx.cfg
+        T, E = x.size(0), w_up.size(0)
+        need = ctx.needs_input_grad
+        grad_out = _rowmajor(grad_out)
+        if grad_out.dtype != x.dtype:
+            grad_out = grad_out.to(x.dtype)
+        d_gates = kernels.ops.gate_grad(per_slot, grad_out, T, k).to(gates.dtype) if need[5] else None
+        d_x = d_w_up = d_b_up = d_w_down = d_b_down = None
+        if need[0] or need[1] or need[2] or need[3] or need[4]:
+            # gate-scaled output gradient in expert order; written over the per-slot outputs, which nothing reads
+            # after the gate gradient (a traced backward must not write into a tensor saved by forward)
+            grouped_grad = kernels.ops.group(grad_out, sorted_scattered_idxs, fan_out=k, coeff=gates.flatten(),
+                                             out=None if torch.compiler.is_compiling() else per_slot)
+            if need[3] or (b_down is not None and need[4]):
+                d_w_down, d_b_down = kernels.ops.group_bwd_W(DY=grouped_grad, X=hidden, expert_offsets=expert_offsets,
+                                                             E=E, has_bias=b_down is not None)
+            if need[0] or need[1] or (b_up is not None and need[2]):
+                d_up = kernels.ops.scatter2scatter_act_bwd(grouped_grad, w_down.permute(0, 2, 1), up, expert_offsets,
+                                                           act_layout, act, alpha, limit)
+                if need[1] or (b_up is not None and need[2]):
+                    grouped = x_in_expert_order is not None
+                    d_w_up, d_b_up = kernels.ops.group_bwd_W(
+                        DY=d_up, X=x_in_expert_order if grouped else x, expert_offsets=expert_offsets, E=E,
+                        has_bias=b_up is not None, x_gather_idx=None if grouped else sorted_scattered_idxs,
+                        fan_out=1 if grouped else k)
+                if need[0]:
+                    d_expanded = kernels.ops.scatter2scatter(
+                        X=d_up, x_grouped=True, W=w_up.permute(0, 2, 1), sorted_expert_idxs=sorted_expert_idxs,
+                        sorted_scattered_idxs=sorted_scattered_idxs, k=1, y_grouped=False,
+                        expert_offsets=expert_offsets)
+                    d_x = d_expanded if k == 1 else kernels.ops.topk_reduce(d_expanded, None, T, k)
+        return (d_x, d_w_up, d_b_up, d_w_down, d_b_down, d_gates, None, None, None, None, None, None, None, None)
+
+
+def expert_mlp(inputs, up_weights, down_weights, gates, k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
+               act_layout, act, up_biases=None, down_biases=None, alpha=1.702, limit=7.0):
+    """The whole expert MLP of one MoE layer as one autograd node (an addition to the reference's surface):
+    `parallel_linear(grouped_out=True)` -> activation -> `parallel_linear(grouped_in=True, gates=gates)`.
+    `up_weights` is (E, in, n_up), `down_weights` (E, hidden, in), any stride order; `gates` (T, k); layout / function
+    codes as in `scattermoe_b200.activation`. Input in token order."""
+    return ExpertMLP.apply(inputs, up_weights, up_biases, down_weights, down_biases, gates, k, sorted_expert_idxs,
+                           sorted_scattered_idxs, expert_offsets, act_layout, act, float(alpha), float(limit))
+
+
 def parallel_linear_act(inputs, expert_weights, k, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
                         act_layout, act, expert_biases=None, alpha=1.702, limit=7.0):
     """`parallel_linear(..., grouped_out=True)` followed by the activation, as one autograd node (an addition to the

@@ -21,7 +21,7 @@ from torch.nn import functional as F
 
 from .. import _lib
 from .. import activation as _act
-from ..parallel_experts import flatten_sort_count, parallel_linear, parallel_linear_act
+from ..parallel_experts import expert_mlp, flatten_sort_count, parallel_linear
 
 PATCHED = {}      # class name -> original forward
 
@@ -69,15 +69,16 @@ try:
             selected = routing_weights                                                  # already (T, k)
         routing = flatten_sort_count(router_indices.flatten(), num_experts=self.num_experts)
         if _act.FUSE:
-            gated = parallel_linear_act(tokens, self.gate_up_proj, k, *routing, _act.LAYOUT_GPT_OSS, _act.ACT_SILU,
-                                        expert_biases=self.gate_up_proj_bias, alpha=self.alpha, limit=self.limit)
+            out = expert_mlp(tokens, self.gate_up_proj, self.down_proj, selected.to(tokens.dtype), k, *routing,
+                             _act.LAYOUT_GPT_OSS, _act.ACT_SILU, up_biases=self.gate_up_proj_bias,
+                             down_biases=self.down_proj_bias, alpha=self.alpha, limit=self.limit)
         else:
             gate_up = parallel_linear(tokens, self.gate_up_proj, k, *routing,
                                       expert_biases=self.gate_up_proj_bias, grouped_in=False, grouped_out=True)
             gated = gpt_oss_glu(gate_up, self.alpha, self.limit)
-        out = parallel_linear(gated, self.down_proj, 1, *routing,
-                              expert_biases=self.down_proj_bias, grouped_in=True, grouped_out=False,
-                              gates=selected.to(tokens.dtype))
+            out = parallel_linear(gated, self.down_proj, 1, *routing,
+                                  expert_biases=self.down_proj_bias, grouped_in=True, grouped_out=False,
+                                  gates=selected.to(tokens.dtype))
         return out.view(batch_size, -1, self.hidden_size)
 except Exception:  # transformers absent or without this model
     logging.info("Failed to replace GptOssExperts")
@@ -115,11 +116,12 @@ try:
                                  grouped_in=False, grouped_out=True)
             gate_half, linear_half = up.chunk(2, dim=-1)
             hidden = self.activation(gate_half) * linear_half
+            layer_output = parallel_linear(hidden, self.output_linear.weight.transpose(2, 1), 1, *routing,
+                                           grouped_in=True, grouped_out=False, gates=probs)
         else:
-            hidden = parallel_linear_act(tokens, self.input_linear.weight.transpose(2, 1), self.router.top_k, *routing,
-                                         _act.LAYOUT_GLU_FIRST, code)
-        layer_output = parallel_linear(hidden, self.output_linear.weight.transpose(2, 1), 1, *routing,
-                                       grouped_in=True, grouped_out=False, gates=probs)
+            layer_output = expert_mlp(tokens, self.input_linear.weight.transpose(2, 1),
+                                      self.output_linear.weight.transpose(2, 1), probs, self.router.top_k, *routing,
+                                      _act.LAYOUT_GLU_FIRST, code)
         layer_output = layer_output.view(bsz, length, emb_size)
         if GRANITE_RETURNS_ROUTER_LOGITS:
             return layer_output, router_logits
@@ -146,11 +148,12 @@ def _fused_glu_experts_forward(cls_name):
             up = parallel_linear(tokens, self.gate_up_proj.transpose(2, 1), k, *routing, grouped_in=False, grouped_out=True)
             gate_half, linear_half = up.chunk(2, dim=-1)
             hidden = self.act_fn(gate_half) * linear_half
+            out = parallel_linear(hidden, self.down_proj.transpose(2, 1), 1, *routing, grouped_in=True,
+                                  grouped_out=False, gates=top_k_weights.reshape(tokens.size(0), k).to(tokens.dtype))
         else:
-            hidden = parallel_linear_act(tokens, self.gate_up_proj.transpose(2, 1), k, *routing, _act.LAYOUT_GLU_FIRST,
-                                         code)
-        out = parallel_linear(hidden, self.down_proj.transpose(2, 1), 1, *routing, grouped_in=True, grouped_out=False,
-                              gates=top_k_weights.reshape(tokens.size(0), k).to(tokens.dtype))
+            out = expert_mlp(tokens, self.gate_up_proj.transpose(2, 1), self.down_proj.transpose(2, 1),
+                             top_k_weights.reshape(tokens.size(0), k).to(tokens.dtype), k, *routing,
+                             _act.LAYOUT_GLU_FIRST, code)
         return out.view(shape)
     forward.__name__ = "fused_glu_experts_forward_" + cls_name
     return forward

@@ -30,7 +30,7 @@ def test_header_symbols_are_exported_and_bound():
 
 
 def test_version_and_library_location():
-    assert _lib.load().smoe_version() == 1
+    assert _lib.load().smoe_version() == _lib.ABI_VERSION == 2
     path = scattermoe_b200.library_path()
     assert os.path.dirname(path) == os.path.join(ROOT, "scattermoe_b200"), "the library must live in-tree"
 
@@ -48,7 +48,7 @@ def test_argument_validation_needs_no_device():
     assert rc == _lib.SMOE_ERR_BAD_ARG and "dtype" in _lib.last_error()
     # index length must be rows * fan_out (reference assertion, ops.py:124-125)
     rc = lib.smoe_scatter2scatter(None, 3, 8, 1, None, 0, 0, 0, None, 0, 0, None, 8, 1, None, None, None,
-                                  7, 8, 8, 2, 2, 0, 0, 0, 0, 0, None, None)
+                                  7, 8, 8, 2, 2, 0, 0, 0, 0, None, None)
     assert rc == _lib.SMOE_ERR_BAD_ARG
     with pytest.raises(AssertionError):
         _lib.check(rc, "smoe_scatter2scatter")

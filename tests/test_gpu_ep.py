@@ -59,7 +59,7 @@ def test_single_rank_equals_glumlp():
     sm.check_device_status(dev)
 
 
-def _worker(rank, world, port, ret, peer=False, chunks=1):
+def _worker(rank, world, port, ret, peer=False, chunks=1, problem=None):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
     dev = torch.device("cuda", rank)
@@ -68,7 +68,7 @@ def _worker(rank, world, port, ret, peer=False, chunks=1):
     try:
         import scattermoe_b200 as sm
         from scattermoe_b200.expert_parallel import ExpertParallelGLUMLP, PeerExpertParallelGLUMLP
-        x, p, idx, w1, w2, dy = _problem()
+        x, p, idx, w1, w2, dy = _problem(**(problem or {}))
         T, E = x.size(0), w1.size(0)
         tl, el = T // world, E // world
         ts, es = slice(rank * tl, (rank + 1) * tl), slice(rank * el, (rank + 1) * el)
@@ -98,14 +98,15 @@ def _worker(rank, world, port, ret, peer=False, chunks=1):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("problem", [None, dict(T=1024, d=256, F=128, E=16, k=8, seed=9)], ids=["k2_E8", "k8_E16"])
 @pytest.mark.parametrize("peer,chunks", [(False, 1), (True, 1), (True, 2)],
                          ids=["nccl_all_to_all", "nvlink_peer_memory", "nvlink_peer_memory_2_chunks"])
-def test_two_ranks_equal_the_single_gpu_layer(peer, chunks):
+def test_two_ranks_equal_the_single_gpu_layer(peer, chunks, problem):
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         ret = mgr.dict()
-        procs = [ctx.Process(target=_worker, args=(r, 2, port, ret, peer, chunks)) for r in range(2)]
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, ret, peer, chunks, problem)) for r in range(2)]
         for q in procs:
             q.start()
         for q in procs:
@@ -115,3 +116,41 @@ def test_two_ranks_equal_the_single_gpu_layer(peer, chunks):
                 q.terminate()
                 raise AssertionError("a rank did not finish")
         assert {r: ret.get(r) for r in range(2)} == {0: "ok", 1: "ok"}
+
+
+def test_barrier_that_nobody_answers_gives_up_and_is_loud():
+    """A bounded wait that runs out (a flag that nothing sets; no fault, no hang): the kernel returns, the status
+    word says which peer stayed silent, `check_device_status` raises, and `smoe_status_poison` turns results that
+    were computed on the strength of that barrier into NaNs. One GPU plays rank 0 of a world of 2 whose rank 1 never
+    signals (both entries of the flag table point at the same local array; slot 1 of it is never written)."""
+    import ctypes
+    import scattermoe_b200 as sm
+    from scattermoe_b200 import _lib
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    sm.check_device_status(dev)
+    flags = torch.zeros(8, dtype=torch.int32, device=dev)
+    table = (ctypes.c_void_p * 2)(flags.data_ptr(), flags.data_ptr())
+    status = _lib.status_word(dev)
+    results = torch.ones(1000, dtype=torch.bfloat16, device=dev)[3:]          # deliberately not 16-byte aligned
+    untouched = torch.ones(64, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        # nothing expired yet: the poison kernel must leave the buffer alone
+        assert lib.smoe_status_poison(status.data_ptr(), untouched.data_ptr(), untouched.numel() * 4,
+                                      _lib.stream_ptr(dev)) == 0
+        rc = lib.smoe_ep_barrier(table, 0, 2, 1, 5_000_000, status.data_ptr(), _lib.stream_ptr(dev))   # ~3 ms of clocks
+        assert rc == 0, _lib.last_error()
+        assert lib.smoe_status_poison(status.data_ptr(), results.data_ptr(), results.numel() * 2,
+                                      _lib.stream_ptr(dev)) == 0
+    torch.cuda.synchronize()                      # the kernel returned
+    assert status.tolist() == [2, 100, 1, 1]
+    assert bool((untouched == 1).all())
+    assert bool(torch.isnan(results.float()).all())
+    with pytest.raises(RuntimeError, match="gave up waiting"):
+        sm.check_device_status(dev)
+    sm.check_device_status(dev)                   # the word was cleared by the check
+    # a barrier every party answers passes: world of 1
+    one = (ctypes.c_void_p * 1)(flags.data_ptr())
+    with torch.cuda.device(dev):
+        assert lib.smoe_ep_barrier(one, 0, 1, 2, 0, status.data_ptr(), _lib.stream_ptr(dev)) == 0
+    sm.check_device_status(dev)

@@ -230,8 +230,25 @@ def test_activation_resolution():
     assert A.resolve_activation(nn.ReLU()) == A.ACT_RELU
     assert A.resolve_activation(nn.Identity()) == A.ACT_IDENTITY
     assert A.resolve_activation(nn.Tanh()) is None and A.resolve_activation(lambda t: t) is None
-    from transformers.activations import ACT2FN
+    from transformers.activations import ACT2FN, GELUActivation
     assert A.resolve_activation(ACT2FN["silu"]) == A.ACT_SILU
+    assert A.resolve_activation(ACT2FN["gelu"]) == A.ACT_GELU_ERF
+    assert A.resolve_activation(ACT2FN["gelu_pytorch_tanh"]) == A.ACT_GELU_TANH
+    assert A.resolve_activation(GELUActivation(use_gelu_python=True)) is None
+    assert A.resolve_activation(ACT2FN["gelu_new"]) is None
+
+    class Swish(nn.Module):                 # same name as a fused function, different arithmetic: must not be fused
+        def __init__(self, beta):
+            super().__init__()
+            self.beta = beta
+
+        def forward(self, t):
+            return t * torch.sigmoid(self.beta * t)
+
+    class MySiLU(nn.SiLU):
+        def forward(self, t):
+            return 2 * super().forward(t)
+    assert A.resolve_activation(Swish(1.5)) is None and A.resolve_activation(MySiLU()) is None
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -360,3 +377,164 @@ def test_cta_pair_kernel_equals_single_cta_kernel(case, w_layout):
         ops.FORCE_PATH, ops.PAIR = None, None
     for single, paired in zip(*results):
         assert torch.equal(single, paired)
+
+
+def _act_reference(layout, act, up):
+    fn = {"gelu": torch.nn.functional.gelu, "silu": torch.nn.functional.silu, None: None}[act]
+    if layout == "plain":
+        return fn(up)
+    if layout == "glu_second":
+        return oracle.act_glu_second_half(up, fn)
+    if layout == "glu_first":
+        return oracle.act_glu_first_half(up, fn)
+    return oracle.act_gpt_oss(up)
+
+
+def _act_codes(layout, act):
+    from scattermoe_b200 import activation as A
+    lay = {"plain": A.LAYOUT_PLAIN, "glu_second": A.LAYOUT_GLU_SECOND, "glu_first": A.LAYOUT_GLU_FIRST,
+           "gpt_oss": A.LAYOUT_GPT_OSS}[layout]
+    return lay, {"gelu": A.ACT_GELU_ERF, "silu": A.ACT_SILU, None: A.ACT_SILU}[act]
+
+
+@pytest.mark.parametrize("w_layout", ["k_contig", "n_contig"])
+@pytest.mark.parametrize("layout,act", [("plain", "gelu"), ("glu_second", "silu"), ("glu_first", "gelu"), ("gpt_oss", None)])
+@pytest.mark.parametrize("T,E,k,K,F", [(300, 4, 2, 64, 136), (513, 8, 3, 320, 200), (1000, 8, 2, 256, 384),
+                                       (2048, 4, 2, 128, 1024)])
+def test_fused_input_gradient_and_activation_gradient(T, E, k, K, F, layout, act, w_layout):
+    """The activation gradient fused into the epilogue of the down-projection's input-gradient GEMM (one launch,
+    the hidden gradient never stored) against the oracle's scatter2scatter followed by PyTorch autograd of the
+    reference's activation formulas (mlp.py:41, :81-87; replace_moe.py:39-43, :76-83)."""
+    from scattermoe_b200.kernels import ops
+    dtype = torch.bfloat16
+    n_up = F if layout == "plain" else 2 * F
+    _, idx, g = _routing(T, E, k, seed=T + K + F + 5, skew=True)
+    se, ss, off = oracle.flatten_sort_count(idx, E)
+    R = T * k
+    DY = torch.randn(R, K, generator=g).to(dtype)                  # gradient of the down-projection's output, grouped
+    up = (torch.randn(R, n_up, generator=g) * 2.5).to(dtype)       # wide enough to reach the gpt-oss clamps
+    if w_layout == "n_contig":
+        W = (torch.randn(E, K, F, generator=g) * 0.1).to(dtype)
+    else:
+        W = (torch.randn(E, F, K, generator=g) * 0.1).to(dtype).permute(0, 2, 1)
+    lay, code = _act_codes(layout, act)
+    ops.FORCE_PATH = "tc"
+    from scattermoe_b200 import _lib
+    d_up = torch.full((R, n_up), float("nan"), dtype=dtype, device="cuda")
+    assert ops._scatter2scatter_act_bwd_impl(d_up, _dev(DY), _dev(W), _dev(up), _dev(off), lay, code, 1.702, 7.0), \
+        "this shape must take the fused tensor-core kernel: " + _lib.last_error()
+    d_hidden = oracle.scatter2scatter(DY.float(), W.float(), se, ss, 1, x_grouped=True, y_grouped=True)
+    ref_in = up.float().requires_grad_()
+    (want,) = torch.autograd.grad(_act_reference(layout, act, ref_in), ref_in, d_hidden)
+    assert not bool(torch.isnan(d_up).any()), "every element of the gradient must be written"
+    assert_close("d_up", d_up, want, True, atol_scale=max(1.0, want.abs().max().item() / 4))
+    # the public wrapper gives the same bits, and the split path (grouped GEMM, then the activation-gradient kernel)
+    # agrees within the rounding of the stored hidden gradient
+    again = ops.scatter2scatter_act_bwd(_dev(DY), _dev(W), _dev(up), _dev(off), lay, code)
+    assert torch.equal(again, d_up)
+    ops.FORCE_PATH = "simt"
+    split = ops.scatter2scatter_act_bwd(_dev(DY), _dev(W), _dev(up), _dev(off), lay, code)
+    assert_close("d_up (split path)", split, want, True, atol_scale=max(1.0, want.abs().max().item() / 4))
+
+
+def _zipf_routing(T, E, k, seed):
+    """Skewed load: a few experts take most rows, some take none (the shape of the granite-style config)."""
+    g = torch.Generator().manual_seed(seed)
+    pop = torch.arange(1, E + 1, dtype=torch.float32) ** -1.2
+    logits = torch.randn(T, E, generator=g) + torch.log(pop / pop.sum())[torch.randperm(E, generator=g)]
+    return torch.topk(logits, k).indices, g
+
+
+LONG_WALKS = [
+    # T, E, k, K, N: every CTA of the persistent kernels walks >= 4 tiles, so tensor-memory buffers and the
+    # shared-memory ring are reused many times inside one launch (as at benchmark sizes)
+    (65536, 8, 2, 64, 256, False),      # 1024 row tiles x 1 column tile
+    (32768, 8, 4, 128, 512, False),     # 1024 x 2
+    (16384, 64, 8, 128, 256, True),     # zipf: ragged, tiny and empty experts among 1024+ row tiles
+]
+
+
+@pytest.mark.parametrize("mode", [(False, True), (True, False), (True, True), (False, False)])
+@pytest.mark.parametrize("T,E,k,K,N,zipf", LONG_WALKS)
+def test_scatter2scatter_many_tiles_per_cta(T, E, k, K, N, zipf, mode):
+    from scattermoe_b200.kernels import ops
+    x_grouped, y_grouped = mode
+    if zipf:
+        idx, g = _zipf_routing(T, E, k, seed=T + E)
+    else:
+        _, idx, g = _routing(T, E, k, seed=T + E + K)
+    se, ss, off = oracle.flatten_sort_count(idx, E)
+    kk = 1 if x_grouped else k
+    X = torch.randn(T * k if x_grouped else T, K, generator=g).bfloat16()
+    W = (torch.randn(E, N, K, generator=g) * 0.05).bfloat16().permute(0, 2, 1)
+    b = (torch.randn(E, N, generator=g) * 0.1).bfloat16()
+    ops.FORCE_PATH = "tc"
+    Y = ops.scatter2scatter(_dev(X), _dev(W), _dev(se), _dev(ss), kk, b=_dev(b), x_grouped=x_grouped,
+                            y_grouped=y_grouped, expert_offsets=_dev(off))
+    assert ops.last_path_was_tensor_core()
+    want = oracle.scatter2scatter(X.float(), W.float(), se, ss, kk, b=b.float(), x_grouped=x_grouped, y_grouped=y_grouped)
+    assert_close("Y", Y, want, True)
+
+
+@pytest.mark.parametrize("layout,act", [("glu_second", "silu"), ("gpt_oss", None), ("plain", "gelu")])
+@pytest.mark.parametrize("T,E,k,K,N,zipf", LONG_WALKS)
+def test_fused_epilogues_many_tiles_per_cta(T, E, k, K, N, zipf, layout, act):
+    """Both fused epilogue families (activation after the up-projection; activation gradient after the
+    down-projection's input gradient) on launches in which a CTA walks many tiles."""
+    from scattermoe_b200.kernels import ops
+    if zipf:
+        idx, g = _zipf_routing(T, E, k, seed=T + E + 1)
+    else:
+        _, idx, g = _routing(T, E, k, seed=T + E + K + 1)
+    se, ss, off = oracle.flatten_sort_count(idx, E)
+    R = T * k
+    lay, code = _act_codes(layout, act)
+    n_up = N if layout == "plain" else 2 * N            # N plays the part of the hidden width F here
+    X = torch.randn(T, K, generator=g).bfloat16()
+    W1 = (torch.randn(E, n_up, K, generator=g) * 0.1).bfloat16().permute(0, 2, 1)
+    res = ops.scatter2scatter_act(_dev(X), _dev(W1), _dev(se), _dev(ss), k, lay, code, expert_offsets=_dev(off))
+    assert res is not None
+    up, hidden = res
+    want_up = oracle.scatter2scatter(X.float(), W1.float(), se, ss, k, y_grouped=True)
+    assert_close("up", up, want_up, True)
+    want_h = _act_reference(layout, act, want_up)
+    assert_close("hidden", hidden, want_h, True, atol_scale=max(1.0, want_h.abs().max().item() / 4))
+    DY = torch.randn(R, K, generator=g).bfloat16()
+    W2t = (torch.randn(E, K, N, generator=g) * 0.1).bfloat16()      # (E, K, F): transposed view of the down-projection
+    ops.FORCE_PATH = "tc"
+    d_up = torch.full((R, n_up), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert ops._scatter2scatter_act_bwd_impl(d_up, _dev(DY), _dev(W2t), up, _dev(off), lay, code, 1.702, 7.0)
+    d_hidden = oracle.scatter2scatter(DY.float(), W2t.float(), se, ss, 1, x_grouped=True, y_grouped=True)
+    ref_in = up.float().cpu().requires_grad_()
+    (want,) = torch.autograd.grad(_act_reference(layout, act, ref_in), ref_in, d_hidden)
+    assert_close("d_up", d_up, want, True, atol_scale=max(1.0, want.abs().max().item() / 4))
+
+
+@pytest.mark.parametrize("gathered", [False, True])
+@pytest.mark.parametrize("T,E,k,K,N,zipf", [
+    (16384, 64, 8, 768, 512, True),      # 64 x 4 x 3 = 768 tiles, ragged / empty experts
+    (16384, 8, 2, 2304, 1280, False),    # 8 x 10 x 9 = 720 tiles, several bands per expert
+    (32768, 16, 2, 512, 1536, False),    # 16 x 12 x 2 = 384 tiles with the band over the other operand
+])
+def test_group_bwd_w_many_tiles_per_cta(T, E, k, K, N, zipf, gathered):
+    from scattermoe_b200.kernels import ops
+    if zipf:
+        idx, g = _zipf_routing(T, E, k, seed=T + E + 2)
+    else:
+        _, idx, g = _routing(T, E, k, seed=T + E + K + 2)
+    se, ss, off = oracle.flatten_sort_count(idx, E)
+    DY = torch.randn(T * k, N, generator=g).bfloat16()
+    if gathered:
+        X = torch.randn(T, K, generator=g).bfloat16()
+        Xg = oracle.group(X, ss, fan_out=k)
+    else:
+        Xg = X = torch.randn(T * k, K, generator=g).bfloat16()
+    ops.FORCE_PATH = "tc"
+    DW, Db = ops.group_bwd_W(_dev(DY), _dev(X), _dev(off), E, has_bias=True,
+                             x_gather_idx=_dev(ss) if gathered else None, fan_out=k if gathered else 1)
+    assert ops.last_path_was_tensor_core()
+    wDW, wDb = oracle.group_bwd_W(DY.float(), Xg.float(), off, E, has_bias=True)
+    counts = torch.bincount(idx.flatten(), minlength=E).clamp(min=1).float()
+    scale = counts.sqrt().view(E, 1, 1)               # sums over the expert's rows of unit-variance products
+    assert_close("DW", DW.float().cpu() / scale, wDW / scale, True)
+    assert_close("Db", Db.float().cpu() / scale.view(E, 1), wDb / scale.view(E, 1), True)

@@ -51,6 +51,25 @@ def test_static_scratch_sort_matches_workspace_sort_twice_in_a_row():
         assert int(a[2][-1]) == R and bool((a[0][1:] >= a[0][:-1]).all())
 
 
+@pytest.mark.parametrize("R,E", [(1 << 21, 128), (2048 * 32, 4096), (2048 * 1024 - 5, 128)])
+def test_static_scratch_accepts_requests_at_its_capacity(R, E):
+    """ceil(R / 2048) * E equal to the capacity (the header's own example, 2^21 slots at 128 experts, and the widest
+    expert range) must be served, with the same bits as the workspace entry point."""
+    from scattermoe_b200 import _lib
+    lib = _lib.load()
+    assert -(-R // 2048) * E == lib.smoe_sort_count_static_capacity()
+    dev = torch.device("cuda", 0)
+    ids = torch.randint(0, E, (R,), generator=torch.Generator().manual_seed(R % 1000 + E), dtype=torch.int64).to(dev)
+    rc_a, a = _call(lib, True, ids, E)
+    rc_b, b = _call(lib, False, ids, E)
+    torch.cuda.synchronize()
+    assert rc_a == 0, _lib.last_error()
+    assert rc_b == 0, _lib.last_error()
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+    assert int(a[2][-1]) == R
+
+
 def test_static_scratch_rejects_oversized_requests_without_touching_memory():
     from scattermoe_b200 import _lib
     lib = _lib.load()
