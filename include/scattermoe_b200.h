@@ -41,10 +41,7 @@ enum smoe_flags {
   SMOE_FLAG_ALLOW_TF32 = 1,   /* fp32 inputs may use reduced-precision tensor cores (ops.py:7 ALLOW_TF32) */
   SMOE_FLAG_FORCE_SIMT = 2,   /* take the CUDA-core kernel even where a tensor-core kernel exists */
   SMOE_FLAG_FORCE_TC = 4,     /* fail with SMOE_ERR_UNSUPPORTED instead of taking the CUDA-core kernel */
-  SMOE_FLAG_GATHER_ROWS = 8,  /* feed grouped inputs through the row-gather path too (testing / comparison) */
-  SMOE_FLAG_PAIR = 16,        /* smoe_scatter2scatter(_act): use the two-CTA (cta_group::2) tensor-core kernel where it
-                                 applies (rows in expert order, N > 128); with SMOE_FLAG_FORCE_TC, fail if it does not */
-  SMOE_FLAG_NO_PAIR = 32      /* never use the two-CTA kernel */
+  SMOE_FLAG_GATHER_ROWS = 8   /* feed grouped inputs through the row-gather path too (testing / comparison) */
 };
 
 int smoe_version(void);

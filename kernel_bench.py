@@ -4,9 +4,8 @@
 
 times, with CUDA events around back-to-back launches on torch's current stream, the launches one layer step makes
 through `kernels.ops` (rows already in expert order, as `parallel_linear` feeds them): the up-projection with and
-without the fused activation, the down-projection, the two input gradients and the two weight gradients. `--pair`
-selects the one-CTA tensor-core kernel, the two-CTA (cta_group::2) one, or both in turn. One JSON line per
-measurement. `--tokens` shrinks the problem (for profiler captures); the weights keep the workload's shape.
+without the fused activation, the down-projection, the two input gradients (the down-projection's also with the
+fused activation gradient) and the two weight gradients. One JSON line per measurement. `--tokens` shrinks the problem (for profiler captures); the weights keep the workload's shape.
 """
 from __future__ import annotations
 
@@ -32,7 +31,6 @@ def main(argv=None):
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="mixtral_8x7b")
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--launch", choices=LAUNCHES + ("all",), default="all")
-    ap.add_argument("--pair", choices=("off", "on", "both"), default="off")
     ap.add_argument("--iters", type=int, default=7)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args(argv)
@@ -67,31 +65,25 @@ def main(argv=None):
         "wgrad2": (lambda: ops.group_bwd_W(x, h, off, E), 2 * R * d * F),
     }
     names = LAUNCHES if a.launch == "all" else (a.launch,)
-    modes = {"off": (False,), "on": (True,), "both": (False, True)}[a.pair]
     ops.FORCE_PATH = "tc"
     try:
         for name in names:
             fn, flop = calls[name]
-            for pair in modes:
-                if pair and name.startswith("wgrad"):
-                    continue                      # the weight gradient has no two-CTA variant
-                ops.PAIR = pair
-                for _ in range(a.warmup):
-                    fn()
-                beg, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                torch.cuda.synchronize()
-                beg.record()
-                for _ in range(a.iters):
-                    fn()
-                end.record()
-                torch.cuda.synchronize()
-                sm.check_device_status()
-                ms = beg.elapsed_time(end) / a.iters
-                print(json.dumps({"workload": a.workload, "tokens": T, "launch": name,
-                                  "kernel": "two-CTA" if pair else "one-CTA", "ms": round(ms, 4),
-                                  "tflops": round(flop / ms / 1e9, 1), "iters": a.iters}), flush=True)
+            for _ in range(a.warmup):
+                fn()
+            beg, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            beg.record()
+            for _ in range(a.iters):
+                fn()
+            end.record()
+            torch.cuda.synchronize()
+            sm.check_device_status()
+            ms = beg.elapsed_time(end) / a.iters
+            print(json.dumps({"workload": a.workload, "tokens": T, "launch": name, "ms": round(ms, 4),
+                              "tflops": round(flop / ms / 1e9, 1), "iters": a.iters}), flush=True)
     finally:
-        ops.FORCE_PATH, ops.PAIR = None, None
+        ops.FORCE_PATH = None
 
 
 if __name__ == "__main__":

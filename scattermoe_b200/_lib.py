@@ -27,8 +27,6 @@ FLAG_ALLOW_TF32 = 1
 FLAG_FORCE_SIMT = 2
 FLAG_FORCE_TC = 4
 FLAG_GATHER_ROWS = 8
-FLAG_PAIR = 16
-FLAG_NO_PAIR = 32
 
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 

@@ -46,9 +46,10 @@ template <int BN> struct Cfg {
   static constexpr int BAR_BYTES = 256;
   static constexpr int TABLE_BYTES = ((2 * (MAX_E + 1) * 4 + 15) / 16) * 16;
   static constexpr int STAGE_ROW_BYTES = 80;                       // 64 payload + 16 pad: conflict-free 16-byte accesses
-  static constexpr int EPI_STAGING_BYTES = 4 * 32 * STAGE_ROW_BYTES;   // one 32-row slab per epilogue warp
+  static constexpr int EPI_STAGING_BYTES = 8 * 32 * STAGE_ROW_BYTES;   // one 32-row slab per epilogue warp (up to 8)
   static constexpr int SMEM_BYTES =
       1024 + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + BAR_BYTES + TABLE_BYTES + EPI_STAGING_BYTES;
+  static_assert(SMEM_BYTES <= 232448, "over the 227 KB of shared memory a CTA can have");
 };
 
 struct S2SParams {
@@ -74,8 +75,8 @@ struct S2SParams {
 
 // Shared by all roles: offsets -> per-expert segment starts and the exclusive prefix of tiles per expert.
 __device__ __forceinline__ void build_tile_table(const int64_t* __restrict__ offsets, int64_t R, int E, int units_per_mtile,
-                                                 int32_t* seg_start, int32_t* tile_prefix, int tid, int nthreads,
-                                                 int mtile_rows = BM) {
+                                                 int32_t* seg_start, int32_t* tile_prefix, int tid, int nthreads) {
+  constexpr int mtile_rows = BM;
   for (int e = tid; e < E; e += nthreads) {
     int64_t v = offsets[e];
     v = v < 0 ? 0 : (v > R ? R : v);
@@ -115,7 +116,8 @@ struct Tile { int e, m0, rows, n0; };
 // m-tiles x a few columns: with group_m chosen so that both footprints are alike, the operands a wave streams
 // from HBM (rows x K of A plus columns x K of W) are at their minimum for the number of tiles in flight.
 __device__ __forceinline__ Tile decode_tile(int t, const int32_t* tile_prefix, const int32_t* seg_start, int E, int BN,
-                                            int mtile_rows = BM, int group_m = 1 << 30) {
+                                            int group_m) {
+  constexpr int mtile_rows = BM;
   int lo = 0, hi = E;
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
@@ -221,12 +223,14 @@ __device__ __forceinline__ void flush_rows(uint8_t* slab, int lane, const uint4 
 // of other rows' tiles or zeros and are never stored): the stores are whole-warp operations.
 template <int BN, int EPI>
 __device__ __forceinline__ void epilogue_rows(const S2SParams& p, int n0, uint32_t taddr, uint8_t* slab, int lane,
-                                              bool valid, uint8_t* yrow, uint8_t* hrow, const uint8_t* brow) {
+                                              bool valid, uint8_t* yrow, uint8_t* hrow, const uint8_t* brow,
+                                              int c_first = 0, int c_step = 1) {
   constexpr int TN = (EPI == EPI_GLU_HALVES) ? BN / 2 : BN;
   const bool write_y = (EPI == EPI_NONE) || p.Y != nullptr;
+  // 32-column chunks c_first, c_first + c_step, ...: with two groups of epilogue warps each takes every other chunk
   if (EPI == EPI_GLU_HALVES) {
 #pragma unroll 1
-    for (int c = 0; c < TN / 32; ++c) {
+    for (int c = c_first; c < TN / 32; c += c_step) {
       const int n = n0 + c * 32;            // column inside one half
       if (n >= p.F) break;
       uint32_t acc_a[32], acc_b[32];
@@ -259,7 +263,7 @@ __device__ __forceinline__ void epilogue_rows(const S2SParams& p, int n0, uint32
     }
   } else {
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
+    for (int c = c_first; c < BN / 32; c += c_step) {
       const int n = n0 + c * 32;
       if (n >= p.N) break;
       uint32_t acc[32];
@@ -342,10 +346,11 @@ __device__ __forceinline__ void load8(const uint8_t* ptr, int is_bf16, bool ok, 
 // (the arithmetic of act_backward_kernel in activation.cu, on fp32 accumulators instead of a rounded dH).
 template <int BN, int EPI>
 __device__ __forceinline__ void epilogue_act_bwd(const S2SParams& p, int n0, uint32_t taddr, uint8_t* slab, int lane,
-                                                 bool valid, uint8_t* durow, const uint8_t* urow) {
+                                                 bool valid, uint8_t* durow, const uint8_t* urow, int c_first = 0,
+                                                 int c_step = 1) {
   const int F = p.N;
 #pragma unroll 1
-  for (int c = 0; c < BN / 32; ++c) {
+  for (int c = c_first; c < BN / 32; c += c_step) {
     const int n = n0 + c * 32;
     if (n >= F) break;
     uint32_t acc[32];
@@ -449,8 +454,8 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
       mbar_init(empty_bar(s), 1);                         // tcgen05.commit
     }
     for (int b = 0; b < 2; ++b) {
-      mbar_init(tfull_bar(b), 1);        // tcgen05.commit
-      mbar_init(tempty_bar(b), 128);     // epilogue threads
+      mbar_init(tfull_bar(b), 1);                        // tcgen05.commit
+      mbar_init(tempty_bar(b), p.a_by_tma ? 256 : 128);  // epilogue threads (the idle gather warps join them)
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -473,7 +478,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, BM, p.group_m);
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, p.group_m);
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
@@ -540,9 +545,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
       if (ok && lane == 0) umma_commit(tfull_bar(buf));
       __syncwarp();
     }
-  } else if (warp < 6 && p.a_by_tma) {
-    // grouped input: the TMA warp feeds both operands, nothing to gather
-  } else if (warp < 6) {
+  } else if (warp < 6 && !p.a_by_tma) {
     // ---------------- token rows: cp.async gather into the swizzled A tile -----------------------------
     const int ptid = tid - 64;
     const int chunk = ptid & 7;          // 16-byte chunk of the 128-byte K slice
@@ -551,7 +554,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, BM, p.group_m);
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, p.group_m);
       const uint8_t* rowptr[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -590,12 +593,17 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     }
   } else {
     // ---------------- epilogue: TMEM -> registers -> bias -> 16-bit -> global rows ----------------------
+    // Warps 6-9 always; warps 2-5 too when the rows come by TMA and there is nothing for them to gather. A warp may
+    // read the tensor-memory lanes of quarter (warp % 4), so each group of four covers all 128 accumulator rows; the
+    // two groups split the tile's 32-column chunks between them (even / odd).
     const int q = warp & 3;              // TMEM lane quarter this warp may read
     const int r = q * 32 + lane;
+    const int group = warp >= 6 ? 0 : 1;
+    const int c_step = p.a_by_tma ? 2 : 1;
     int tile_iter = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
-      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, BM, p.group_m);
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, p.group_m);
       const int buf = tile_iter & 1;
       const uint32_t tph = (tile_iter >> 1) & 1;
       bool valid = r < tl.rows;
@@ -610,12 +618,12 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
       if (!mbar_wait_warp(tfull_bar(buf), tph, abort_flag, p.status, 5)) { ok = false; break; }
       tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-      uint8_t* slab = epi_staging + q * (32 * C::STAGE_ROW_BYTES);
+      uint8_t* slab = epi_staging + (group * 4 + q) * (32 * C::STAGE_ROW_BYTES);
       if constexpr (EPI >= EPI_BWD_PLAIN) {
-        epilogue_act_bwd<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, p.U + out_row * p.u_row_bytes);
+        epilogue_act_bwd<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, p.U + out_row * p.u_row_bytes, group, c_step);
       } else {
         uint8_t* hrow = (EPI != EPI_NONE) ? p.H + out_row * p.h_row_bytes : nullptr;
-        epilogue_rows<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, hrow, brow);
+        epilogue_rows<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, hrow, brow, group, c_step);
       }
       tc_fence_before_sync();
       mbar_arrive(tempty_bar(buf));
@@ -628,203 +636,6 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, C::TMEM_COLS);
-  }
-}
-
-// ---------------------------------------------------------------------------------------------------------
-// CTA-pair variant of the grouped GEMM (tcgen05 cta_group::2): the two CTAs of a cluster compute one tile of 256
-// sorted positions x 256 output columns. Each CTA stages its own 128 rows of A and only ITS half (128 columns) of
-// the weight tile, so a stage is 32 KB instead of 48 KB: a third less traffic from L2 into shared memory per flop
-// and a 6-deep ring instead of 4. The leader (cluster rank 0) issues the MMAs for both; every CTA keeps its 128
-// accumulator rows in its own tensor memory and runs its own epilogue. Needs both operands TMA-addressable (rows in
-// expert order); other requests take s2s_tc_kernel.
-//   full[s]   (leader's)  1 arrival (leader's expect_tx for both CTAs' bytes) + the bytes of both CTAs' copies
-//   empty[s]  (each CTA)  1 arrival: the leader's commit, sent to both CTAs
-//   tfull[b]  (each CTA)  1 arrival: the leader's commit, sent to both CTAs
-//   tempty[b] (leader's)  256 arrivals: the epilogue threads of both CTAs
-struct PairCfg {
-  static constexpr int BN = 256;
-  static constexpr int STAGES = 6;
-  static constexpr int B_HALF_BYTES = 128 * BK * 2;
-  static constexpr int TMEM_COLS = 512;
-  static constexpr int BAR_BYTES = 256;
-  static constexpr int TABLE_BYTES = ((2 * (MAX_E + 1) * 4 + 15) / 16) * 16;
-  static constexpr int STAGE_ROW_BYTES = 80;
-  static constexpr int EPI_STAGING_BYTES = 4 * 32 * STAGE_ROW_BYTES;
-  static constexpr int SMEM_BYTES =
-      1024 + STAGES * (A_STAGE_BYTES + B_HALF_BYTES) + BAR_BYTES + TABLE_BYTES + EPI_STAGING_BYTES;
-};
-constexpr int PAIR_ROWS = 2 * BM;
-constexpr bool PAIR_BY_DEFAULT = false;   // the single-CTA kernel unless SMOE_FLAG_PAIR asks for pairs
-
-template <bool B_KMAJOR, int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-s2s_pair_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-                const S2SParams p) {
-  using C = PairCfg;
-  constexpr int STAGES = C::STAGES;
-  constexpr int BN = C::BN;
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw_addr = smem_u32(smem_raw);
-  uint8_t* smem = smem_raw + (((raw_addr + 1023u) & ~1023u) - raw_addr);
-  uint8_t* sA = smem;
-  uint8_t* sB = smem + STAGES * A_STAGE_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * (A_STAGE_BYTES + C::B_HALF_BYTES));
-  const uint32_t bar0 = smem_u32(bars);
-  auto full_bar = [&](int s) { return bar0 + 8u * s; };
-  auto empty_bar = [&](int s) { return bar0 + 8u * (STAGES + s); };
-  auto tfull_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + b); };
-  auto tempty_bar = [&](int b) { return bar0 + 8u * (2 * STAGES + 2 + b); };
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
-  int32_t* seg_start = reinterpret_cast<int32_t*>(reinterpret_cast<uint8_t*>(bars) + C::BAR_BYTES);
-  int32_t* tile_prefix = seg_start + (MAX_E + 1);
-  uint8_t* epi_staging = reinterpret_cast<uint8_t*>(bars) + C::BAR_BYTES + C::TABLE_BYTES;
-
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const uint32_t rank = cluster_ctarank();          // 0: leader
-  const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  constexpr int TN = (EPI == EPI_GLU_HALVES) ? BN / 2 : BN;
-  const int n_tiles = ((EPI == EPI_GLU_HALVES ? p.F : p.N) + TN - 1) / TN;
-  const int num_kb = (p.K + BK - 1) / BK;
-
-  if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(tfull_bar(b), 1);
-      mbar_init(tempty_bar(b), 256);
-    }
-    *abort_flag = 0;
-    fence_mbar_init();
-    tma_prefetch_desc(&tmap_w);
-    tma_prefetch_desc(&tmap_x);
-  }
-  build_tile_table(p.offsets, p.R, p.E, n_tiles, seg_start, tile_prefix, tid, NUM_THREADS, PAIR_ROWS);
-  if (warp == 1) {
-    tmem_alloc_pair(smem_u32(tmem_holder), C::TMEM_COLS);
-    tmem_relinquish_pair();
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  cluster_sync();                 // the peer's barriers exist before anything is sent to them
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_holder;
-  const int total_tiles = tile_prefix[p.E];
-
-  if (warp == 0) {
-    // ---------------- this CTA's rows of A and its half of the weight tile: TMA producer ------------------
-    int it = 0;
-    bool ok = true;
-    for (int t = pair_id; t < total_tiles && ok; t += num_pairs) {
-      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, PAIR_ROWS);
-      const int m0 = tl.m0 + static_cast<int>(rank) * BM;
-      // first weight row / column of this CTA's half of the B tile
-      const int nb = (EPI == EPI_GLU_HALVES) ? (rank == 0 ? tl.n0 : p.F + tl.n0) : tl.n0 + static_cast<int>(rank) * 128;
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1;
-        if (!mbar_wait_warp(empty_bar(s), ph ^ 1, abort_flag, p.status, 21)) { ok = false; break; }
-        if (lane == 0) {
-          const uint32_t full_leader = mapa_shared(full_bar(s), 0);
-          if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * (A_STAGE_BYTES + C::B_HALF_BYTES));
-          tma_load_2d_pair(smem_u32(sA + s * A_STAGE_BYTES), &tmap_x, full_leader, kb * BK, m0);
-          const uint32_t dst = smem_u32(sB + s * C::B_HALF_BYTES);
-          if (B_KMAJOR) {
-            tma_load_3d_pair(dst, &tmap_w, full_leader, kb * BK, nb, tl.e);
-          } else {
-            tma_load_3d_pair(dst, &tmap_w, full_leader, nb, kb * BK, tl.e);
-            tma_load_3d_pair(dst + 64 * BK * 2, &tmap_w, full_leader, nb + 64, kb * BK, tl.e);
-          }
-        }
-        __syncwarp();
-      }
-    }
-    // the leader's last commits still arrive on this CTA's empty barriers: take them before leaving the loop
-    for (int i = 0; i < STAGES && ok; ++i, ++it) {
-      const int s = it % STAGES;
-      const uint32_t ph = (it / STAGES) & 1;
-      if (!mbar_wait_warp(empty_bar(s), ph ^ 1, abort_flag, p.status, 26)) ok = false;
-    }
-    if (!ok) {
-      for (int i = 0; i < 64; ++i) __nanosleep(1000);
-    }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer: leader CTA only ---------------------------------------------------------
-    if (rank == 0) {
-      int it = 0, tile_iter = 0;
-      bool ok = true;
-      for (int t = pair_id; t < total_tiles && ok; t += num_pairs, ++tile_iter) {
-        const int buf = tile_iter & 1;
-        const uint32_t tph = (tile_iter >> 1) & 1;
-        if (!mbar_wait_warp(tempty_bar(buf), tph ^ 1, abort_flag, p.status, 22)) { ok = false; break; }
-        tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + buf * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait_warp(full_bar(s), ph, abort_flag, p.status, 23)) { ok = false; break; }
-          tc_fence_after_sync();
-          if (lane == 0) {
-            const uint32_t a_addr = smem_u32(sA + s * A_STAGE_BYTES);
-            const uint32_t b_addr = smem_u32(sB + s * C::B_HALF_BYTES);
-#pragma unroll
-            for (int j = 0; j < BK / UMMA_K; ++j) {
-              const uint64_t adesc = make_smem_desc_sw128(a_addr + j * (UMMA_K * 2), 16, 1024);
-              const uint64_t bdesc = B_KMAJOR ? make_smem_desc_sw128(b_addr + j * (UMMA_K * 2), 16, 1024)
-                                              : make_smem_desc_sw128(b_addr + j * (UMMA_K * 128), 64 * BK * 2, 1024);
-              umma_f16_pair(d_tmem, adesc, bdesc, p.idesc, (kb | j) != 0 ? 1u : 0u);
-            }
-            umma_commit_pair(empty_bar(s), 3);
-          }
-          __syncwarp();
-        }
-        if (ok && lane == 0) umma_commit_pair(tfull_bar(buf), 3);
-        __syncwarp();
-      }
-    }
-  } else if (warp < 6) {
-    // both operands come by TMA: nothing to gather
-  } else {
-    // ---------------- epilogue: this CTA's 128 rows of the pair's tile -------------------------------------
-    const int q = warp & 3;
-    const int r = q * 32 + lane;
-    int tile_iter = 0;
-    bool ok = true;
-    for (int t = pair_id; t < total_tiles && ok; t += num_pairs, ++tile_iter) {
-      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, PAIR_ROWS);
-      const int buf = tile_iter & 1;
-      const uint32_t tph = (tile_iter >> 1) & 1;
-      const int row_in_tile = static_cast<int>(rank) * BM + r;
-      bool valid = row_in_tile < tl.rows;
-      int64_t out_row = 0;
-      if (valid) {
-        const int64_t m = tl.m0 + row_in_tile;
-        out_row = p.y_grouped ? m : p.sorted_idx[m];
-        valid = out_row >= 0 && out_row < p.R;
-      }
-      uint8_t* yrow = p.Y + out_row * p.y_row_bytes;
-      const uint8_t* brow = p.bias ? p.bias + static_cast<int64_t>(tl.e) * p.bias_row_elems * 2 : nullptr;
-      if (!mbar_wait_warp(tfull_bar(buf), tph, abort_flag, p.status, 25)) { ok = false; break; }
-      tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-      uint8_t* hrow = (EPI != EPI_NONE) ? p.H + out_row * p.h_row_bytes : nullptr;
-      uint8_t* slab = epi_staging + q * (32 * C::STAGE_ROW_BYTES);
-      epilogue_rows<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, hrow, brow);
-      tc_fence_before_sync();
-      mbar_arrive_cluster(mapa_shared(tempty_bar(buf), 0));
-    }
-  }
-
-  // ---------------- teardown: nobody leaves while the peer may still read its memory or signal it -----------
-  tc_fence_before_sync();
-  __syncthreads();
-  cluster_sync();
-  if (warp == 1) {
-    tc_fence_after_sync();
-    tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
   }
 }
 
@@ -1327,39 +1138,6 @@ static int launch_s2s_cfg(const CUtensorMap& map, const CUtensorMap& map_x, cons
   return SMOE_OK;
 }
 
-template <bool B_KMAJOR, int EPI>
-static int launch_s2s_pair(const CUtensorMap& map, const CUtensorMap& map_x, const S2SParams& p, int64_t max_tiles,
-                           cudaStream_t stream) {
-  static std::mutex mu;
-  static int max_pairs[64] = {0};          // 0: not asked yet
-  int dev = 0;
-  SMOE_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return SMOE_ERR_UNSUPPORTED;
-  {
-    std::lock_guard<std::mutex> lock(mu);
-    if (max_pairs[dev] == 0) {
-      SMOE_CUDA(cudaFuncSetAttribute(s2s_pair_kernel<B_KMAJOR, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     PairCfg::SMEM_BYTES));
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(2, 1, 1);
-      cfg.blockDim = dim3(NUM_THREADS, 1, 1);
-      cfg.dynamicSmemBytes = PairCfg::SMEM_BYTES;
-      int n = 0;
-      const cudaError_t err = cudaOccupancyMaxActiveClusters(&n, s2s_pair_kernel<B_KMAJOR, EPI>, &cfg);
-      if (err != cudaSuccess) (void)cudaGetLastError();
-      DeviceInfo di;
-      if (int rc = get_device_info(&di)) return rc;
-      // resident pairs decide only how the tiles are dealt out; without an answer assume one CTA per SM
-      max_pairs[dev] = (err == cudaSuccess && n > 0) ? n : (di.sm_count / 2 > 0 ? di.sm_count / 2 : 1);
-    }
-  }
-  const int pairs = static_cast<int>(max_tiles < max_pairs[dev] ? max_tiles : max_pairs[dev]);
-  if (pairs <= 0) return SMOE_ERR_UNSUPPORTED;
-  s2s_pair_kernel<B_KMAJOR, EPI><<<2 * pairs, NUM_THREADS, PairCfg::SMEM_BYTES, stream>>>(map, map_x, p);
-  SMOE_LAUNCH_CHECK();
-  return SMOE_OK;
-}
-
 // rank-2 map over (feature, row) of 16-bit elements, box0 x box1 box (64 x 64 by default), 128-byte swizzle.
 static bool encode_map2(CUtensorMap* map, bool bf16, const void* base, uint64_t d0, uint64_t d1,
                         uint64_t stride1_bytes, uint32_t box0 = 64, uint32_t box1 = BK) {
@@ -1463,44 +1241,6 @@ int launch_s2s_tc(const S2SArgs& a) {
                 encode_map2(&map_x, bf16, a.X, a.K, a.x_rows, static_cast<uint64_t>(a.sxm) * 2, 64, BM)) ? 1 : 0;
 
   const int tile_cols = epi == EPI_GLU_HALVES ? BN / 2 : BN;
-
-  // CTA-pair kernel: rows in expert order, a full-width tile, and enough rows per expert that 256-row tiles are
-  // mostly full. SMOE_FLAG_PAIR / SMOE_FLAG_NO_PAIR override the choice.
-  const bool pair_auto = PAIR_BY_DEFAULT && a.R >= static_cast<int64_t>(a.E) * 4 * PAIR_ROWS;
-  const bool want_pair = !(a.flags & SMOE_FLAG_NO_PAIR) && ((a.flags & SMOE_FLAG_PAIR) || pair_auto);
-  if (want_pair && p.a_by_tma && BN == 256 && epi < EPI_BWD_PLAIN) {
-    CUtensorMap map_pair = map;
-    bool okp = true;
-    if (k_major && epi != EPI_GLU_HALVES)
-      okp = encode_map3(&map_pair, bf16, a.W, a.K, a.N, a.E, static_cast<uint64_t>(a.swn) * 2, e_stride, BK, 128);
-    if (okp) {
-      S2SParams pp = p;
-      pp.idesc = make_idesc_f16(bf16, false, !k_major, PAIR_ROWS, 256);
-      const int64_t pair_tiles = (cdiv64(a.R, PAIR_ROWS) + a.E) * cdiv(epi == EPI_GLU_HALVES ? F : a.N, tile_cols);
-      int rc = SMOE_ERR_UNSUPPORTED;
-      switch (epi) {
-        case EPI_NONE:
-          rc = k_major ? launch_s2s_pair<true, EPI_NONE>(map_pair, map_x, pp, pair_tiles, a.stream)
-                       : launch_s2s_pair<false, EPI_NONE>(map_pair, map_x, pp, pair_tiles, a.stream);
-          break;
-        case EPI_ACT:
-          rc = k_major ? launch_s2s_pair<true, EPI_ACT>(map_pair, map_x, pp, pair_tiles, a.stream)
-                       : launch_s2s_pair<false, EPI_ACT>(map_pair, map_x, pp, pair_tiles, a.stream);
-          break;
-        case EPI_GLU_HALVES:
-          rc = k_major ? launch_s2s_pair<true, EPI_GLU_HALVES>(map_pair, map_x, pp, pair_tiles, a.stream)
-                       : launch_s2s_pair<false, EPI_GLU_HALVES>(map_pair, map_x, pp, pair_tiles, a.stream);
-          break;
-        case EPI_GPT_OSS:
-          rc = k_major ? launch_s2s_pair<true, EPI_GPT_OSS>(map_pair, map_x, pp, pair_tiles, a.stream)
-                       : launch_s2s_pair<false, EPI_GPT_OSS>(map_pair, map_x, pp, pair_tiles, a.stream);
-          break;
-        default: break;
-      }
-      if (rc != SMOE_ERR_UNSUPPORTED) return rc;
-    }
-  }
-  if ((a.flags & SMOE_FLAG_PAIR) && (a.flags & SMOE_FLAG_FORCE_TC)) return SMOE_ERR_UNSUPPORTED;
 
   const int64_t max_tiles = (cdiv64(a.R, BM) + a.E) * cdiv(epi == EPI_GLU_HALVES ? F : a.N, tile_cols);
   const int grid = static_cast<int>(max_tiles < di.sm_count ? max_tiles : di.sm_count);

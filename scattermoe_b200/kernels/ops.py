@@ -21,7 +21,6 @@ BLOCK_M = 128        # rows of the expert-sorted slot list per tensor-core tile 
 ALLOW_TF32 = True    # fp32 inputs may use reduced-precision tensor cores (ops.py:7); read at call time
 FORCE_PATH = None    # testing hook: None (automatic) | "simt" | "tc"
 GATHER_ROWS = False  # testing hook: feed grouped inputs through the cp.async row-gather path instead of TMA
-PAIR = None          # None: the library chooses | True / False: ask for / forbid the two-CTA tensor-core kernel
 
 
 def _flags() -> int:
@@ -32,8 +31,6 @@ def _flags() -> int:
         f |= _lib.FLAG_FORCE_TC
     if GATHER_ROWS:
         f |= _lib.FLAG_GATHER_ROWS
-    if PAIR is not None:
-        f |= _lib.FLAG_PAIR if PAIR else _lib.FLAG_NO_PAIR
     return f
 
 
@@ -237,9 +234,10 @@ def _scatter2scatter_act_bwd_fill(d_up, DY, W, up, expert_offsets, act_layout, a
     from .. import activation as _act
     R = DY.size(0)
     d_hidden = torch.empty((R, W.size(-1)), device=DY.device, dtype=DY.dtype)
-    # rows are in expert order on both sides: the index tensors are not read
-    dummy = expert_offsets.new_zeros(R)
-    _scatter2scatter_impl(d_hidden, W, DY, 1, dummy, dummy, None, True, True, expert_offsets)
+    # rows are in expert order on both sides; the CUDA-core kernel still reads each row's expert id
+    rows = torch.arange(R, device=DY.device, dtype=torch.int64)
+    sorted_e = torch.searchsorted(_i64(expert_offsets), rows, right=True)
+    _scatter2scatter_impl(d_hidden, W, DY, 1, sorted_e, rows, None, True, True, expert_offsets)
     _act._call(True, up, d_hidden, d_up, d_hidden.size(1), act_layout, act, alpha, limit)
 
 

@@ -46,7 +46,7 @@ class _ExpertMLPBase(nn.Module):
             # activation gradient in the epilogue of the down-projection's input-gradient GEMM (tensor-core cases;
             # separate one-pass kernels otherwise)
             y = expert_mlp(tokens, self.experts.weight.permute(0, 2, 1), self.output_experts.weight.permute(0, 2, 1),
-                           expert_p.reshape(tokens.size(0), -1), self.top_k, *routing, self.act_layout, code,
+                           expert_p.reshape(tokens.size(0), expert_idxs.shape[-1]), self.top_k, *routing, self.act_layout, code,
                            up_biases=self.experts.bias, down_biases=self.output_experts.bias)
         else:
             up = self.experts(tokens, self.top_k, *routing, grouped_out=True)

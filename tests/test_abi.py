@@ -101,7 +101,7 @@ def test_python_constants_match_the_header():
     enum = {m.group(1): int(m.group(2)) for m in re.finditer(r"\b(SMOE_[A-Z0-9_]+)\s*=\s*(\d+)", text)}
     assert enum["SMOE_OK"] == _lib.SMOE_OK and enum["SMOE_ERR_BAD_ARG"] == _lib.SMOE_ERR_BAD_ARG
     assert enum["SMOE_ERR_UNSUPPORTED"] == _lib.SMOE_ERR_UNSUPPORTED
-    for name in ("ALLOW_TF32", "FORCE_SIMT", "FORCE_TC", "GATHER_ROWS", "PAIR", "NO_PAIR"):
+    for name in ("ALLOW_TF32", "FORCE_SIMT", "FORCE_TC", "GATHER_ROWS"):
         assert enum["SMOE_FLAG_" + name] == getattr(_lib, "FLAG_" + name), name
     assert {torch.float32: enum["SMOE_F32"], torch.bfloat16: enum["SMOE_BF16"], torch.float16: enum["SMOE_F16"]} == _lib.DTYPE_CODE
     flags = [v for k, v in enum.items() if k.startswith("SMOE_FLAG_")]

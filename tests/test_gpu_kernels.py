@@ -327,58 +327,6 @@ def test_fused_up_projection_declines_what_it_cannot_do():
                                    A.LAYOUT_PLAIN, A.ACT_SILU) is None          # N <= 128
 
 
-@pytest.mark.parametrize("w_layout", ["k_contig", "n_contig"])
-@pytest.mark.parametrize("case", ["plain", "scatter_bias", "ragged", "tiny_experts", "fp16", "glu_second", "glu_first",
-                                  "act_plain", "gpt_oss"])
-def test_cta_pair_kernel_equals_single_cta_kernel(case, w_layout):
-    """The two-CTA (cta_group::2) grouped GEMM accumulates every output element in the same order as the one-CTA
-    kernel, so the two must agree bit for bit: plain / scattered / biased outputs, ragged and nearly empty experts,
-    K and N that are not tile multiples, fp16, and every fused epilogue."""
-    import scattermoe_b200 as sm
-    from scattermoe_b200 import activation as A
-    from scattermoe_b200.kernels import ops
-    torch.manual_seed(11)
-    T, K, N, E, k, dtype, bias, y_grouped, skew, layout = {
-        "plain": (2048, 512, 512, 4, 2, torch.bfloat16, False, True, False, None),
-        "scatter_bias": (2048, 512, 768, 4, 2, torch.bfloat16, True, False, False, None),
-        "ragged": (1000, 520, 384, 8, 2, torch.bfloat16, True, False, True, None),
-        "tiny_experts": (300, 256, 256, 16, 2, torch.bfloat16, False, True, True, None),
-        "fp16": (1024, 256, 512, 4, 2, torch.float16, True, False, False, None),
-        "glu_second": (2048, 512, 768, 4, 2, torch.bfloat16, True, True, False, A.LAYOUT_GLU_SECOND),
-        "glu_first": (1000, 320, 528, 8, 2, torch.bfloat16, False, True, True, A.LAYOUT_GLU_FIRST),
-        "act_plain": (2048, 512, 512, 4, 2, torch.bfloat16, False, True, False, A.LAYOUT_PLAIN),
-        "gpt_oss": (2048, 512, 512, 4, 2, torch.bfloat16, True, True, False, A.LAYOUT_GPT_OSS),
-    }[case]
-    logits = torch.randn(T, E, device="cuda")
-    if skew:
-        logits = logits + torch.linspace(3, -3, E, device="cuda")
-    se, ss, off = sm.flatten_sort_count(torch.topk(logits, k).indices, E)
-    x = torch.randn(T * k, K, device="cuda", dtype=dtype)
-    if w_layout == "k_contig":
-        w = (torch.randn(E, N, K, device="cuda", dtype=dtype) * 0.05).permute(0, 2, 1)
-    else:
-        w = torch.randn(E, K, N, device="cuda", dtype=dtype) * 0.05
-    b = torch.randn(E, N, device="cuda", dtype=dtype) if bias else None
-
-    def launch():
-        if layout is None:
-            return (ops.scatter2scatter(x, w, se, ss, 1, b=b, x_grouped=True, y_grouped=y_grouped, expert_offsets=off),)
-        return ops.scatter2scatter_act(x, w, se, ss, 1, layout, A.ACT_SILU, b=b, x_grouped=True, expert_offsets=off)
-    results = []
-    try:
-        ops.FORCE_PATH = "tc"          # with PAIR = True: fail instead of silently taking the one-CTA kernel
-        for pair in (False, True):
-            ops.PAIR = pair
-            out = launch()
-            assert out is not None
-            results.append(out)
-            sm.check_device_status()
-    finally:
-        ops.FORCE_PATH, ops.PAIR = None, None
-    for single, paired in zip(*results):
-        assert torch.equal(single, paired)
-
-
 def _act_reference(layout, act, up):
     fn = {"gelu": torch.nn.functional.gelu, "silu": torch.nn.functional.silu, None: None}[act]
     if layout == "plain":
