@@ -76,6 +76,23 @@ int smoe_sort_count_static(const int64_t* expert_idxs, int64_t R, int32_t E,
                            int64_t* sorted_expert_idxs, int64_t* sorted_scattered_idxs, int64_t* expert_offsets,
                            void* stream);
 
+/* Router fusion: from the router's logits to everything flatten_sort_count returns, without the (T, E) softmax
+ * round trip and the separate top-k / renormalise / histogram kernels of the callers of flatten_sort_count
+ * (scattermoe/utils/replace_moe.py:67-71; the reference test, tests/test_mlp.py:46-51; Hugging Face's top-k routers).
+ *   mode 0: p = softmax(logits) over all E experts, gates = the k largest p (renormalize != 0: divided by their sum)
+ *   mode 1: gates = softmax over the k largest logits
+ * Outputs: expert_idxs (T, k) int64, descending by logit (equal logits: lower expert id first); gates (T, k) fp32;
+ * lse (T) fp32 log-sum-exp over all experts (nullable); and the three outputs of smoe_sort_count for expert_idxs.
+ * logits is (T, E), row stride `stride_t` elements, inner stride 1, dtype SMOE_F32 / BF16 / F16 (arithmetic in fp32).
+ * One kernel produces ids, gates and the sort's block histograms; the sort's scan and scatter kernels follow.
+ * Limits: E <= 1024, k <= min(E, 32), beyond which SMOE_ERR_UNSUPPORTED is returned (no error text) and the caller
+ * runs its own top-k followed by smoe_sort_count. */
+size_t smoe_route_topk_workspace_bytes(int64_t T, int32_t k, int32_t E);
+int smoe_route_topk(const void* logits, int64_t T, int32_t E, int64_t stride_t, int32_t logits_dtype, int32_t k,
+                    int32_t mode, int32_t renormalize, int64_t* expert_idxs, float* gates, float* lse,
+                    int64_t* sorted_expert_idxs, int64_t* sorted_scattered_idxs, int64_t* expert_offsets,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
 /* Inclusive end offsets from the sorted ids alone. The reference's kernels.ops.scatter2scatter
  * (scattermoe/kernels/ops.py:120) receives no offsets and masks rows per expert inside the kernel
  * (:81-91); this build's grouped GEMM walks expert segments, so callers that only hold the sorted ids

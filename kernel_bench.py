@@ -30,7 +30,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="mixtral_8x7b")
     ap.add_argument("--tokens", type=int, default=None)
-    ap.add_argument("--launch", choices=LAUNCHES + ("all",), default="all")
+    ap.add_argument("--launch", default="all", help="'all' or a comma-separated list of: " + ", ".join(LAUNCHES))
     ap.add_argument("--iters", type=int, default=7)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args(argv)
@@ -64,7 +64,10 @@ def main(argv=None):
         "wgrad1": (lambda: ops.group_bwd_W(d_up, x, off, E), 2 * R * d * 2 * F),
         "wgrad2": (lambda: ops.group_bwd_W(x, h, off, E), 2 * R * d * F),
     }
-    names = LAUNCHES if a.launch == "all" else (a.launch,)
+    names = LAUNCHES if a.launch == "all" else tuple(a.launch.split(","))
+    for n in names:
+        if n not in LAUNCHES:
+            ap.error("unknown launch %r" % n)
     ops.FORCE_PATH = "tc"
     try:
         for name in names:

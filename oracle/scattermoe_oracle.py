@@ -193,6 +193,23 @@ def single2scatter(X, W, expert_idxs):
 # --------------------------------------------------------------------------------------
 
 
+def route_topk(logits, k, mode="softmax_topk", renormalize=True):
+    """The router prologue that every caller of flatten_sort_count runs first, restated: fp32 softmax over the
+    experts, top-k, division by the sum of the selected probabilities (scattermoe/utils/replace_moe.py:67-71, the
+    granite patch; `renormalize=False` is the reference test's router, tests/test_mlp.py:46-51), or, for
+    mode "topk_softmax", top-k of the logits followed by a softmax over the selected ones (the gpt-oss router whose
+    outputs scattermoe/utils/replace_moe.py:22-27 consumes). Returns (gates (T, k) fp32, expert ids (T, k) int64)."""
+    z = logits.float()
+    if mode == "topk_softmax":
+        top, ids = torch.topk(z, k, dim=-1)
+        return torch.softmax(top, dim=-1), ids
+    p = torch.softmax(z, dim=-1)
+    g, ids = torch.topk(p, k, dim=-1)
+    if renormalize:
+        g = g / g.sum(-1, keepdim=True)
+    return g, ids
+
+
 def act_gelu(h):
     """nn.GELU() default (erf form), as used by tests/test_mlp.py:55."""
     return torch.nn.functional.gelu(h)

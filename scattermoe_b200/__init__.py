@@ -12,6 +12,7 @@ from . import parallel_experts
 from . import kernels
 from . import mlp
 from . import utils
+from .routing import route_topk
 from ._lib import check_device_status, library_path
 
 __all__ = [
@@ -19,6 +20,7 @@ __all__ = [
     "parallel_linear",
     "parallel_linear_act",
     "expert_mlp",
+    "route_topk",
     "ParallelExperts",
     "parallel_experts",
     "kernels",

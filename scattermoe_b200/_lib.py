@@ -41,6 +41,8 @@ SIGNATURES = {
     "smoe_sort_count": ([_P, _I64, _I32, _P, _P, _P, _P, c_size_t, _P], c_int32),
     "smoe_sort_count_static_capacity": ([], c_int64),
     "smoe_sort_count_static": ([_P, _I64, _I32, _P, _P, _P, _P], c_int32),
+    "smoe_route_topk_workspace_bytes": ([_I64, _I32, _I32], c_size_t),
+    "smoe_route_topk": ([_P, _I64, _I32, _I64, _I32, _I32, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, c_size_t, _P], c_int32),
     "smoe_offsets_from_sorted": ([_P, _I64, _I32, _P, _P], c_int32),
     "smoe_scatter2scatter": ([_P, _I64, _I64, _I64,          # X
                               _P, _I64, _I64, _I64,          # W

@@ -139,6 +139,101 @@ sc_scatter_kernel(const int64_t* __restrict__ ids, int64_t R, int E, int nblk,
   }
 }
 
+// ---- router fusion: logits -> top-k ids, gates and the block histograms of the sort, in one pass -----------------
+// Replaces, for the callers of flatten_sort_count (scattermoe/utils/replace_moe.py:67-71, the reference test's
+// tests/test_mlp.py:46-51, Hugging Face's top-k routers), the softmax / topk / renormalise / histogram sequence of
+// separate PyTorch kernels with a (T, E) round trip through HBM between each: one warp reads a token's E logits once,
+// keeps them in registers, and emits the k selected expert ids (int64, descending by logit; equal logits: lower
+// expert id first), their gates (fp32) and its share of the counting sort's block histogram. Block b covers the
+// slots [b * SC_CHUNK, (b + 1) * SC_CHUNK) of the flat (T, k) id tensor, exactly what sc_scan_kernel and
+// sc_scatter_kernel expect from sc_hist_kernel; a token whose slots straddle two blocks is evaluated by both, each
+// writing and counting only its own slots.
+//   mode 0: p = softmax(logits) over all experts, gates = top-k of p (renorm: divided by their sum)
+//   mode 1: gates = softmax over the k selected logits
+// lse (nullable): log-sum-exp of the token's logits over all experts (what the backward of mode 0 needs).
+enum { ROUTE_SOFTMAX_TOPK = 0, ROUTE_TOPK_SOFTMAX = 1 };
+constexpr int ROUTE_MAX_E = 1024;
+constexpr int ROUTE_MAX_K = 32;
+
+template <typename T, int NV>
+__global__ void __launch_bounds__(SC_THREADS)
+route_topk_kernel(const T* __restrict__ logits, int64_t stride_t, int64_t Tn, int E, int k, int mode, int renorm,
+                  int64_t* __restrict__ ids, float* __restrict__ gates, float* __restrict__ lse, int nblk,
+                  int32_t* __restrict__ block_hist) {
+  extern __shared__ int32_t hist[];     // [E]
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (int e = tid; e < E; e += SC_THREADS) hist[e] = 0;
+  __syncthreads();
+  const int64_t R = Tn * k;
+  const int64_t s_beg = static_cast<int64_t>(blockIdx.x) * SC_CHUNK;
+  const int64_t s_end = min(R, s_beg + SC_CHUNK);
+  const int64_t t_beg = s_beg / k, t_end = (s_end + k - 1) / k;
+  const float NEG = -INFINITY;
+  for (int64_t t = t_beg + warp; t < t_end; t += SC_WARPS) {
+    float v[NV];
+    const T* row = logits + t * stride_t;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int e = i * 32 + lane;
+      v[i] = e < E ? to_f32<T>(row[e]) : NEG;
+    }
+    // maximum and sum of exponentials over all experts
+    float m = v[0];
+#pragma unroll
+    for (int i = 1; i < NV; ++i) m = fmaxf(m, v[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float ssum = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) ssum += (v[i] == NEG) ? 0.f : expf(v[i] - m);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ssum += __shfl_xor_sync(0xffffffffu, ssum, o);
+    if (lse && lane == 0 && t * k >= s_beg) lse[t] = m + logf(ssum);     // the block that owns the token's first slot
+    // k rounds of arg-max; lane j keeps the j-th winner
+    float my_val = 0.f;
+    int my_id = 0;
+    for (int j = 0; j < k; ++j) {
+      float best = v[0];
+      int bi = 0;
+#pragma unroll
+      for (int i = 1; i < NV; ++i)
+        if (v[i] > best) { best = v[i]; bi = i; }
+      int be = bi * 32 + lane;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+        if (ov > best || (ov == best && oe < be)) { best = ov; be = oe; }
+      }
+      if (lane == j) { my_val = best; my_id = be; }
+      if ((be & 31) == lane) {
+#pragma unroll
+        for (int i = 0; i < NV; ++i)
+          if (i == (be >> 5)) v[i] = NEG;
+      }
+    }
+    // gates of the k winners (lanes 0..k-1)
+    const bool sel = lane < k;
+    const float top = __shfl_sync(0xffffffffu, my_val, 0);
+    float g = sel ? expf(my_val - (mode == ROUTE_TOPK_SOFTMAX ? top : m)) : 0.f;
+    float gs = g;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) gs += __shfl_xor_sync(0xffffffffu, gs, o);
+    if (mode == ROUTE_TOPK_SOFTMAX) g = g / gs;
+    else g = renorm ? g / gs : g / ssum;
+    if (sel) {
+      const int64_t slot = t * k + lane;
+      if (slot >= s_beg && slot < s_end) {
+        ids[slot] = my_id;
+        gates[slot] = g;
+        if (my_id < E) atomicAdd(&hist[my_id], 1);
+      }
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += SC_THREADS) block_hist[static_cast<int64_t>(e) * nblk + blockIdx.x] = hist[e];
+}
+
 __global__ void zero_offsets_kernel(int64_t* expert_offsets, int E) {
   const int e = blockIdx.x * blockDim.x + threadIdx.x;
   if (e < E) expert_offsets[e] = 0;
@@ -278,4 +373,71 @@ extern "C" int smoe_sort_count_static(const int64_t* expert_idxs, int64_t R, int
   // call needs clearing.
   return sort_count_launch("sort_count_static", expert_idxs, R, E, sorted_expert_idxs, sorted_scattered_idxs,
                            expert_offsets, scratch, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" size_t smoe_route_topk_workspace_bytes(int64_t T, int32_t k, int32_t E) {
+  if (T < 0 || k < 1 || E < 1) return 0;
+  return smoe_sort_count_workspace_bytes(T * k, E);
+}
+
+template <typename T>
+static int route_launch(const void* logits, int64_t stride_t, int64_t Tn, int E, int k, int mode, int renorm,
+                        int64_t* ids, float* gates, float* lse, int nblk, int32_t* block_hist, cudaStream_t stream) {
+  const size_t smem = static_cast<size_t>(E) * sizeof(int32_t);
+  const int nv = cdiv(E, 32);
+#define SMOE_ROUTE_CASE(NV)                                                                                         \
+  route_topk_kernel<T, NV><<<nblk, SC_THREADS, smem, stream>>>(static_cast<const T*>(logits), stride_t, Tn, E, k, mode, \
+                                                               renorm, ids, gates, lse, nblk, block_hist)
+  if (nv <= 1) SMOE_ROUTE_CASE(1);
+  else if (nv <= 2) SMOE_ROUTE_CASE(2);
+  else if (nv <= 4) SMOE_ROUTE_CASE(4);
+  else if (nv <= 8) SMOE_ROUTE_CASE(8);
+  else if (nv <= 16) SMOE_ROUTE_CASE(16);
+  else SMOE_ROUTE_CASE(32);
+#undef SMOE_ROUTE_CASE
+  SMOE_LAUNCH_CHECK();
+  return SMOE_OK;
+}
+
+extern "C" int smoe_route_topk(const void* logits, int64_t T, int32_t E, int64_t stride_t, int32_t logits_dtype,
+                               int32_t k, int32_t mode, int32_t renormalize, int64_t* expert_idxs, float* gates,
+                               float* lse, int64_t* sorted_expert_idxs, int64_t* sorted_scattered_idxs,
+                               int64_t* expert_offsets, void* workspace, size_t workspace_bytes, void* stream_) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  SMOE_CHECK_ARG(T >= 0 && E >= 1 && k >= 1 && k <= E, "route_topk: bad sizes T=%lld E=%d k=%d", (long long)T, E, k);
+  SMOE_CHECK_ARG(T * k < (int64_t(1) << 31), "route_topk: T*k=%lld out of range [0, 2^31)", (long long)(T * k));
+  SMOE_CHECK_ARG(mode == ROUTE_SOFTMAX_TOPK || mode == ROUTE_TOPK_SOFTMAX, "route_topk: unknown mode %d", mode);
+  SMOE_CHECK_ARG(logits_dtype == SMOE_F32 || logits_dtype == SMOE_BF16 || logits_dtype == SMOE_F16,
+                 "route_topk: unknown dtype %d", logits_dtype);
+  if (E > ROUTE_MAX_E || k > ROUTE_MAX_K) return SMOE_ERR_UNSUPPORTED;     // the caller uses separate kernels
+  SMOE_CHECK_ARG(expert_offsets != nullptr, "route_topk: expert_offsets is null");
+  const int64_t R = T * k;
+  if (R == 0) {
+    zero_offsets_kernel<<<cdiv(E, 256), 256, 0, stream>>>(expert_offsets, E);
+    SMOE_LAUNCH_CHECK();
+    return SMOE_OK;
+  }
+  SMOE_CHECK_ARG(logits && expert_idxs && gates && sorted_expert_idxs && sorted_scattered_idxs, "route_topk: null pointer");
+  SMOE_CHECK_ARG(stride_t >= E, "route_topk: row stride %lld smaller than E=%d", (long long)stride_t, E);
+  if (workspace == nullptr || workspace_bytes < smoe_route_topk_workspace_bytes(T, k, E)) {
+    set_error("route_topk: workspace of %zu bytes needed, %zu given", smoe_route_topk_workspace_bytes(T, k, E),
+              workspace_bytes);
+    return SMOE_ERR_WORKSPACE;
+  }
+  const int nblk = static_cast<int>(cdiv64(R, SC_CHUNK));
+  int32_t* block_hist = static_cast<int32_t*>(workspace);
+  int rc;
+  switch (logits_dtype) {
+    case SMOE_F32: rc = route_launch<float>(logits, stride_t, T, E, k, mode, renormalize ? 1 : 0, expert_idxs, gates, lse, nblk, block_hist, stream); break;
+    case SMOE_BF16: rc = route_launch<__nv_bfloat16>(logits, stride_t, T, E, k, mode, renormalize ? 1 : 0, expert_idxs, gates, lse, nblk, block_hist, stream); break;
+    default: rc = route_launch<__half>(logits, stride_t, T, E, k, mode, renormalize ? 1 : 0, expert_idxs, gates, lse, nblk, block_hist, stream); break;
+  }
+  if (rc != SMOE_OK) return rc;
+  const size_t smem = static_cast<size_t>(SC_WARPS) * E * sizeof(int32_t);     // E <= 1024: at most 32 KB
+  sc_scan_kernel<<<1, 1024, 0, stream>>>(block_hist, E * nblk, E, nblk, expert_offsets);
+  SMOE_LAUNCH_CHECK();
+  sc_scatter_kernel<<<nblk, SC_THREADS, smem, stream>>>(expert_idxs, R, E, nblk, block_hist, sorted_expert_idxs,
+                                                        sorted_scattered_idxs);
+  SMOE_LAUNCH_CHECK();
+  return SMOE_OK;
 }

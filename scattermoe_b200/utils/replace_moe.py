@@ -22,6 +22,7 @@ from torch.nn import functional as F
 from .. import _lib
 from .. import activation as _act
 from ..parallel_experts import expert_mlp, flatten_sort_count, parallel_linear
+from ..routing import route_topk
 
 PATCHED = {}      # class name -> original forward
 
@@ -102,13 +103,11 @@ try:
             return PATCHED['GraniteMoeHybridMoE'](self, layer_input)
         bsz, length, emb_size = layer_input.size()
         tokens = layer_input.reshape(-1, emb_size)
-        # top-k routing decision (replace_moe.py:67-71)
+        # top-k routing decision (replace_moe.py:67-71: fp32 softmax over the experts, top-k, renormalise) fused with
+        # the routing bookkeeping: one kernel from the logits to ids, gates and the sort's histograms
         router_logits = self.router.layer(tokens)
-        probs = F.softmax(router_logits, dim=1, dtype=torch.float)
-        probs, selected_experts = torch.topk(probs, self.router.top_k, dim=-1)
-        probs = probs / probs.sum(dim=-1, keepdim=True)
+        probs, selected_experts, routing = route_topk(router_logits, self.router.top_k, "softmax_topk", renormalize=True)
         probs = probs.to(tokens.dtype)
-        routing = flatten_sort_count(selected_experts, num_experts=self.router.num_experts)
         # experts: the FIRST half of the up-projection is the activated one here (replace_moe.py:76-83)
         code = _act.resolve_activation(self.activation) if _act.FUSE else None
         if code is None:

@@ -72,3 +72,60 @@ def test_int32_ids_keep_their_dtype():
     se, ss, off = sm.flatten_sort_count(idx.cuda(), 8)
     assert se.dtype == torch.int32 and ss.dtype == torch.int64 and off.dtype == torch.int64
     assert torch.equal(se.cpu().long(), torch.sort(idx.flatten().long()).values)
+
+
+def _torch_router(logits, k, mode, renormalize):
+    return oracle.route_topk(logits, k, mode, renormalize)
+
+
+@pytest.mark.parametrize("mode,renorm", [("softmax_topk", True), ("softmax_topk", False), ("topk_softmax", True)])
+@pytest.mark.parametrize("T,E,k,dtype", [
+    (256, 8, 2, torch.float32),          # the reference test's and config 1's router
+    (1000, 64, 8, torch.float32),        # 8000 slots: four histogram blocks, the last one partial
+    (4099, 128, 3, torch.float32),       # k does not divide the block size: tokens straddle histogram blocks
+    (32768, 128, 8, torch.bfloat16),     # the expert-parallel configuration's router, 16-bit logits
+    (513, 1000, 5, torch.float32),       # widest register tier, ragged last register
+    (64, 1024, 32, torch.float16),       # the limits of the fused kernel
+    (300, 16, 16, torch.float32),        # k == E
+    (1, 8, 2, torch.float32),
+    (0, 8, 2, torch.float32),
+    (700, 2048, 4, torch.float32),       # beyond the fused kernel: separate kernels, same results
+])
+def test_route_topk_matches_the_callers_router(T, E, k, dtype, mode, renorm):
+    import scattermoe_b200 as sm
+    g = torch.Generator().manual_seed(T * 7 + E + k)
+    logits = (torch.randn(T, E, generator=g) * 2).to(dtype).cuda()
+    gates, ids, (se, ss, off) = sm.route_topk(logits, k, mode, renormalize=renorm)
+    assert gates.dtype == torch.float32 and ids.dtype == torch.int64 and gates.shape == ids.shape == (T, k)
+    want_g, want_ids = _torch_router(logits, k, mode, renorm)
+    if dtype == torch.float32:
+        assert torch.equal(ids, want_ids)                 # random fp32 logits: no ties inside a row
+    else:
+        # 16-bit logits tie often; the stated rule (lower id first) must hold and the selected VALUES must agree
+        z = logits.float()
+        assert torch.equal(torch.gather(z, 1, ids), torch.gather(z, 1, want_ids))
+        same = torch.gather(z, 1, ids)
+        tie = same[:, 1:] == same[:, :-1]
+        assert bool((ids[:, 1:][tie] > ids[:, :-1][tie]).all())
+        want_g = _torch_router(logits, k, mode, renorm)[0]
+    torch.testing.assert_close(gates, want_g, rtol=1e-5, atol=1e-6)
+    # the routing bookkeeping is exactly the sort of the ids this call returned
+    rse, rss, roff = sm.flatten_sort_count(ids, E)
+    assert torch.equal(se, rse) and torch.equal(ss, rss) and torch.equal(off, roff)
+    sm.check_device_status()
+
+
+@pytest.mark.parametrize("mode,renorm", [("softmax_topk", True), ("softmax_topk", False), ("topk_softmax", True)])
+def test_route_topk_gradient(mode, renorm):
+    import scattermoe_b200 as sm
+    g = torch.Generator().manual_seed(3)
+    T, E, k = 300, 32, 4
+    logits = torch.randn(T, E, generator=g).cuda().requires_grad_()
+    dg = torch.randn(T, k, generator=g).cuda()
+    gates, ids, _ = sm.route_topk(logits, k, mode, renormalize=renorm)
+    (got,) = torch.autograd.grad(gates, logits, dg)
+    ref_in = logits.detach().clone().requires_grad_()
+    want_g, want_ids = _torch_router(ref_in, k, mode, renorm)
+    assert torch.equal(ids, want_ids)
+    (want,) = torch.autograd.grad(want_g, ref_in, dg)
+    torch.testing.assert_close(got, want, rtol=1e-4, atol=1e-6)
