@@ -412,3 +412,79 @@ def test_layer_replays_from_a_cuda_graph():
         gxe, gpe = torch.autograd.grad(ye, [xe, pe], dy)
         assert torch.equal(y, ye) and torch.equal(gx, gxe) and torch.equal(gp, gpe)
     sm.check_device_status()
+
+
+@pytest.mark.parametrize("names_kind,renorm", [("qwen", True), ("qwen", False), ("mixtral", True)])
+def test_consolidated_module_list_block(names_kind, renorm):
+    """A sparse-MoE block whose experts are an nn.ModuleList (the layout the reference's abandoned Qwen3 patch was
+    written for, replace_moe.py:97-208): after consolidation the block's forward and every gradient equal the
+    per-expert loop over the original modules."""
+    import scattermoe_b200 as sm
+    from scattermoe_b200.utils import consolidate as C
+    names = C.QWEN_NAMES if names_kind == "qwen" else C.MIXTRAL_NAMES
+    torch.manual_seed(7)
+    H, I, E, k, T = 256, 192, 8, 2, 300
+    g_, u_, d_ = names
+
+    class Expert(nn.Module):
+        def __init__(self):
+            super().__init__()
+            setattr(self, g_, nn.Linear(H, I, bias=False))
+            setattr(self, u_, nn.Linear(H, I, bias=False))
+            setattr(self, d_, nn.Linear(I, H, bias=False))
+            self.act_fn = nn.SiLU()
+
+        def forward(self, x):
+            return getattr(self, d_)(self.act_fn(getattr(self, g_)(x)) * getattr(self, u_)(x))
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate = nn.Linear(H, E, bias=False)
+            self.experts = nn.ModuleList([Expert() for _ in range(E)])
+            self.top_k, self.norm_topk_prob = k, renorm
+
+    ref = Block().cuda().float()
+    x = torch.randn(2, T // 2, H, device="cuda")
+    dy = torch.randn_like(x)
+
+    def loop_forward(block, inp):          # what Hugging Face's ModuleList blocks do: one expert at a time
+        tokens = inp.reshape(-1, H)
+        logits = block.gate(tokens)
+        p = torch.softmax(logits, dim=-1, dtype=torch.float)
+        w, ids = torch.topk(p, k, dim=-1)
+        if renorm:
+            w = w / w.sum(-1, keepdim=True)
+        out = torch.zeros_like(tokens)
+        for e in range(E):
+            tok, slot = (ids == e).nonzero(as_tuple=True)
+            if tok.numel():
+                out = out.index_add(0, tok, block.experts[e](tokens[tok]) * w[tok, slot].unsqueeze(1))
+        return out.view(inp.shape), logits
+
+    xr = x.clone().requires_grad_()
+    want_y, want_logits = loop_forward(ref, xr)
+    want_params = dict(ref.named_parameters())
+    want_grads = torch.autograd.grad(want_y, [xr] + list(want_params.values()), dy)
+    want_sd = {n: t.detach().clone() for n, t in ref.state_dict().items()}
+
+    fused = Block().cuda().float()
+    fused.load_state_dict(want_sd)
+    C.consolidate_moe_block(fused, names=names)
+    xf = x.clone().requires_grad_()
+    y, logits = C.moe_block_forward(fused, xf)
+    torch.testing.assert_close(logits, want_logits)
+    assert (y - want_y).abs().max().item() < 1e-4
+    got = torch.autograd.grad(y, [xf, fused.gate.weight, fused.experts.gate_up_proj, fused.experts.down_proj], dy)
+    assert (got[0] - want_grads[0]).abs().max().item() < 1e-4
+    names_list = list(want_params)
+    by_name = dict(zip(names_list, want_grads[1:]))
+    assert (got[1] - by_name["gate.weight"]).abs().max().item() < 1e-4
+    for e in range(E):
+        assert (got[2][e, :I] - by_name["experts.%d.%s.weight" % (e, g_)]).abs().max().item() < 1e-4
+        assert (got[2][e, I:] - by_name["experts.%d.%s.weight" % (e, u_)]).abs().max().item() < 1e-4
+        assert (got[3][e] - by_name["experts.%d.%s.weight" % (e, d_)]).abs().max().item() < 1e-4
+    # checkpoint of the consolidated block == checkpoint of the original
+    sd = fused.state_dict()
+    assert sorted(sd) == sorted(want_sd) and all(torch.equal(sd[n], want_sd[n]) for n in sd)
+    sm.check_device_status()
