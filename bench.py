@@ -198,7 +198,7 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_layer(name, c, tokens, device, seed, ep_world=1, exchange="nvlink", chunks=1):
+def build_layer(name, c, tokens, device, seed, ep_world=1, exchange="nvlink", chunks=1, once_per_rank=None):
     """Parameters and inputs of one rank: weights ~N(0, 0.02), X ~N(0, 1), softmax top-k routing."""
     import scattermoe_b200 as sm
     g = torch.Generator().manual_seed(seed)
@@ -221,8 +221,8 @@ def build_layer(name, c, tokens, device, seed, ep_world=1, exchange="nvlink", ch
     elif ep_world > 1:
         from scattermoe_b200.expert_parallel import ExpertParallelGLUMLP, PeerExpertParallelGLUMLP
         if exchange == "nvlink":
-            m = PeerExpertParallelGLUMLP(d, F, E, k, global_tokens=tokens * ep_world,
-                                         chunks=chunks).to(device=device, dtype=bf)
+            m = PeerExpertParallelGLUMLP(d, F, E, k, global_tokens=tokens * ep_world, chunks=chunks,
+                                         once_per_rank=once_per_rank).to(device=device, dtype=bf)
         else:
             m = ExpertParallelGLUMLP(d, F, E, k).to(device=device, dtype=bf)
         with torch.no_grad():
@@ -275,7 +275,8 @@ class LaunchCounter:
                "smoe_ep_return": 1, "smoe_ep_barrier": 1, "smoe_sort_count": 3, "smoe_sort_count_static": 3,
                "smoe_offsets_from_sorted": 1, "smoe_scatter2scatter": 1, "smoe_group_bwd_w": 1, "smoe_group": 1,
                "smoe_topk_reduce": 1, "smoe_gate_grad": 1, "smoe_activation_forward": 1, "smoe_activation_backward": 1,
-               "smoe_route_topk": 3, "smoe_status_poison": 1}
+               "smoe_route_topk": 3, "smoe_status_poison": 1, "smoe_ep_plan_tokens": 1, "smoe_ep_dispatch_meta": 1,
+               "smoe_ep_expand": 1, "smoe_ep_combine": 1, "smoe_ep_sum_parts": 1}
 
     def __init__(self):
         from scattermoe_b200 import _lib
@@ -594,7 +595,7 @@ def parity_check(name, c, layer, dev_in, triton_ref, sample_rows=256):
     return out
 
 
-def ep_parity_check(device, rank, world, dist, exchange, chunks):
+def ep_parity_check(device, rank, world, dist, exchange, chunks, once_per_rank=None):
     """N > 1: one small seeded expert-parallel step; every rank compares its outputs and gradient slices with the
     single-GPU layer on the gathered problem (same seed on every rank, so nothing needs gathering)."""
     import scattermoe_b200 as sm
@@ -619,7 +620,7 @@ def ep_parity_check(device, rank, world, dist, exchange, chunks):
     tl, el = T // world, E // world
     ts, es = slice(rank * tl, (rank + 1) * tl), slice(rank * el, (rank + 1) * el)
     if exchange == "nvlink":
-        m = PeerExpertParallelGLUMLP(d, F, E, k, chunks=chunks).to(device=device, dtype=bf)
+        m = PeerExpertParallelGLUMLP(d, F, E, k, chunks=chunks, once_per_rank=once_per_rank).to(device=device, dtype=bf)
     else:
         m = ExpertParallelGLUMLP(d, F, E, k).to(device=device, dtype=bf)
     with torch.no_grad():
@@ -676,7 +677,7 @@ def cpu_reference(name, c, steps, warmup, budget_s=None):
 # ---- one workload on this process's GPU -----------------------------------------------------------------------
 
 def measure(name, c, device, rank, world, dist, steps, warmup, with_e2e=True, sampler_gpu=None, exchange="nvlink",
-            chunks=1, keep=False):
+            chunks=1, keep=False, once_per_rank=None):
     """Device-timed forward+backward (and forward, and end-to-end) of one workload. Returns (fields, state)."""
     import scattermoe_b200 as sm
     peaks = load_peaks()
@@ -684,7 +685,7 @@ def measure(name, c, device, rank, world, dist, steps, warmup, with_e2e=True, sa
     tokens_local = c["T"] // world if ep else c["T"]
     tokens_all = c["T"] if ep else c["T"] * world
     layer, host = build_layer(name, c, tokens_local, device, seed=rank, ep_world=world if ep else 1, exchange=exchange,
-                             chunks=chunks)
+                             chunks=chunks, once_per_rank=once_per_rank)
     dev_in = {n: t.to(device) for n, t in host.items()}
 
     def barrier():
@@ -892,6 +893,9 @@ def main():
                     help="expert-parallel row exchange for N > 1: peer-memory kernels over NVLink, or NCCL all-to-all-v")
     ap.add_argument("--chunks", type=int, default=1,
                     help="pipeline chunks of the NVLink exchange (each chunk's transfers overlap the other's GEMMs)")
+    ap.add_argument("--once-per-rank", choices=("auto", "on", "off"), default="auto",
+                    help="NVLink exchange: send each token once per owning rank instead of once per slot (auto: when "
+                         "that saves at least a fifth of the rows)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-triton-ref", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
@@ -935,8 +939,10 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=device)
 
+    once = {"auto": None, "on": True, "off": False}[args.once_per_rank]
     fields, st = measure(name, c, device, rank, world, dist, args.steps, args.warmup, with_e2e=True,
-                         sampler_gpu=local_rank, exchange=args.exchange, chunks=args.chunks, keep=(world == 1))
+                         sampler_gpu=local_rank, exchange=args.exchange, chunks=args.chunks, keep=(world == 1),
+                         once_per_rank=once)
     line = {"metric": METRIC, "value": fields.pop("value"), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": fields.pop("ms_per_step"), "higher_is_better": True,
             "scaling": scaling, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
@@ -960,7 +966,7 @@ def main():
         st.clear()
         torch.cuda.empty_cache()
     elif not args.no_parity and ep:
-        line["parity"] = ep_parity_check(device, rank, world, dist, args.exchange, args.chunks)
+        line["parity"] = ep_parity_check(device, rank, world, dist, args.exchange, args.chunks, once)
         failed = failed or not line["parity"]["ok"]
 
     if not args.no_other_configs and name == "mixtral_8x7b":
@@ -973,7 +979,8 @@ def main():
                 continue
             try:
                 f, ost = measure(other, oc, device, rank, world, dist, short_steps, short_warm, with_e2e=(world > 1),
-                                 sampler_gpu=None, exchange=args.exchange, chunks=args.chunks, keep=(world == 1))
+                                 sampler_gpu=None, exchange=args.exchange, chunks=args.chunks, keep=(world == 1),
+                                 once_per_rank=once)
                 entry = {"ms_per_step": f["ms_per_step"], "value": f["value"], "unit": "tokens/s", "steps": short_steps,
                          "warmup": short_warm, "layer_frac_of_bf16_peak": f["layer_frac_of_bf16_peak"],
                          "forward_ms": f["forward"]["ms_per_step"], "abi_ms_per_step": f["abi_ms_per_step"],

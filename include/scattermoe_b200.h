@@ -239,6 +239,47 @@ int smoe_ep_dispatch(const void* X, int64_t x_rows, int64_t stride_xm, const int
 int smoe_ep_return(const void* Y, int64_t stride_ym, const int64_t* return_addr, const int64_t* live_rows,
                    int64_t capacity_rows, void* const* peer_slot_bufs, int64_t peer_stride_rows, int64_t peer_rows,
                    int32_t K, int32_t world, int32_t my_rank, int32_t local_experts, int32_t dtype, void* stream);
+/* ---- the same exchange with every token row crossing NVLink once per owning rank (no counterpart in the reference) ----
+ * A token whose k slots fall on n distinct ranks is sent n times instead of k times, and n rows come back. The caller
+ * lists the distinct (token, rank) pairs in rank order (a counting sort of each token's first slot per rank) and
+ * pushes the token rows with smoe_ep_dispatch over that list (E = world). The calls below carry the rest:
+ *
+ * smoe_ep_plan_tokens: for pair i (rank w = pair_rank[i], token t = pair_slot[i] / k), whose row lands at
+ *     row(t, w) = tok_base[w] + (i - first pair of w) of owner w's token buffer: tok_row[t, w] = row(t, w),
+ *     tok_parts[t] = number of owners of t, and into owner w's record buffer (smoe_ep_tokmeta_ints(k) int32 per row):
+ *     [this rank, return row t*min(k,world) + ordinal of w among t's owners, n slots, 0, position[k], gate bits[k]]
+ *     where position = place of each of t's slots at w in w's expert-grouped slot buffer (as in smoe_ep_dispatch) and
+ *     slot_pos[s] = position of slot s in this rank's expert-sorted list.
+ * smoe_ep_dispatch_meta: for every position m of the expert-sorted slot list, 16 bytes into the owner's slot record
+ *     buffer at the slot's position: [this rank << 40 | slot, row(t, w) | gate bits << 32].
+ * smoe_ep_expand (owner): out[p, :] = tok_rows[row(p), :] (* gate(p) if scale_by_gate) for p < *live_slots; with y_rows
+ *     also peer_dgate[rank(p)][slot(p)] = <y_rows[p, :], tok_rows[row(p), :]> as fp32 (the gate gradient).
+ * smoe_ep_combine (owner): for every received token row u < *live_tok with record [src, ret, n, -, pos[], gate[]]:
+ *     peer_comb[src][ret, :] = sum_i (gate[i] if use_gates else 1) * rows[pos[i], :]. src_base (world + 1, nullable):
+ *     first token row of each sending rank, used to start with the next rank's rows.
+ * smoe_ep_sum_parts (token owner): out[t, :] = sum over c < parts[t] of comb[t*kw + c, :].
+ * 16-bit dtypes, row widths multiples of 8, k <= 16. */
+int32_t smoe_ep_tokmeta_ints(int32_t k);
+int smoe_ep_plan_tokens(const int64_t* expert_idxs, const void* gates, int64_t T, int32_t k, const int64_t* pair_rank,
+                        const int64_t* pair_slot, const int64_t* pair_offsets, const int64_t* tok_base,
+                        const int64_t* slot_pos, const int64_t* expert_offsets, const int64_t* dst_offsets,
+                        int32_t* tok_row, int32_t* tok_parts, void* const* peer_tokmeta, int64_t cap_tok,
+                        int64_t cap_slots, int32_t my_rank, int32_t E, int32_t world, int32_t dtype, void* stream);
+int smoe_ep_dispatch_meta(const int64_t* sorted_expert_idxs, const int64_t* sorted_scattered_idxs,
+                          const int64_t* expert_offsets, const int64_t* dst_offsets, const void* gates,
+                          const int32_t* tok_row, int32_t k, void* const* peer_meta, int64_t cap_slots, int32_t my_rank,
+                          int64_t R, int32_t E, int32_t world, int32_t dtype, void* stream);
+int smoe_ep_expand(const void* tok_rows, int64_t stride_tok, int64_t cap_tok, const void* meta, const int64_t* live_slots,
+                   int64_t cap_slots, int32_t scale_by_gate, void* out, int64_t stride_out, const void* y_rows,
+                   int64_t stride_y, void* const* peer_dgate, int64_t peer_slots, int32_t K, int32_t world, int32_t dtype,
+                   void* stream);
+int smoe_ep_combine(const void* rows, int64_t stride_rows, int64_t cap_slots, const int32_t* tokmeta,
+                    const int64_t* live_tok, int64_t cap_tok, const int64_t* src_base, int32_t use_gates,
+                    void* const* peer_comb, int64_t peer_stride, int64_t peer_rows, int32_t K, int32_t k, int32_t my_rank,
+                    int32_t world, int32_t dtype, void* stream);
+int smoe_ep_sum_parts(const void* comb, int64_t stride_comb, const int32_t* parts, int32_t kw, void* out,
+                      int64_t stride_out, int64_t T, int32_t K, int32_t dtype, void* stream);
+
 /* Stream-ordered barrier across the ranks through peer memory: `peer_flags[w]` is rank w's int32[world] flag array
  * (zeroed once, before the first barrier, with the ranks synchronised by other means). Call with epoch = 1, 2, 3,
  * ... in the same order on every rank. Work enqueued after it on a rank runs after everything every rank

@@ -13,18 +13,9 @@
 //             slot-ordered (T*k, d) buffer, where the gate-weighted top-k sum and the gate gradient are local.
 // Synchronisation between the phases is the caller's (a stream-ordered barrier across the ranks); the kernels
 // themselves never wait on another GPU.
-#include "smoe_common.cuh"
+#include "ep_common.cuh"
 
 namespace smoe {
-
-constexpr int EP_MAX_WORLD = 16;
-struct PeerPtrs { uint8_t* p[EP_MAX_WORLD]; };
-
-__device__ __forceinline__ int64_t pack_dest(int rank, int64_t row) { return (static_cast<int64_t>(rank) << 40) | row; }
-__device__ __forceinline__ int dest_rank(int64_t d) { return static_cast<int>(d >> 40); }
-__device__ __forceinline__ int64_t dest_row(int64_t d) { return d & ((int64_t(1) << 40) - 1); }
-
-template <typename T> struct V16 { static constexpr int N = 16 / sizeof(T); };
 
 // One warp per sorted position m. Row m belongs to global expert e = sorted_e[m], owned by rank e / e_local; its
 // position in the owner's buffer is dst_off[e] + (m - first position of e in this rank's sorted list).
@@ -37,16 +28,19 @@ ep_dispatch_kernel(const T* __restrict__ X, int64_t x_rows, int64_t sxm, const i
                    int e_local, int world) {
   const int lane = threadIdx.x & 31;
   int64_t m = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
-  if (m >= R) return;
+  // the sorted list may be shorter than R (ids outside [0, E) are not part of it): its length is the last offset
+  int64_t live = offsets[E - 1];
+  live = live < 0 ? 0 : (live > R ? R : live);
+  if (m >= live) return;
   // Rank r starts with the rows of rank r+1's experts and wraps around: at any moment the ranks are then writing
   // to DIFFERENT owners. In plain sorted order every rank would first write to rank 0, then all to rank 1, ...:
   // eight senders into one receiver's NVLink ingress at a time.
   {
     const int first = ((my_rank + 1) % world) * e_local;
     int64_t shift = first ? offsets[first - 1] : 0;
-    shift = shift < 0 ? 0 : (shift > R ? R : shift);
+    shift = shift < 0 ? 0 : (shift > live ? live : shift);
     m += shift;
-    if (m >= R) m -= R;
+    if (m >= live) m -= live;
   }
   const int64_t e = sorted_e[m];
   const int64_t slot = sorted_idx[m];
@@ -146,25 +140,6 @@ ep_barrier_kernel(PeerPtrs flags, int my_rank, int world, int epoch, long long l
     }
     __nanosleep(64);
   }
-}
-
-static bool a16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
-
-static int fill_peers(PeerPtrs* pp, void* const* peer_bufs, int world, const char* who, bool* all_aligned) {
-  if (world < 1 || world > EP_MAX_WORLD) {
-    set_error("%s: world size %d out of range [1, %d]", who, world, EP_MAX_WORLD);
-    return SMOE_ERR_BAD_ARG;
-  }
-  *all_aligned = true;
-  for (int i = 0; i < EP_MAX_WORLD; ++i) {
-    pp->p[i] = i < world ? static_cast<uint8_t*>(peer_bufs[i]) : nullptr;
-    if (i < world && pp->p[i] == nullptr) {
-      set_error("%s: peer buffer %d is null", who, i);
-      return SMOE_ERR_BAD_ARG;
-    }
-    if (i < world && !a16(pp->p[i])) *all_aligned = false;
-  }
-  return SMOE_OK;
 }
 
 template <typename T>

@@ -200,14 +200,13 @@ class ExpertParallelGLUMLP(nn.Module):
 # NVLink peer-memory exchange: no all-to-all, no regroup copies, no host synchronisation
 # ------------------------------------------------------------------------------------------------------------
 
-class PeerRowBuffers:
-    """Symmetric (peer-mapped) buffers of one expert-parallel layer. At the expert owner: `x` (dispatched tokens),
-    `g` (dispatched output gradients), both (capacity, width) and expert-grouped, and `ret` (capacity,) int64
-    return addresses. At the token owner: `yslot`, `dxslot` (tokens*k, width), one row per (token, slot). Every
-    rank can address every rank's copy with plain stores over NVLink. Capacity is the worst case (all rows of all
-    ranks routed to one rank) unless told otherwise, so no routing outcome can overflow a buffer."""
+class PeerBuffers:
+    """Symmetric (peer-mapped) buffers of one expert-parallel layer: every rank can address every rank's copy with
+    plain loads and stores over NVLink. `shapes`: name -> (shape, dtype). `local[name]` is this rank's tensor,
+    `ptrs[name]` the table of all ranks' device pointers the C entry points take. Also holds the flag array of the
+    peer-memory barrier."""
 
-    def __init__(self, capacity_rows: int, slot_rows: int, width: int, dtype, device, group=None):
+    def __init__(self, shapes, device, group=None):
         import ctypes
         import os
         # plain peer mappings only: this code never uses NVLink multicast
@@ -216,11 +215,7 @@ class PeerRowBuffers:
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
-        self.capacity, self.slot_rows, self.width = int(capacity_rows), int(slot_rows), int(width)
         self.local, self.ptrs = {}, {}
-        shapes = {"x": ((self.capacity, self.width), dtype), "g": ((self.capacity, self.width), dtype),
-                  "ret": ((self.capacity,), torch.int64),
-                  "yslot": ((self.slot_rows, self.width), dtype), "dxslot": ((self.slot_rows, self.width), dtype)}
         for name, (shape, dt) in shapes.items():
             t = symm.empty(shape, dtype=dt, device=device)
             hdl = symm.rendezvous(t, self.group)
@@ -260,6 +255,45 @@ class PeerRowBuffers:
                 if t is not None and t.numel():
                     _ep_call("smoe_status_poison", _lib.status_word(self.device).data_ptr(), t.data_ptr(),
                              t.numel() * t.element_size(), _lib.stream_ptr(self.device))
+
+
+class PeerRowBuffers(PeerBuffers):
+    """Buffers of the per-slot exchange. At the expert owner: `x` (dispatched tokens), `g` (dispatched output
+    gradients), both (capacity, width) and expert-grouped, and `ret` (capacity,) int64 return addresses. At the token
+    owner: `yslot`, `dxslot` (tokens*k, width), one row per (token, slot). Capacity is the worst case (all rows of
+    all ranks routed to one rank) unless told otherwise, so no routing outcome can overflow a buffer."""
+
+    def __init__(self, capacity_rows: int, slot_rows: int, width: int, dtype, device, group=None):
+        self.capacity, self.slot_rows, self.width = int(capacity_rows), int(slot_rows), int(width)
+        super().__init__({"x": ((self.capacity, self.width), dtype), "g": ((self.capacity, self.width), dtype),
+                          "ret": ((self.capacity,), torch.int64),
+                          "yslot": ((self.slot_rows, self.width), dtype), "dxslot": ((self.slot_rows, self.width), dtype)},
+                         device, group)
+
+
+class PeerTokenBuffers(PeerBuffers):
+    """Buffers of the exchange that sends every token once per owning rank. At the expert owner: `xtok`, `gtok`
+    (token capacity, width) received token / output-gradient rows, `meta` (slot capacity, 2) int64 one record per
+    slot in expert-grouped order, `tokmeta` (token capacity, n) int32 one record per received token row. At the token
+    owner: `ycomb`, `dxcomb` (tokens * min(k, world), width) one row per (token, owning rank), `dgate` (tokens*k,)
+    fp32 gate gradients. Capacities are the worst case (every token of every rank routed here)."""
+
+    def __init__(self, token_capacity: int, local_tokens: int, k: int, width: int, dtype, device, group=None):
+        from . import _lib
+        world = dist.get_world_size(group if group is not None else dist.group.WORLD)
+        self.token_capacity, self.capacity = int(token_capacity), int(token_capacity) * k      # rows: tokens, slots
+        self.local_tokens, self.k, self.width = int(local_tokens), int(k), int(width)
+        self.slot_rows = self.local_tokens * k
+        self.kw = min(k, world)
+        self.tm_ints = int(_lib.load().smoe_ep_tokmeta_ints(k))
+        if self.tm_ints <= 0:
+            raise AssertionError("the once-per-rank exchange lists at most 16 slots per token (k=%d)" % k)
+        super().__init__({"xtok": ((self.token_capacity, self.width), dtype), "gtok": ((self.token_capacity, self.width), dtype),
+                          "meta": ((self.capacity, 2), torch.int64),
+                          "tokmeta": ((self.token_capacity, self.tm_ints), torch.int32),
+                          "ycomb": ((self.local_tokens * self.kw, self.width), dtype),
+                          "dxcomb": ((self.local_tokens * self.kw, self.width), dtype),
+                          "dgate": ((self.slot_rows,), torch.float32)}, device, group)
 
 
 # Wait limit of the peer-memory barrier in SM clocks (0: the library's default, about one second). A rank that is
@@ -386,6 +420,151 @@ class _PeerExchangeMLP(torch.autograd.Function):
         return dx, d_gates, None, d_w_up.permute(0, 2, 1), d_w_down.permute(0, 2, 1), None
 
 
+class _PeerTokenExchangeMLP(torch.autograd.Function):
+    """dispatch -> local expert GLU-MLP -> return on `PeerTokenBuffers`: every token row crosses NVLink once per
+    owning rank each way (csrc/ep_dedup.cu). Same results as `_PeerExchangeMLP`; the gate weighting and the gate
+    gradient are computed at the expert owner, which receives the gates with the slot records."""
+
+    @staticmethod
+    def forward(ctx, x, gates, expert_idxs, w_up, w_down, layer):
+        from . import _lib
+        bufs: PeerTokenBuffers = layer.buffers
+        W, rank, E = bufs.world, bufs.rank, layer.num_experts
+        e_local = E // W
+        T, k = expert_idxs.shape
+        R, d = T * k, x.size(1)
+        dev = x.device
+        code = _lib.DTYPE_CODE[x.dtype]
+        stream = _lib.stream_ptr(dev)
+        x = x.contiguous()
+        gates = gates.to(x.dtype).contiguous()
+        ids = expert_idxs.to(torch.int64).contiguous()
+
+        # 1. plan. Slots sorted by expert (as in the per-slot exchange) and the distinct (token, owning rank) pairs
+        #    sorted by rank: a slot opens a pair when no earlier slot of its token has the same owner.
+        sorted_e, sorted_idx, offsets = flatten_sort_count(ids, E)
+        slot_pos = torch.empty_like(sorted_idx)
+        slot_pos[sorted_idx] = torch.arange(R, device=dev, dtype=sorted_idx.dtype)
+        owner = ids // e_local
+        repeat = (owner.unsqueeze(2) == owner.unsqueeze(1)).tril(-1).any(-1)
+        pair_rank, pair_slot, pair_offsets = flatten_sort_count(torch.where(repeat, -1, owner), W)
+        counts = torch.diff(offsets, prepend=offsets.new_zeros(1))
+        pair_counts = torch.diff(pair_offsets, prepend=pair_offsets.new_zeros(1))
+        gathered = torch.empty((W, E + W), dtype=counts.dtype, device=dev)
+        dist.all_gather_into_tensor(gathered, torch.cat([counts, pair_counts]), group=bufs.group)
+        counts_all, pairs_all = gathered[:, :E], gathered[:, E:]          # [sender, expert], [sender, owner]
+        tot = counts_all.sum(0).view(W, e_local)
+        ebase = (tot.cumsum(1) - tot).flatten()
+        dst_off = (ebase + (counts_all.cumsum(0) - counts_all)[rank]).contiguous()
+        local_offsets = tot[rank].cumsum(0).contiguous()
+        live_slots = local_offsets[-1:]
+        tok_base = (pairs_all.cumsum(0) - pairs_all)[rank].contiguous()   # my first row in each owner's token buffer
+        src_base = torch.cat([pairs_all.new_zeros(1), pairs_all[:, rank].cumsum(0)]).contiguous()   # here, per sender
+        live_tok = src_base[-1:]
+        tok_row = torch.empty((T, W), dtype=torch.int32, device=dev)
+        tok_parts = torch.zeros((T,), dtype=torch.int32, device=dev)
+        # 2. dispatch: one record per (token, owner) pair, the token rows (once per owner), one record per slot
+        with torch.cuda.device(dev):
+            _ep_call("smoe_ep_plan_tokens", ids.data_ptr(), gates.data_ptr(), T, k, pair_rank.data_ptr(),
+                     pair_slot.data_ptr(), pair_offsets.data_ptr(), tok_base.data_ptr(), slot_pos.data_ptr(),
+                     offsets.data_ptr(), dst_off.data_ptr(), tok_row.data_ptr(), tok_parts.data_ptr(), bufs.ptrs["tokmeta"],
+                     bufs.token_capacity, bufs.capacity, rank, E, W, code, stream)
+            _ep_call("smoe_ep_dispatch", x.data_ptr(), T, x.stride(0), pair_rank.data_ptr(), pair_slot.data_ptr(),
+                     pair_offsets.data_ptr(), tok_base.data_ptr(), 0, k, bufs.ptrs["xtok"], bufs.width,
+                     bufs.token_capacity, 0, rank, R, d, W, W, code, stream)
+            _ep_call("smoe_ep_dispatch_meta", sorted_e.data_ptr(), sorted_idx.data_ptr(), offsets.data_ptr(),
+                     dst_off.data_ptr(), gates.data_ptr(), tok_row.data_ptr(), k, bufs.ptrs["meta"], bufs.capacity, rank, R,
+                     E, W, code, stream)
+        bufs.barrier()
+        # 3. owner: token rows into expert order (a copy in local HBM), then the expert MLP as in the per-slot exchange
+        cap = bufs.capacity
+        dummy = layer.dummy_index(cap, dev)
+        xb = torch.empty((cap, d), dtype=x.dtype, device=dev)
+        with torch.cuda.device(dev):
+            _ep_call("smoe_ep_expand", bufs.local["xtok"].data_ptr(), bufs.width, bufs.token_capacity,
+                     bufs.local["meta"].data_ptr(), live_slots.data_ptr(), cap, 0, xb.data_ptr(), xb.stride(0), 0, 0, 0, 0,
+                     d, W, code, stream)
+        fused = ops.scatter2scatter_act(xb, w_up.permute(0, 2, 1), dummy, dummy, 1, _act.LAYOUT_GLU_SECOND,
+                                        layer.act_code, x_grouped=True, expert_offsets=local_offsets)
+        if fused is None:
+            up = ops.scatter2scatter(xb, w_up.permute(0, 2, 1), dummy, dummy, 1, x_grouped=True, y_grouped=True,
+                                     expert_offsets=local_offsets)
+            hidden = torch.empty((cap, w_down.size(2)), dtype=x.dtype, device=dev)
+            _act._call(False, up, None, hidden, hidden.size(1), _act.LAYOUT_GLU_SECOND, layer.act_code, 1.702, 7.0,
+                       live_slots)
+        else:
+            up, hidden = fused
+        y_rows = ops.scatter2scatter(hidden, w_down.permute(0, 2, 1), dummy, dummy, 1, x_grouped=True, y_grouped=True,
+                                     expert_offsets=local_offsets)
+        # 4. one gate-weighted row per received token goes back to its owner
+        with torch.cuda.device(dev):
+            _ep_call("smoe_ep_combine", y_rows.data_ptr(), y_rows.stride(0), cap, bufs.local["tokmeta"].data_ptr(),
+                     live_tok.data_ptr(), bufs.token_capacity, src_base.data_ptr(), 1, bufs.ptrs["ycomb"], bufs.width,
+                     T * bufs.kw, d, k, rank, W, code, stream)
+        bufs.barrier()
+        out = torch.empty((T, d), dtype=x.dtype, device=dev)
+        with torch.cuda.device(dev):
+            _ep_call("smoe_ep_sum_parts", bufs.local["ycomb"].data_ptr(), bufs.width, tok_parts.data_ptr(), bufs.kw,
+                     out.data_ptr(), out.stride(0), T, d, code, stream)
+        bufs.poison_if_a_wait_expired(out)
+        layer.last_rows_dev = live_slots
+        ctx.layer = layer
+        ctx.shape = (T, k, d)
+        ctx.gates_dtype = gates.dtype
+        ctx.save_for_backward(pair_rank, pair_slot, pair_offsets, tok_base, src_base, local_offsets, tok_parts, xb, up,
+                              hidden, y_rows, w_up, w_down)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        from . import _lib
+        layer = ctx.layer
+        bufs: PeerTokenBuffers = layer.buffers
+        (pair_rank, pair_slot, pair_offsets, tok_base, src_base, local_offsets, tok_parts, xb, up, hidden, y_rows, w_up,
+         w_down) = ctx.saved_tensors
+        live_slots, live_tok = local_offsets[-1:], src_base[-1:]
+        T, k, d = ctx.shape
+        W, rank = bufs.world, bufs.rank
+        dev = grad_out.device
+        grad_out = grad_out.to(up.dtype).contiguous()
+        code = _lib.DTYPE_CODE[up.dtype]
+        stream = _lib.stream_ptr(dev)
+        cap = bufs.capacity
+        e_local = w_up.size(0)
+        # the output gradient of every token goes, un-weighted and once, to each rank that owns one of its slots
+        with torch.cuda.device(dev):
+            _ep_call("smoe_ep_dispatch", grad_out.data_ptr(), T, grad_out.stride(0), pair_rank.data_ptr(),
+                     pair_slot.data_ptr(), pair_offsets.data_ptr(), tok_base.data_ptr(), 0, k, bufs.ptrs["gtok"], bufs.width,
+                     bufs.token_capacity, 0, rank, T * k, d, W, W, code, stream)
+        bufs.barrier()
+        # owner: expand with the gate applied; the same pass computes every slot's gate gradient (its saved expert
+        # output times the un-weighted output gradient) and stores it at the token owner
+        gb = torch.empty((cap, d), dtype=up.dtype, device=dev)
+        with torch.cuda.device(dev):
+            _ep_call("smoe_ep_expand", bufs.local["gtok"].data_ptr(), bufs.width, bufs.token_capacity,
+                     bufs.local["meta"].data_ptr(), live_slots.data_ptr(), cap, 1, gb.data_ptr(), gb.stride(0),
+                     y_rows.data_ptr(), y_rows.stride(0), bufs.ptrs["dgate"], T * k, d, W, code, stream)
+        dummy = layer.dummy_index(cap, dev)
+        d_up = ops.scatter2scatter_act_bwd(gb, w_down, up, local_offsets, _act.LAYOUT_GLU_SECOND, layer.act_code)
+        dx_rows = ops.scatter2scatter(d_up, w_up, dummy, dummy, 1, x_grouped=True, y_grouped=True,
+                                      expert_offsets=local_offsets)
+        with torch.cuda.device(dev):
+            _ep_call("smoe_ep_combine", dx_rows.data_ptr(), dx_rows.stride(0), cap, bufs.local["tokmeta"].data_ptr(),
+                     live_tok.data_ptr(), bufs.token_capacity, src_base.data_ptr(), 0, bufs.ptrs["dxcomb"], bufs.width,
+                     T * bufs.kw, d, k, rank, W, code, stream)
+        # the rows travel home while the two weight gradients run
+        d_w_down, _ = ops.group_bwd_W(gb, hidden, local_offsets, e_local)
+        d_w_up, _ = ops.group_bwd_W(d_up, xb, local_offsets, e_local)
+        bufs.barrier()
+        dx = torch.empty((T, d), dtype=up.dtype, device=dev)
+        with torch.cuda.device(dev):
+            _ep_call("smoe_ep_sum_parts", bufs.local["dxcomb"].data_ptr(), bufs.width, tok_parts.data_ptr(), bufs.kw,
+                     dx.data_ptr(), dx.stride(0), T, d, code, stream)
+        d_gates = bufs.local["dgate"].view(T, k).to(ctx.gates_dtype) if ctx.needs_input_grad[1] else None
+        bufs.poison_if_a_wait_expired(dx, d_gates, d_w_up, d_w_down)
+        return dx, d_gates, None, d_w_up.permute(0, 2, 1), d_w_down.permute(0, 2, 1), None
+
+
 class _PeerChunk:
     """State of one pipeline chunk of a peer-memory layer: its own buffers (so chunks never touch each other's
     rows or flags), its stream, and the bits of layer configuration the autograd function needs."""
@@ -421,8 +600,18 @@ class PeerExpertParallelGLUMLP(ExpertParallelGLUMLP):
     """
 
     def __init__(self, input_size, hidden_size, num_experts, top_k, group=None, activation=nn.SiLU(),
-                 capacity_rows=None, global_tokens=None, chunks=1):
+                 capacity_rows=None, global_tokens=None, chunks=1, once_per_rank=None):
         super().__init__(input_size, hidden_size, num_experts, top_k, group=group, activation=activation)
+        # once_per_rank: send every token row once per owning rank (csrc/ep_dedup.cu) instead of once per slot.
+        # Default: when that saves at least a fifth of the rows. With uniform routing a token's top_k slots fall on
+        # about world * (1 - (1 - 1/world) ** top_k) distinct ranks.
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        owners = world * (1.0 - (1.0 - 1.0 / world) ** self.top_k)
+        if once_per_rank is None:
+            once_per_rank = 1 < self.top_k <= 16 and owners <= 0.8 * self.top_k
+        self.once_per_rank = bool(once_per_rank)
+        if self.once_per_rank and not (1 <= self.top_k <= 16):
+            raise AssertionError("once_per_rank needs top_k <= 16")
         self.act_code = _act.resolve_activation(activation)
         if self.act_code is None:
             raise AssertionError("PeerExpertParallelGLUMLP needs an activation this library fuses (SiLU, GELU, ReLU)")
@@ -450,7 +639,12 @@ class PeerExpertParallelGLUMLP(ExpertParallelGLUMLP):
             if cap is None:
                 cap = (self._global_tokens * self.top_k) if self._global_tokens else chunk_rows * self.chunks * world
             cap = ((int(cap) + self.chunks - 1) // self.chunks + 127) // 128 * 128
-            c.buffers = PeerRowBuffers(cap, chunk_rows, self.input_size, x.dtype, x.device, self.group)
+            if self.once_per_rank:
+                k = self.top_k
+                c.buffers = PeerTokenBuffers((cap + k - 1) // k, chunk_rows // k, k, self.input_size, x.dtype, x.device,
+                                             self.group)
+            else:
+                c.buffers = PeerRowBuffers(cap, chunk_rows, self.input_size, x.dtype, x.device, self.group)
             c.stream = torch.cuda.Stream(device=x.device) if self.chunks > 1 else None
 
     def forward(self, x: torch.Tensor, expert_p: torch.Tensor, expert_idxs: torch.Tensor):
@@ -466,8 +660,9 @@ class PeerExpertParallelGLUMLP(ExpertParallelGLUMLP):
         tc = T // self.chunks
         self._ensure_buffers(tokens, tc * idx.size(1))
         w_up, w_down = self.experts.weight, self.output_experts.weight
+        exchange = _PeerTokenExchangeMLP if self.once_per_rank else _PeerExchangeMLP
         if self.chunks == 1:
-            y = _PeerExchangeMLP.apply(tokens, gates, idx, w_up, w_down, self._chunk_state[0])
+            y = exchange.apply(tokens, gates, idx, w_up, w_down, self._chunk_state[0])
             return y.view(*lead, y.size(-1))
         cur = torch.cuda.current_stream(tokens.device)
         outs = []
@@ -475,7 +670,7 @@ class PeerExpertParallelGLUMLP(ExpertParallelGLUMLP):
             c.stream.wait_stream(cur)
             sl = slice(i * tc, (i + 1) * tc)
             with torch.cuda.stream(c.stream):
-                outs.append(_PeerExchangeMLP.apply(tokens[sl], gates[sl], idx[sl], w_up, w_down, c))
+                outs.append(exchange.apply(tokens[sl], gates[sl], idx[sl], w_up, w_down, c))
         for c, o in zip(self._chunk_state, outs):
             cur.wait_stream(c.stream)
             o.record_stream(cur)

@@ -59,7 +59,7 @@ def test_single_rank_equals_glumlp():
     sm.check_device_status(dev)
 
 
-def _worker(rank, world, port, ret, peer=False, chunks=1, problem=None):
+def _worker(rank, world, port, ret, peer=False, chunks=1, problem=None, once_per_rank=None):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
     dev = torch.device("cuda", rank)
@@ -74,7 +74,8 @@ def _worker(rank, world, port, ret, peer=False, chunks=1, problem=None):
         ts, es = slice(rank * tl, (rank + 1) * tl), slice(rank * el, (rank + 1) * el)
         want = _reference_on(dev, x, p, idx, w1, w2, dy)
         if peer:
-            m = PeerExpertParallelGLUMLP(x.size(1), w2.size(2), E, idx.size(1), chunks=chunks).to(dev).bfloat16()
+            m = PeerExpertParallelGLUMLP(x.size(1), w2.size(2), E, idx.size(1), chunks=chunks,
+                                         once_per_rank=once_per_rank).to(dev).bfloat16()
         else:
             m = ExpertParallelGLUMLP(x.size(1), w2.size(2), E, idx.size(1)).to(dev).bfloat16()
         with torch.no_grad():
@@ -99,14 +100,15 @@ def _worker(rank, world, port, ret, peer=False, chunks=1, problem=None):
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 @pytest.mark.parametrize("problem", [None, dict(T=1024, d=256, F=128, E=16, k=8, seed=9)], ids=["k2_E8", "k8_E16"])
-@pytest.mark.parametrize("peer,chunks", [(False, 1), (True, 1), (True, 2)],
-                         ids=["nccl_all_to_all", "nvlink_peer_memory", "nvlink_peer_memory_2_chunks"])
-def test_two_ranks_equal_the_single_gpu_layer(peer, chunks, problem):
+@pytest.mark.parametrize("peer,chunks,once", [(False, 1, None), (True, 1, False), (True, 1, True), (True, 2, False), (True, 2, True)],
+                         ids=["nccl_all_to_all", "nvlink_per_slot", "nvlink_once_per_rank", "nvlink_per_slot_2_chunks",
+                              "nvlink_once_per_rank_2_chunks"])
+def test_two_ranks_equal_the_single_gpu_layer(peer, chunks, once, problem):
     s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         ret = mgr.dict()
-        procs = [ctx.Process(target=_worker, args=(r, 2, port, ret, peer, chunks, problem)) for r in range(2)]
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, ret, peer, chunks, problem, once)) for r in range(2)]
         for q in procs:
             q.start()
         for q in procs:
