@@ -230,9 +230,7 @@ int smoe_single2scatter(const void* X, int64_t x_rows, int64_t stride_xm, int64_
  *     (r, s) = return_addr[i];  peer_slot_bufs[r][s, :] = Y[i, :]           (peer buffers are (peer_rows, stride))
  * Both kernels walk their rows in an order rotated by the calling rank (dispatch: starting with the next rank's
  * experts; return: starting `my_rank` (expert, sender) sub-segments in, `local_experts` = E / world), so that at any
- * moment the ranks write to different peers instead of all to the same one. `grid_limit` (smoe_ep_return,
- * smoe_ep_combine; 0 = the default) caps the number of thread blocks: a caller that runs the push on a second stream
- * beside a grouped GEMM keeps it small (a few blocks per SM) so that both kernels fit on the SMs at once. */
+ * moment the ranks write to different peers instead of all to the same one. */
 int smoe_ep_dispatch(const void* X, int64_t x_rows, int64_t stride_xm, const int64_t* sorted_expert_idxs,
                      const int64_t* sorted_scattered_idxs, const int64_t* expert_offsets, const int64_t* dst_offsets,
                      const void* coeff, int32_t fan_out, void* const* peer_bufs, int64_t peer_stride_rows,
@@ -240,8 +238,7 @@ int smoe_ep_dispatch(const void* X, int64_t x_rows, int64_t stride_xm, const int
                      int32_t E, int32_t world, int32_t dtype, void* stream);
 int smoe_ep_return(const void* Y, int64_t stride_ym, const int64_t* return_addr, const int64_t* live_rows,
                    int64_t capacity_rows, void* const* peer_slot_bufs, int64_t peer_stride_rows, int64_t peer_rows,
-                   int32_t K, int32_t world, int32_t my_rank, int32_t local_experts, int32_t dtype, int32_t grid_limit,
-                   void* stream);
+                   int32_t K, int32_t world, int32_t my_rank, int32_t local_experts, int32_t dtype, void* stream);
 /* ---- the same exchange with every token row crossing NVLink once per owning rank (no counterpart in the reference) ----
  * A token whose k slots fall on n distinct ranks is sent n times instead of k times, and n rows come back. The caller
  * lists the distinct (token, rank) pairs in rank order (a counting sort of each token's first slot per rank) and
@@ -279,7 +276,7 @@ int smoe_ep_expand(const void* tok_rows, int64_t stride_tok, int64_t cap_tok, co
 int smoe_ep_combine(const void* rows, int64_t stride_rows, int64_t cap_slots, const int32_t* tokmeta,
                     const int64_t* live_tok, int64_t cap_tok, const int64_t* src_base, int32_t use_gates,
                     void* const* peer_comb, int64_t peer_stride, int64_t peer_rows, int32_t K, int32_t k, int32_t my_rank,
-                    int32_t world, int32_t dtype, int32_t grid_limit, void* stream);
+                    int32_t world, int32_t dtype, void* stream);
 int smoe_ep_sum_parts(const void* comb, int64_t stride_comb, const int32_t* parts, int32_t kw, void* out,
                       int64_t stride_out, int64_t T, int32_t K, int32_t dtype, void* stream);
 

@@ -74,15 +74,14 @@ SIGNATURES = {
                             c_int32),
     "smoe_ep_dispatch": ([_P, _I64, _I64, _P, _P, _P, _P, _P, _I32, _P, _I64, _I64, _P, _I32, _I64, _I32, _I32, _I32, _I32,
                           _P], c_int32),
-    "smoe_ep_return": ([_P, _I64, _P, _P, _I64, _P, _I64, _I64, _I32, _I32, _I32, _I32, _I32, _I32, _P], c_int32),
+    "smoe_ep_return": ([_P, _I64, _P, _P, _I64, _P, _I64, _I64, _I32, _I32, _I32, _I32, _I32, _P], c_int32),
     "smoe_ep_barrier": ([_P, _I32, _I32, _I32, _I64, _P, _P], c_int32),
     "smoe_ep_tokmeta_ints": ([_I32], c_int32),
     "smoe_ep_plan_tokens": ([_P, _P, _I64, _I32, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _I32, _I32, _I32,
                              _P], c_int32),
     "smoe_ep_dispatch_meta": ([_P, _P, _P, _P, _P, _P, _I32, _P, _I64, _I32, _I64, _I32, _I32, _I32, _P], c_int32),
     "smoe_ep_expand": ([_P, _I64, _I64, _P, _P, _I64, _I32, _P, _I64, _P, _I64, _P, _I64, _I32, _I32, _I32, _P], c_int32),
-    "smoe_ep_combine": ([_P, _I64, _I64, _P, _P, _I64, _P, _I32, _P, _I64, _I64, _I32, _I32, _I32, _I32, _I32, _I32, _P],
-                        c_int32),
+    "smoe_ep_combine": ([_P, _I64, _I64, _P, _P, _I64, _P, _I32, _P, _I64, _I64, _I32, _I32, _I32, _I32, _I32, _P], c_int32),
     "smoe_ep_sum_parts": ([_P, _I64, _P, _I32, _P, _I64, _I64, _I32, _I32, _P], c_int32),
     "smoe_status_poison": ([_P, _P, _I64, _P], c_int32),
 }

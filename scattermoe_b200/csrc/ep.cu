@@ -166,12 +166,11 @@ static int dispatch_typed(const void* X, int64_t x_rows, int64_t sxm, const int6
 template <typename T>
 static int return_typed(const void* Y, int64_t sym, const int64_t* ret_addr, const int64_t* live_rows, int64_t cap_rows,
                         const PeerPtrs& pp, bool aligned, int64_t peer_row_elems, int64_t peer_rows, int K, int world,
-                        int64_t shift_num, int64_t shift_den, int grid_limit, cudaStream_t st) {
+                        int64_t shift_num, int64_t shift_den, cudaStream_t st) {
   constexpr int V = 16 / sizeof(T);
   const bool vec = aligned && K % V == 0 && sym % V == 0 && peer_row_elems % V == 0 && a16(Y);
   const int64_t want = cdiv64(cap_rows, 8);
-  const int64_t cap = grid_limit > 0 ? grid_limit : 148 * 16;
-  const unsigned grid = static_cast<unsigned>(want < cap ? want : cap);
+  const unsigned grid = static_cast<unsigned>(want < 148 * 16 ? want : 148 * 16);
   if (vec)
     ep_return_kernel<T, true><<<grid, 256, 0, st>>>((const T*)Y, sym, ret_addr, live_rows, cap_rows, pp, peer_row_elems,
                                                     peer_rows, K, world, shift_num, shift_den);
@@ -222,7 +221,7 @@ extern "C" int smoe_ep_dispatch(const void* X, int64_t x_rows, int64_t stride_xm
 extern "C" int smoe_ep_return(const void* Y, int64_t stride_ym, const int64_t* return_addr, const int64_t* live_rows,
                               int64_t capacity_rows, void* const* peer_slot_bufs, int64_t peer_stride_rows,
                               int64_t peer_rows, int32_t K, int32_t world, int32_t my_rank, int32_t local_experts,
-                              int32_t dtype, int32_t grid_limit, void* stream) {
+                              int32_t dtype, void* stream) {
   SMOE_CHECK_ARG(capacity_rows >= 0 && K >= 0, "ep_return: bad sizes rows=%lld K=%d", (long long)capacity_rows, K);
   SMOE_CHECK_ARG(my_rank >= 0 && my_rank < world && local_experts >= 1, "ep_return: rank %d of %d, %d local experts",
                  my_rank, world, local_experts);
@@ -234,9 +233,9 @@ extern "C" int smoe_ep_return(const void* Y, int64_t stride_ym, const int64_t* r
   if (int rc = fill_peers(&pp, peer_slot_bufs, world, "ep_return", &aligned)) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
-    case SMOE_F32: return return_typed<float>(Y, stride_ym, return_addr, live_rows, capacity_rows, pp, aligned, peer_stride_rows, peer_rows, K, world, shift_num, shift_den, grid_limit, st);
-    case SMOE_BF16: return return_typed<__nv_bfloat16>(Y, stride_ym, return_addr, live_rows, capacity_rows, pp, aligned, peer_stride_rows, peer_rows, K, world, shift_num, shift_den, grid_limit, st);
-    case SMOE_F16: return return_typed<__half>(Y, stride_ym, return_addr, live_rows, capacity_rows, pp, aligned, peer_stride_rows, peer_rows, K, world, shift_num, shift_den, grid_limit, st);
+    case SMOE_F32: return return_typed<float>(Y, stride_ym, return_addr, live_rows, capacity_rows, pp, aligned, peer_stride_rows, peer_rows, K, world, shift_num, shift_den, st);
+    case SMOE_BF16: return return_typed<__nv_bfloat16>(Y, stride_ym, return_addr, live_rows, capacity_rows, pp, aligned, peer_stride_rows, peer_rows, K, world, shift_num, shift_den, st);
+    case SMOE_F16: return return_typed<__half>(Y, stride_ym, return_addr, live_rows, capacity_rows, pp, aligned, peer_stride_rows, peer_rows, K, world, shift_num, shift_den, st);
   }
   set_error("ep_return: unknown dtype %d", dtype);
   return SMOE_ERR_BAD_ARG;

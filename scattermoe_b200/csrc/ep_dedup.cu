@@ -260,9 +260,9 @@ static int check16(const char* who, int dtype, int K) {
   return SMOE_OK;
 }
 
-static unsigned capped_grid(int64_t units_of_8_rows, int64_t limit = 148 * 16) {
+static unsigned capped_grid(int64_t units_of_8_rows) {
   const int64_t want = units_of_8_rows > 0 ? units_of_8_rows : 1;
-  return static_cast<unsigned>(want < limit ? want : limit);
+  return static_cast<unsigned>(want < 148 * 16 ? want : 148 * 16);
 }
 
 }  // namespace smoe
@@ -366,7 +366,7 @@ extern "C" int smoe_ep_expand(const void* tok_rows, int64_t stride_tok, int64_t 
 extern "C" int smoe_ep_combine(const void* rows, int64_t stride_rows, int64_t cap_slots, const int32_t* tokmeta,
                                const int64_t* live_tok, int64_t cap_tok, const int64_t* src_base, int32_t use_gates,
                                void* const* peer_comb, int64_t peer_stride, int64_t peer_rows, int32_t K, int32_t k,
-                               int32_t my_rank, int32_t world, int32_t dtype, int32_t grid_limit, void* stream) {
+                               int32_t my_rank, int32_t world, int32_t dtype, void* stream) {
   SMOE_CHECK_ARG(cap_tok >= 0 && cap_slots >= 0 && K >= 0 && k >= 1 && k <= EP_MAX_K, "ep_combine: bad sizes (k=%d)", k);
   SMOE_CHECK_ARG(my_rank >= 0 && my_rank < world, "ep_combine: rank %d of %d", my_rank, world);
   if (int rc = check16("ep_combine", dtype, K)) return rc;
@@ -377,7 +377,7 @@ extern "C" int smoe_ep_combine(const void* rows, int64_t stride_rows, int64_t ca
   bool aligned;
   if (int rc = fill_peers(&pp, peer_comb, world, "ep_combine", &aligned)) return rc;
   SMOE_CHECK_ARG(aligned, "ep_combine: the return buffers must be 16-byte aligned");
-  const unsigned grid = capped_grid(cdiv64(cap_tok, 8), grid_limit > 0 ? grid_limit : 148 * 16);
+  const unsigned grid = capped_grid(cdiv64(cap_tok, 8));
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == SMOE_BF16)
     ep_combine_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(rows), stride_rows, cap_slots,

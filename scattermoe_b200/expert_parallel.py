@@ -302,37 +302,6 @@ class PeerTokenBuffers(PeerBuffers):
 BARRIER_LIMIT_CYCLES = 0
 
 
-# Thread blocks of a push kernel that runs on a second stream beside a grouped GEMM: three per SM leave the GEMM's
-# one 320-thread block per SM its registers and thread slots.
-PUSH_BLOCKS_BESIDE_A_GEMM = 148 * 3
-
-
-class _beside:
-    """`with _beside(layer, device, tensor) as stream_ptr:` enqueue on the layer's second stream, after everything
-    enqueued so far on the current one; `_join` makes the current stream wait for it again."""
-
-    def __init__(self, layer, device, *tensors):
-        self.layer, self.device, self.tensors = layer, device, tensors
-
-    def __enter__(self):
-        if self.layer.side_stream is None:
-            self.layer.side_stream = torch.cuda.Stream(device=self.device)
-        side = self.layer.side_stream
-        side.wait_stream(torch.cuda.current_stream(self.device))
-        for t in self.tensors:
-            t.record_stream(side)
-        self._ctx = torch.cuda.stream(side)
-        self._ctx.__enter__()
-        return side.cuda_stream
-
-    def __exit__(self, *exc):
-        return self._ctx.__exit__(*exc)
-
-
-def _join(layer, device):
-    torch.cuda.current_stream(device).wait_stream(layer.side_stream)
-
-
 def _ep_call(name, *args):
     from . import _lib
     rc = getattr(_lib.load(), name)(*args)
@@ -396,7 +365,7 @@ class _PeerExchangeMLP(torch.autograd.Function):
         with torch.cuda.device(dev):
             _ep_call("smoe_ep_return", y_rows.data_ptr(), y_rows.stride(0), bufs.local["ret"].data_ptr(),
                      rows_dev.data_ptr(), cap, bufs.ptrs["yslot"], bufs.width, bufs.slot_rows, d, W, rank, e_local, code,
-                     0, stream)
+                     stream)
         bufs.barrier()
         out = ops.topk_reduce(bufs.local["yslot"], gates, T, k)
         bufs.poison_if_a_wait_expired(out)
@@ -437,15 +406,13 @@ class _PeerExchangeMLP(torch.autograd.Function):
         d_up = ops.scatter2scatter_act_bwd(gb, w_down, up, local_offsets, _act.LAYOUT_GLU_SECOND, layer.act_code)
         dx_rows = ops.scatter2scatter(d_up, w_up, dummy, dummy, 1, x_grouped=True, y_grouped=True,
                                       expert_offsets=local_offsets)
-        # ... on a second stream, with few enough thread blocks to share the SMs with the two weight gradients that run
-        # meanwhile; the barrier that follows waits for both
-        with _beside(layer, dev, dx_rows) as side_stream:
+        with torch.cuda.device(dev):
             _ep_call("smoe_ep_return", dx_rows.data_ptr(), dx_rows.stride(0), bufs.local["ret"].data_ptr(),
                      rows_dev.data_ptr(), cap, bufs.ptrs["dxslot"], bufs.width, bufs.slot_rows, d, W, rank, e_local, code,
-                     PUSH_BLOCKS_BESIDE_A_GEMM, side_stream)
+                     stream)
+        # ... while the two weight gradients run: the barrier that follows them finds the peers' rows already here
         d_w_down, _ = ops.group_bwd_W(gb, hidden, local_offsets, e_local)
         d_w_up, _ = ops.group_bwd_W(d_up, xb, local_offsets, e_local)
-        _join(layer, dev)
         bufs.barrier()
         dx = ops.topk_reduce(bufs.local["dxslot"], None, T, k) if k > 1 else bufs.local["dxslot"].clone()
         bufs.poison_if_a_wait_expired(dx, d_gates, d_w_up, d_w_down)
@@ -533,7 +500,7 @@ class _PeerTokenExchangeMLP(torch.autograd.Function):
         with torch.cuda.device(dev):
             _ep_call("smoe_ep_combine", y_rows.data_ptr(), y_rows.stride(0), cap, bufs.local["tokmeta"].data_ptr(),
                      live_tok.data_ptr(), bufs.token_capacity, src_base.data_ptr(), 1, bufs.ptrs["ycomb"], bufs.width,
-                     T * bufs.kw, d, k, rank, W, code, 0, stream)
+                     T * bufs.kw, d, k, rank, W, code, stream)
         bufs.barrier()
         out = torch.empty((T, d), dtype=x.dtype, device=dev)
         with torch.cuda.device(dev):
@@ -581,14 +548,13 @@ class _PeerTokenExchangeMLP(torch.autograd.Function):
         d_up = ops.scatter2scatter_act_bwd(gb, w_down, up, local_offsets, _act.LAYOUT_GLU_SECOND, layer.act_code)
         dx_rows = ops.scatter2scatter(d_up, w_up, dummy, dummy, 1, x_grouped=True, y_grouped=True,
                                       expert_offsets=local_offsets)
-        # the rows travel home on a second stream while the two weight gradients run on this one
-        with _beside(layer, dev, dx_rows) as side_stream:
+        with torch.cuda.device(dev):
             _ep_call("smoe_ep_combine", dx_rows.data_ptr(), dx_rows.stride(0), cap, bufs.local["tokmeta"].data_ptr(),
                      live_tok.data_ptr(), bufs.token_capacity, src_base.data_ptr(), 0, bufs.ptrs["dxcomb"], bufs.width,
-                     T * bufs.kw, d, k, rank, W, code, PUSH_BLOCKS_BESIDE_A_GEMM, side_stream)
+                     T * bufs.kw, d, k, rank, W, code, stream)
+        # the rows travel home while the two weight gradients run
         d_w_down, _ = ops.group_bwd_W(gb, hidden, local_offsets, e_local)
         d_w_up, _ = ops.group_bwd_W(d_up, xb, local_offsets, e_local)
-        _join(layer, dev)
         bufs.barrier()
         dx = torch.empty((T, d), dtype=up.dtype, device=dev)
         with torch.cuda.device(dev):
@@ -605,9 +571,8 @@ class _PeerChunk:
 
     def __init__(self, num_experts, act_code):
         self.num_experts, self.act_code = num_experts, act_code
-        self.buffers: Optional[PeerBuffers] = None
+        self.buffers: Optional[PeerRowBuffers] = None
         self.stream = None
-        self.side_stream = None
         self.last_rows_dev = None
         self._dummy = None
 
