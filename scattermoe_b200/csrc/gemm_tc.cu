@@ -320,9 +320,8 @@ __device__ __forceinline__ void epilogue_rows(const S2SParams& p, int n0, uint32
   }
 }
 
-// Eight 16-bit values of one row as floats; zeros when the row is not valid.
-__device__ __forceinline__ void load8(const uint8_t* ptr, int is_bf16, bool ok, float (&v)[8]) {
-  const uint4 raw = ok ? __ldg(reinterpret_cast<const uint4*>(ptr)) : make_uint4(0u, 0u, 0u, 0u);
+// Eight 16-bit values (one 16-byte piece of a row) as floats.
+__device__ __forceinline__ void cvt8(const uint4& raw, int is_bf16, float (&v)[8]) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -344,15 +343,42 @@ __device__ __forceinline__ void load8(const uint8_t* ptr, int is_bf16, bool ok, 
 //   gpt-oss     g = U[2j], u = U[2j+1] (clamped in forward): dU[2j+1] = dH[j] * glu(g) inside the clamp, else 0;
 //               dU[2j] = dH[j] * (u_c + 1) * glu'(g) below the limit, else 0
 // (the arithmetic of act_backward_kernel in activation.cu, on fp32 accumulators instead of a rounded dH).
-template <int BN, int EPI>
-__device__ __forceinline__ void epilogue_act_bwd(const S2SParams& p, int n0, uint32_t taddr, uint8_t* slab, int lane,
-                                                 bool valid, uint8_t* durow, const uint8_t* urow, int c_first = 0,
-                                                 int c_step = 1) {
+// U does not depend on the MMAs: the pieces of a chunk are requested one chunk ahead, the first chunk's before
+// `wait_acc()` (the caller's wait for the accumulator), so that their HBM latency hides behind the wait, the
+// tensor-memory loads and the arithmetic of the chunk before. Returns what `wait_acc()` returned.
+template <int BN, int EPI, typename WaitFn>
+__device__ __forceinline__ bool epilogue_act_bwd(const S2SParams& p, int n0, uint32_t taddr, uint8_t* slab, int lane,
+                                                 bool valid, uint8_t* durow, const uint8_t* urow, int c_first, int c_step,
+                                                 WaitFn wait_acc) {
+  constexpr int NRAW = (EPI == EPI_BWD_PLAIN) ? 4 : 8;       // 16-byte pieces of U per 32 hidden columns
   const int F = p.N;
+  const int lin_off = p.glu_first ? F : 0, gate_off = p.glu_first ? 0 : F;
+  // byte offset inside the row of piece q of the chunk that starts at hidden column n (clamped to stay inside
+  // the row: the flush masks what lies beyond it)
+  auto piece_offset = [&](int n, int q) -> int64_t {
+    if (EPI == EPI_BWD_PLAIN) return static_cast<int64_t>(min(n + q * 8, F - 8)) * 2;
+    if (EPI == EPI_BWD_GLU) return static_cast<int64_t>((q < 4 ? lin_off : gate_off) + min(n + (q & 3) * 8, F - 8)) * 2;
+    return static_cast<int64_t>(2 * min(n + (q >> 1) * 8, F - 8) + (q & 1) * 8) * 2;
+  };
+  uint4 nxt[NRAW];
+  auto request = [&](int c) {
+    const int n = n0 + c * 32;
+    const bool live = valid && c < BN / 32 && n < F;
+#pragma unroll
+    for (int q = 0; q < NRAW; ++q)
+      nxt[q] = live ? __ldg(reinterpret_cast<const uint4*>(urow + piece_offset(n, q))) : make_uint4(0u, 0u, 0u, 0u);
+  };
+  request(c_first);
+  if (!wait_acc()) return false;
+  tc_fence_after_sync();
 #pragma unroll 1
   for (int c = c_first; c < BN / 32; c += c_step) {
     const int n = n0 + c * 32;
     if (n >= F) break;
+    uint4 cur[NRAW];
+#pragma unroll
+    for (int q = 0; q < NRAW; ++q) cur[q] = nxt[q];
+    request(c + c_step);
     uint32_t acc[32];
     tmem_ld_32x32b_x32(taddr + c * 32, acc);
     tmem_ld_wait();
@@ -360,23 +386,20 @@ __device__ __forceinline__ void epilogue_act_bwd(const S2SParams& p, int n0, uin
       uint4 pd[4];
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
-        const int nn = min(n + g * 8, F - 8);       // clamped for the loads; the flush masks the columns
         float u[8], d[8];
-        load8(urow + nn * 2, p.is_bf16, valid, u);
+        cvt8(cur[g], p.is_bf16, u);
         SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj)
           d[jj] = __uint_as_float(acc[g * 8 + jj]) * act_bwd<ACT_, true>(u[jj]);)
         pd[g] = pack8(d, p.is_bf16);
       }
       flush_rows<4>(slab, lane, pd, durow, valid, n, F);
     } else if (EPI == EPI_BWD_GLU) {
-      const int lin_off = p.glu_first ? F : 0, gate_off = p.glu_first ? 0 : F;
       uint4 pl[4], pg[4];
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
-        const int nn = min(n + g * 8, F - 8);
         float lin[8], gate[8], dl[8], dg[8];
-        load8(urow + static_cast<int64_t>(lin_off + nn) * 2, p.is_bf16, valid, lin);
-        load8(urow + static_cast<int64_t>(gate_off + nn) * 2, p.is_bf16, valid, gate);
+        cvt8(cur[g], p.is_bf16, lin);
+        cvt8(cur[4 + g], p.is_bf16, gate);
         SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj) {
           const float dh = __uint_as_float(acc[g * 8 + jj]);
           dl[jj] = dh * act_fwd<ACT_, true>(gate[jj]);
@@ -393,10 +416,9 @@ __device__ __forceinline__ void epilogue_act_bwd(const S2SParams& p, int n0, uin
         uint4 po[4];
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
-          const int nn = min(n + hh * 16 + g * 8, F - 8);
           float u0[8], u1[8], o0[8], o1[8];
-          load8(urow + static_cast<int64_t>(2 * nn) * 2, p.is_bf16, valid, u0);
-          load8(urow + static_cast<int64_t>(2 * nn + 8) * 2, p.is_bf16, valid, u1);
+          cvt8(cur[(hh * 2 + g) * 2], p.is_bf16, u0);
+          cvt8(cur[(hh * 2 + g) * 2 + 1], p.is_bf16, u1);
 #pragma unroll
           for (int jj = 0; jj < 8; ++jj) {
             const float g0 = (jj < 4) ? u0[2 * jj] : u1[2 * jj - 8];
@@ -417,6 +439,7 @@ __device__ __forceinline__ void epilogue_act_bwd(const S2SParams& p, int n0, uin
       }
     }
   }
+  return true;
 }
 
 template <int BN, bool B_KMAJOR, int EPI>
@@ -615,13 +638,16 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
       }
       uint8_t* yrow = p.Y + out_row * p.y_row_bytes;
       const uint8_t* brow = p.bias ? p.bias + static_cast<int64_t>(tl.e) * p.bias_row_elems * 2 : nullptr;
-      if (!mbar_wait_warp(tfull_bar(buf), tph, abort_flag, p.status, 5)) { ok = false; break; }
-      tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
       uint8_t* slab = epi_staging + (group * 4 + q) * (32 * C::STAGE_ROW_BYTES);
+      auto wait_acc = [&]() { return mbar_wait_warp(tfull_bar(buf), tph, abort_flag, p.status, 5); };
       if constexpr (EPI >= EPI_BWD_PLAIN) {
-        epilogue_act_bwd<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, p.U + out_row * p.u_row_bytes, group, c_step);
+        // (the first pieces of the saved up-projection are requested before the wait for the accumulator)
+        if (!epilogue_act_bwd<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, p.U + out_row * p.u_row_bytes, group,
+                                       c_step, wait_acc)) { ok = false; break; }
       } else {
+        if (!wait_acc()) { ok = false; break; }
+        tc_fence_after_sync();
         uint8_t* hrow = (EPI != EPI_NONE) ? p.H + out_row * p.h_row_bytes : nullptr;
         epilogue_rows<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, hrow, brow, group, c_step);
       }
