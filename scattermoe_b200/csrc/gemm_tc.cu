@@ -1258,9 +1258,13 @@ int launch_s2s_tc(const S2SArgs& a) {
   p.H = static_cast<uint8_t*>(a.H); p.h_row_bytes = a.shm * 2;
   p.F = F; p.glu_first = a.act_layout == LAYOUT_GLU_FIRST ? 1 : 0; p.act = a.act; p.alpha = a.alpha; p.limit = a.limit;
   p.U = static_cast<const uint8_t*>(a.U); p.u_row_bytes = a.sum * 2;
-  // raster: about sqrt(tiles in flight * tile columns / tile rows) m-tiles per group (see decode_tile)
+  // Raster (see decode_tile). While one expert's A panel (its rows x K) fits comfortably in L2, every m-tile of the
+  // expert runs beside each column tile, so each weight tile is fetched from HBM once and the A panel comes from L2.
+  // When the panel does not fit, both operands stream from HBM for every wave of tiles in flight and the wave is
+  // shaped to minimise their sum: about sqrt(tiles in flight * tile columns / tile rows) m-tiles per group.
   static const int group_m_env = env_int("SMOE_GROUP_M", 0);
-  p.group_m = group_m_env ? group_m_env : (BN == 256 ? 16 : 12);
+  const double a_panel_bytes = static_cast<double>(a.R) / a.E * a.K * 2.0;
+  p.group_m = group_m_env ? group_m_env : (a_panel_bytes <= 48e6 ? (1 << 20) : (BN == 256 ? 16 : 12));
 
   CUtensorMap map_x = map;   // placeholder when the rows are gathered: the kernel then never touches it
   p.a_by_tma = (a.x_grouped && !(a.flags & SMOE_FLAG_GATHER_ROWS) && a.sxm >= a.K &&
