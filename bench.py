@@ -54,9 +54,11 @@ METRIC = "moe_layer_fwd_bwd_tokens_per_s"
 # of one layer step). Not measured by this script: it is the figure of the last profiler capture, printed beside
 # the live numbers together with where it came from.
 NCU_TRAFFIC = {
-    "mixtral_8x7b": dict(bytes_per_launch=5.547e9,
-                         source="ncu capture of the four launches of one step at 8192 tokens, scaled to 16384 (the "
-                                "traffic grows with the rows); taken before the raster and fused-gradient changes"),
+    "mixtral_8x7b": dict(bytes_per_launch=7.176e9,
+                         source="ncu, full size (16384 tokens), the four launches of one timed step of this script "
+                                "(up-projection + activation 5.65 GB, down-projection 5.11 GB, down-projection input "
+                                "gradient + activation gradient 6.90 GB, up-projection input gradient 11.05 GB; "
+                                "algorithmic 4.97 / 2.15 / 4.97 / 4.03 GB), captured at commit 430a1b7"),
 }
 
 
