@@ -897,7 +897,7 @@ def main():
                     help="pipeline chunks of the NVLink exchange (each chunk's transfers overlap the other's GEMMs)")
     ap.add_argument("--once-per-rank", choices=("auto", "on", "off"), default="auto",
                     help="NVLink exchange: send each token once per owning rank instead of once per slot (auto: when "
-                         "that saves at least a fifth of the rows)")
+                         "that saves at least 30 % of the rows)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-triton-ref", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
