@@ -420,6 +420,57 @@ class _PeerExchangeMLP(torch.autograd.Function):
         return dx, d_gates, None, d_w_up.permute(0, 2, 1), d_w_down.permute(0, 2, 1), None
 
 
+@dataclass
+class TokenExchangeLocalPlan:
+    """What one rank derives from its own routing for the once-per-owning-rank exchange."""
+    sorted_e: torch.Tensor        # (R,) global expert of every slot, ascending (stable)
+    sorted_idx: torch.Tensor      # (R,) flat slot t*k+j of every sorted position
+    offsets: torch.Tensor         # (E,) inclusive per-expert ends of the sorted list
+    slot_pos: torch.Tensor        # (R,) sorted position of every slot (inverse of sorted_idx)
+    pair_rank: torch.Tensor       # (>= P,) owning rank of every distinct (token, owner) pair, ascending
+    pair_slot: torch.Tensor       # (>= P,) the first slot of the pair's token at that owner (token = slot // k)
+    pair_offsets: torch.Tensor    # (W,) inclusive per-owner ends of the pair list; P = pair_offsets[-1]
+    counts: torch.Tensor          # (E,) slots per expert
+    pair_counts: torch.Tensor     # (W,) pairs (= distinct tokens) per owner
+
+
+def token_exchange_local_plan(ids: torch.Tensor, num_experts: int, world: int, rowops=RowOps) -> TokenExchangeLocalPlan:
+    """Slots sorted by expert (as in the per-slot exchange) and the distinct (token, owning rank) pairs sorted by rank:
+    a slot opens a pair when no earlier slot of its token has the same owner; the other slots get id -1, which the
+    counting sort leaves out (entries of the pair list beyond `pair_offsets[-1]` are not written)."""
+    e_local = num_experts // world
+    R = ids.numel()
+    sorted_e, sorted_idx, offsets = rowops.sort(ids, num_experts)
+    slot_pos = torch.empty_like(sorted_idx)
+    slot_pos[sorted_idx] = torch.arange(R, device=ids.device, dtype=sorted_idx.dtype)
+    owner = ids // e_local
+    repeat = (owner.unsqueeze(2) == owner.unsqueeze(1)).tril(-1).any(-1)
+    pair_rank, pair_slot, pair_offsets = rowops.sort(torch.where(repeat, -1, owner), world)
+    counts = torch.diff(offsets, prepend=offsets.new_zeros(1))
+    pair_counts = torch.diff(pair_offsets, prepend=pair_offsets.new_zeros(1))
+    return TokenExchangeLocalPlan(sorted_e, sorted_idx, offsets, slot_pos, pair_rank, pair_slot, pair_offsets, counts,
+                                  pair_counts)
+
+
+def token_exchange_placement(gathered: torch.Tensor, num_experts: int, world: int, rank: int):
+    """From every rank's counts (`gathered[s] = cat(counts of s, pair_counts of s)`, shape (W, E + W)) to where this
+    rank's rows go and what it will hold:
+      dst_off (E,)        first position of this rank's slots of expert e in the owner's expert-grouped slot buffer
+                          (expert-major, then sender, as in the per-slot exchange)
+      local_offsets (E/W,) inclusive ends of this rank's own experts in its slot buffer (all senders' slots)
+      tok_base (W,)       first row of this rank's tokens in each owner's token buffer (sender-major)
+      src_base (W + 1,)   in this rank's token buffer, the first row of every sender; src_base[-1] = rows held"""
+    e_local = num_experts // world
+    counts_all, pairs_all = gathered[:, :num_experts], gathered[:, num_experts:]     # [sender, expert], [sender, owner]
+    tot = counts_all.sum(0).view(world, e_local)
+    ebase = (tot.cumsum(1) - tot).flatten()
+    dst_off = (ebase + (counts_all.cumsum(0) - counts_all)[rank]).contiguous()
+    local_offsets = tot[rank].cumsum(0).contiguous()
+    tok_base = (pairs_all.cumsum(0) - pairs_all)[rank].contiguous()
+    src_base = torch.cat([pairs_all.new_zeros(1), pairs_all[:, rank].cumsum(0)]).contiguous()
+    return dst_off, local_offsets, tok_base, src_base
+
+
 class _PeerTokenExchangeMLP(torch.autograd.Function):
     """dispatch -> local expert GLU-MLP -> return on `PeerTokenBuffers`: every token row crosses NVLink once per
     owning rank each way (csrc/ep_dedup.cu). Same results as `_PeerExchangeMLP`; the gate weighting and the gate
@@ -440,27 +491,15 @@ class _PeerTokenExchangeMLP(torch.autograd.Function):
         gates = gates.to(x.dtype).contiguous()
         ids = expert_idxs.to(torch.int64).contiguous()
 
-        # 1. plan. Slots sorted by expert (as in the per-slot exchange) and the distinct (token, owning rank) pairs
-        #    sorted by rank: a slot opens a pair when no earlier slot of its token has the same owner.
-        sorted_e, sorted_idx, offsets = flatten_sort_count(ids, E)
-        slot_pos = torch.empty_like(sorted_idx)
-        slot_pos[sorted_idx] = torch.arange(R, device=dev, dtype=sorted_idx.dtype)
-        owner = ids // e_local
-        repeat = (owner.unsqueeze(2) == owner.unsqueeze(1)).tril(-1).any(-1)
-        pair_rank, pair_slot, pair_offsets = flatten_sort_count(torch.where(repeat, -1, owner), W)
-        counts = torch.diff(offsets, prepend=offsets.new_zeros(1))
-        pair_counts = torch.diff(pair_offsets, prepend=pair_offsets.new_zeros(1))
-        gathered = torch.empty((W, E + W), dtype=counts.dtype, device=dev)
-        dist.all_gather_into_tensor(gathered, torch.cat([counts, pair_counts]), group=bufs.group)
-        counts_all, pairs_all = gathered[:, :E], gathered[:, E:]          # [sender, expert], [sender, owner]
-        tot = counts_all.sum(0).view(W, e_local)
-        ebase = (tot.cumsum(1) - tot).flatten()
-        dst_off = (ebase + (counts_all.cumsum(0) - counts_all)[rank]).contiguous()
-        local_offsets = tot[rank].cumsum(0).contiguous()
-        live_slots = local_offsets[-1:]
-        tok_base = (pairs_all.cumsum(0) - pairs_all)[rank].contiguous()   # my first row in each owner's token buffer
-        src_base = torch.cat([pairs_all.new_zeros(1), pairs_all[:, rank].cumsum(0)]).contiguous()   # here, per sender
-        live_tok = src_base[-1:]
+        # 1. plan (device-side integers only; one small all-gather of the counts)
+        local = token_exchange_local_plan(ids, E, W)
+        gathered = torch.empty((W, E + W), dtype=local.counts.dtype, device=dev)
+        dist.all_gather_into_tensor(gathered, torch.cat([local.counts, local.pair_counts]), group=bufs.group)
+        placed = token_exchange_placement(gathered, E, W, rank)
+        sorted_e, sorted_idx, offsets, slot_pos = local.sorted_e, local.sorted_idx, local.offsets, local.slot_pos
+        pair_rank, pair_slot, pair_offsets = local.pair_rank, local.pair_slot, local.pair_offsets
+        dst_off, local_offsets, tok_base, src_base = placed
+        live_slots, live_tok = local_offsets[-1:], src_base[-1:]
         tok_row = torch.empty((T, W), dtype=torch.int32, device=dev)
         tok_parts = torch.zeros((T,), dtype=torch.int32, device=dev)
         # 2. dispatch: one record per (token, owner) pair, the token rows (once per owner), one record per slot

@@ -130,3 +130,140 @@ def test_plan_on_a_single_process_is_the_plain_routing_sort():
     assert torch.equal(plan.recv_expert_ids, torch.sort(idx.flatten()).values)
     rows = ep.dispatch(x, plan, rowops=TorchRowOps)
     assert torch.equal(rows, x[plan.sorted_scattered_idxs // idx.size(1)])
+
+
+# ---- the once-per-owning-rank exchange: its plan and placement arithmetic, with the peer stores played on the host ----
+
+class SkippingSort:
+    """`RowOps.sort` stand-in that, like the CUDA counting sort, leaves out ids outside [0, E): their entries of the
+    two sorted outputs are never written (filled with a poison value here)."""
+
+    @staticmethod
+    def sort(ids, E):
+        flat = ids.reshape(-1).to(torch.int64)
+        valid = (flat >= 0) & (flat < E)
+        order = torch.sort(torch.where(valid, flat, torch.full_like(flat, E)), stable=True).indices
+        n = int(valid.sum())
+        sorted_e = torch.full_like(flat, -7)
+        sorted_idx = torch.full_like(flat, -7)
+        sorted_e[:n], sorted_idx[:n] = flat[order[:n]], order[:n]
+        return sorted_e, sorted_idx, torch.bincount(flat[valid], minlength=E).cumsum(-1)
+
+
+def _token_exchange_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import scattermoe_oracle as oracle
+        from scattermoe_b200 import expert_parallel as ep
+        x, p, idx, w1, w2, dy = _problem(seed=11, T=64, E=8, k=4)
+        T, E, k, d = x.size(0), w1.size(0), idx.size(1), x.size(1)
+        tl, el = T // world, E // world
+        sl = slice(rank * tl, (rank + 1) * tl)
+        ids, gates, xl = idx[sl], p[sl], x[sl]
+        kw = min(k, world)
+
+        local = ep.token_exchange_local_plan(ids, E, world, rowops=SkippingSort)
+        mine = torch.cat([local.counts, local.pair_counts])
+        everyone = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        gathered = torch.stack(everyone)
+        dst_off, local_offsets, tok_base, src_base = ep.token_exchange_placement(gathered, E, world, rank)
+        pairs = int(local.pair_offsets[-1])
+        # every (token, owner) pair exactly once, owners ascending, tokens ascending inside an owner
+        owner_of = ids // el
+        want_pairs = sorted({(int(owner_of[t, j]), t) for t in range(tl) for j in range(k)})
+        got_pairs = [(int(local.pair_rank[i]), int(local.pair_slot[i]) // k) for i in range(pairs)]
+        assert got_pairs == want_pairs
+
+        # what the kernels do, on the host: peer stores become lists of (destination, buffer, row, payload)
+        writes = []
+        tok_row = {}
+        for i in range(pairs):
+            w, t = got_pairs[i]
+            start = int(local.pair_offsets[w - 1]) if w else 0
+            row = int(tok_base[w]) + (i - start)
+            tok_row[(t, w)] = row
+            owners = sorted({int(o) for o in owner_of[t]})
+            slots = [j for j in range(k) if int(owner_of[t, j]) == w]
+            pos = []
+            for j in slots:
+                e = int(ids[t, j])
+                seg = int(local.offsets[e - 1]) if e else 0
+                pos.append(int(dst_off[e]) + int(local.slot_pos[t * k + j]) - seg)
+            writes.append((w, "xtok", row, xl[t]))
+            writes.append((w, "tokmeta", row, (rank, t * kw + owners.index(w), pos, [gates[t, j] for j in slots])))
+        for m in range(tl * k):
+            e, slot = int(local.sorted_e[m]), int(local.sorted_idx[m])
+            w, t = e // el, slot // k
+            seg = int(local.offsets[e - 1]) if e else 0
+            writes.append((w, "meta", int(dst_off[e]) + m - seg, tok_row[(t, w)]))
+        inbox = [None] * world
+        dist.all_gather_object(inbox, writes)
+        bufs = {"xtok": {}, "tokmeta": {}, "meta": {}}
+        for sender in inbox:
+            for dest, name, row, payload in sender:
+                if dest == rank:
+                    assert row not in bufs[name], "two stores to row %d of %s" % (row, name)
+                    bufs[name][row] = payload
+        live_slots, live_tok = int(local_offsets[-1]), int(src_base[-1])
+        assert sorted(bufs["meta"]) == list(range(live_slots)) and sorted(bufs["xtok"]) == list(range(live_tok))
+        assert sorted(bufs["tokmeta"]) == list(range(live_tok))
+        # owner: expand, expert MLP per local expert, gate-weighted sum per received token row, one row back
+        xb = torch.stack([bufs["xtok"][bufs["meta"][q]] for q in range(live_slots)]) if live_slots else x.new_zeros((0, d))
+        y_rows = torch.zeros_like(xb)
+        start = 0
+        for e_l, end in enumerate(local_offsets.tolist()):
+            e = rank * el + e_l
+            if end > start:
+                y_rows[start:end] = oracle.act_glu_second_half(xb[start:end] @ w1[e]) @ w2[e]
+            start = end
+        back = []
+        for u in range(live_tok):
+            src, ret_row, pos, gs = bufs["tokmeta"][u]
+            back.append((src, ret_row, sum(g * y_rows[q] for q, g in zip(pos, gs))))
+        inbox = [None] * world
+        dist.all_gather_object(inbox, back)
+        parts = {}
+        for sender in inbox:
+            for dest, ret_row, row in sender:
+                if dest == rank:
+                    assert ret_row not in parts
+                    parts[ret_row] = row
+        y = torch.stack([sum(parts[t * kw + c] for c in range(len({int(o) for o in owner_of[t]}))) for t in range(tl)])
+        want = oracle.dense_moe_mlp(x, p, idx, w1, w2, None, None, oracle.act_glu_second_half, torch.float64)
+        err = (y - want[sl]).abs().max().item()
+        assert err < 1e-9, "y rank %d: %g" % (rank, err)
+        assert len(parts) == sum(len({int(o) for o in owner_of[t]}) for t in range(tl))
+        ret[rank] = "ok"
+    except Exception:
+        import traceback
+        ret[rank] = "FAILED: " + traceback.format_exc()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_once_per_owning_rank_exchange_plan_on_gloo_ranks(world):
+    """Plan and placement arithmetic of the once-per-owning-rank exchange (token_exchange_local_plan /
+    token_exchange_placement): with the peer stores of the CUDA kernels replayed on the host, every buffer row is
+    written exactly once, the buffers are dense, and the forward result equals the oracle's dense loop."""
+    import socket
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        procs = [ctx.Process(target=_token_exchange_worker, args=(r, world, port, ret)) for r in range(world)]
+        for q in procs:
+            q.start()
+        for q in procs:
+            q.join(timeout=180)
+        for q in procs:
+            if q.is_alive():
+                q.terminate()
+                raise AssertionError("a rank did not finish")
+        assert {r: ret.get(r) for r in range(world)} == {r: "ok" for r in range(world)}
