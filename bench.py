@@ -436,7 +436,10 @@ class TritonReference:
 
     def time(self, iters=5, warmup=3):
         out = {}
-        for key, fn in (("ms_per_step", self.step), ("forward_ms", self.forward)):
+        def inference():
+            with torch.no_grad():
+                return self.fwd(self.x, self.p)
+        for key, fn in (("ms_per_step", self.step), ("forward_ms", self.forward), ("inference_ms", inference)):
             for _ in range(warmup):
                 fn()
             torch.cuda.synchronize()
@@ -450,7 +453,8 @@ class TritonReference:
         T = self.x.size(0)
         return {"impl": "reference Triton kernels (unmodified, baseline/_ref), same GPU, same weights and inputs",
                 "ms_per_step": out["ms_per_step"], "value": T / (out["ms_per_step"] / 1e3), "unit": "tokens/s",
-                "forward_ms": out["forward_ms"], "forward_value": T / (out["forward_ms"] / 1e3), "iters": iters}
+                "forward_ms": out["forward_ms"], "forward_value": T / (out["forward_ms"] / 1e3),
+                "inference_ms": out["inference_ms"], "iters": iters}
 
 
 # ---- parity, outside the timed regions ------------------------------------------------------------------------
@@ -820,6 +824,13 @@ def measure(name, c, device, rank, world, dist, steps, warmup, with_e2e=True, sa
         forward_step()
     ms_fwd = timed(loop(forward_step), steps)
 
+    def inference_step():
+        with torch.no_grad():
+            return forward_only(c, layer, dev_in["x"], dev_in["p"], dev_in["idx"])
+    for _ in range(2):
+        inference_step()
+    ms_inf = timed(loop(inference_step), steps)
+
     ms_e2e = None
     if with_e2e:
         e2e_loop(2)
@@ -852,7 +863,10 @@ def measure(name, c, device, rank, world, dist, steps, warmup, with_e2e=True, sa
         "roofline": roofline,
         "forward": {"value": tokens_all / (ms_fwd / steps / 1e3), "unit": "tokens/s", "ms_per_step": ms_fwd / steps,
                     "frac_of_bf16_peak": fwd_flops / world / (ms_fwd / steps / 1e3) / 1e12 / peak,
-                    "what": "the training forward alone (autograd on, tensors for backward saved)"},
+                    "what": "the training forward alone (autograd on, tensors for backward saved)",
+                    "inference_ms_per_step": ms_inf / steps,
+                    "inference_value": tokens_all / (ms_inf / steps / 1e3),
+                    "inference_what": "the same forward under torch.no_grad (nothing kept for backward)"},
         # kernels of this library launched by this rank inside the timed region (counted at the C-ABI boundary)
         "gpu_launches": launches,
         # device time between the events bracketing each C-ABI call, summed over the timed region, per step

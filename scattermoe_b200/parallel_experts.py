@@ -249,9 +249,12 @@ class ExpertMLP(torch.autograd.Function):
         x_src, kk, grouped = x, k, False
         if GROUP_INPUT_COPY and x.size(1) % 8 == 0 and x.dtype in (torch.bfloat16, torch.float16):
             x_src, kk, grouped = kernels.ops.group(x, sorted_scattered_idxs, fan_out=k), 1, True
+        # the up-projection itself is only kept for backward: without a gradient to compute (inference, torch.no_grad)
+        # the fused kernel writes the hidden rows alone
+        training = any(ctx.needs_input_grad[:6])
         res = kernels.ops.scatter2scatter_act(x_src, w_up, sorted_expert_idxs, sorted_scattered_idxs, kk, act_layout,
                                               act, b=b_up, x_grouped=grouped, expert_offsets=expert_offsets,
-                                              alpha=alpha, limit=limit)
+                                              alpha=alpha, limit=limit, need_up=training)
         if res is None:     # not a tensor-core case: the two separate kernels
             up = kernels.ops.scatter2scatter(x_src, w_up, sorted_expert_idxs, sorted_scattered_idxs, kk, b=b_up,
                                              x_grouped=grouped, y_grouped=True, expert_offsets=expert_offsets)

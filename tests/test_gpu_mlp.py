@@ -488,3 +488,20 @@ def test_consolidated_module_list_block(names_kind, renorm):
     sd = fused.state_dict()
     assert sorted(sd) == sorted(want_sd) and all(torch.equal(sd[n], want_sd[n]) for n in sd)
     sm.check_device_status()
+
+
+def test_forward_without_gradients_equals_the_training_forward():
+    """Under torch.no_grad the fused up-projection kernel does not write the up-projection (nothing needs it); the
+    layer's output must be the same bits."""
+    import scattermoe_b200 as sm
+    torch.manual_seed(2)
+    T, d, F, E, k = 1000, 256, 320, 8, 2
+    m = sm.mlp.GLUMLP(d, F, E, k).cuda().bfloat16()
+    x = torch.randn(T, d, device="cuda", dtype=torch.bfloat16)
+    p, idx = torch.topk(torch.softmax(torch.randn(T, E, device="cuda"), -1), k)
+    p = p.bfloat16()
+    y_train = m(x.clone().requires_grad_(), p.clone().requires_grad_(), idx)
+    with torch.no_grad():
+        y_inf = m(x, p, idx)
+    assert not y_inf.requires_grad and torch.equal(y_inf, y_train.detach())
+    sm.check_device_status()
