@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define SMOE_ABI_VERSION 2
+#define SMOE_ABI_VERSION 3
 
 enum smoe_status {
   SMOE_OK = 0,
@@ -180,7 +180,10 @@ int smoe_activation_backward(const void* U, int64_t stride_um, const void* DH, i
  * epilogue also writes H = activation(Y) (layouts / functions as above; Y nullable when the up-projection itself
  * is not needed, e.g. inference). Fuses scattermoe/mlp.py:35-41 / :76-87 (the first expert linear and the
  * activation after it). Tensor-core kernel only: returns SMOE_ERR_UNSUPPORTED when the request does not fit it
- * (dtype, alignment, N <= 128), and the caller runs the two separate calls instead. */
+ * (dtype, alignment, N <= 128), and the caller runs the two separate calls instead.
+ * `row_gates` (nullable; the (T, k) gates, flat, in the dtype of X): H receives activation(Y) * gates[slot of the row]
+ * instead. The down-projection is linear, so a layer whose hidden rows carry the gate needs no gate weighting after
+ * it (scattermoe/parallel_experts.py:44-46 becomes a plain sum over the k slots); Y stays un-weighted. */
 int smoe_scatter2scatter_act(const void* X, int64_t x_rows, int64_t stride_xm, int64_t stride_xk,
                              const void* W, int64_t stride_we, int64_t stride_wk, int64_t stride_wn,
                              const void* bias, int64_t stride_be, int64_t stride_bn,
@@ -188,7 +191,8 @@ int smoe_scatter2scatter_act(const void* X, int64_t x_rows, int64_t stride_xm, i
                              const int64_t* sorted_expert_idxs, const int64_t* sorted_scattered_idxs,
                              const int64_t* expert_offsets, int64_t R, int32_t K, int32_t N, int32_t E,
                              int32_t fan_out, int32_t x_grouped, int32_t dtype, int32_t flags, int32_t act_layout,
-                             int32_t act, float alpha, float limit, int32_t* status, void* stream);
+                             int32_t act, float alpha, float limit, const void* row_gates, int32_t* status,
+                             void* stream);
 
 /* Input gradient of the down-projection + activation gradient in one kernel. Fuses the backward of
  * scattermoe/mlp.py:41 / :81-87 (PyTorch autograd of the activation in the reference) into the grouped GEMM that the
@@ -197,13 +201,23 @@ int smoe_scatter2scatter_act(const void* X, int64_t x_rows, int64_t stride_xm, i
  * DY (R, K) and U, DU (R, n_up) are in expert order, W is (E, K, F) in element strides (the transposed view of the
  * down-projection weight), layouts / functions as for smoe_activation_backward, n_up = F (plain) or 2F.
  * Tensor-core kernel only: returns SMOE_ERR_UNSUPPORTED when the request does not fit it (dtype, alignment,
- * F <= 128); the caller then runs smoe_scatter2scatter and smoe_activation_backward. */
+ * F <= 128); the caller then runs smoe_scatter2scatter and smoe_activation_backward.
+ * With `row_gates` (nullable, as in smoe_scatter2scatter_act; then `sorted_scattered_idxs` and `gate_partials` are
+ * required too) DY is the UN-weighted output gradient in expert order: the epilogue scales dH by the row's gate and
+ * also writes, for the gate gradient of scattermoe/parallel_experts.py:79 (<expert output, output gradient> =
+ * <hidden, dH>), the partial dot products of dH with the un-weighted hidden row over its chunks of columns:
+ * gate_partials is (smoe_act_bwd_partial_lines(F), R) fp32, every entry written; smoe_gate_grad_from_partials adds
+ * the lines up into d_gates[slot of row m] (T*k values in `dtype`). Deterministic: no atomics. */
 int smoe_scatter2scatter_act_bwd(const void* DY, int64_t stride_dym, int64_t stride_dyk,
                                  const void* W, int64_t stride_we, int64_t stride_wk, int64_t stride_wn,
                                  const void* U, int64_t stride_um, void* DU, int64_t stride_dum,
                                  const int64_t* expert_offsets, int64_t R, int32_t K, int32_t F, int32_t E,
                                  int32_t dtype, int32_t flags, int32_t act_layout, int32_t act, float alpha,
-                                 float limit, int32_t* status, void* stream);
+                                 float limit, const void* row_gates, const int64_t* sorted_scattered_idxs,
+                                 float* gate_partials, int32_t* status, void* stream);
+int32_t smoe_act_bwd_partial_lines(int32_t F);
+int smoe_gate_grad_from_partials(const float* partials, int32_t lines, int64_t R, const int64_t* sorted_scattered_idxs,
+                                 void* d_gates, int32_t dtype, void* stream);
 
 /* ---- single-token decode ---------------------------------------------------------------------------------
  * Replaces kernels.single.single2scatter (scattermoe/kernels/single.py:41-59, kernel :5-39): the k expert

@@ -17,7 +17,7 @@ from . import build as _build
 _lock = threading.Lock()
 _lib = None
 
-ABI_VERSION = 2          # SMOE_ABI_VERSION of include/scattermoe_b200.h this binding was written against
+ABI_VERSION = 3          # SMOE_ABI_VERSION of include/scattermoe_b200.h this binding was written against
 
 SMOE_OK = 0
 SMOE_ERR_BAD_ARG = 1
@@ -67,9 +67,11 @@ SIGNATURES = {
                                  c_int32),
     "smoe_scatter2scatter_act": ([_P, _I64, _I64, _I64, _P, _I64, _I64, _I64, _P, _I64, _I64, _P, _I64, _I64, _P, _I64,
                                   _P, _P, _P, _I64, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, c_float, c_float,
-                                  _P, _P], c_int32),
+                                  _P, _P, _P], c_int32),
     "smoe_scatter2scatter_act_bwd": ([_P, _I64, _I64, _P, _I64, _I64, _I64, _P, _I64, _P, _I64, _P, _I64, _I32, _I32, _I32,
-                                      _I32, _I32, _I32, _I32, c_float, c_float, _P, _P], c_int32),
+                                      _I32, _I32, _I32, _I32, c_float, c_float, _P, _P, _P, _P, _P], c_int32),
+    "smoe_act_bwd_partial_lines": ([_I32], c_int32),
+    "smoe_gate_grad_from_partials": ([_P, _I32, _I64, _P, _P, _I32, _P], c_int32),
     "smoe_single2scatter": ([_P, _I64, _I64, _I64, _P, _I64, _I64, _I64, _P, _I64, _I64, _P, _I32, _I32, _I32, _I32, _I32, _P],
                             c_int32),
     "smoe_ep_dispatch": ([_P, _I64, _I64, _P, _P, _P, _P, _P, _I32, _P, _I64, _I64, _P, _I32, _I64, _I32, _I32, _I32, _I32,

@@ -138,8 +138,8 @@ extern "C" int smoe_scatter2scatter_act(const void* X, int64_t x_rows, int64_t s
                                         const int64_t* sorted_expert_idxs, const int64_t* sorted_scattered_idxs,
                                         const int64_t* expert_offsets, int64_t R, int32_t K, int32_t N, int32_t E,
                                         int32_t fan_out, int32_t x_grouped, int32_t dtype, int32_t flags,
-                                        int32_t act_layout, int32_t act, float alpha, float limit, int32_t* status,
-                                        void* stream) {
+                                        int32_t act_layout, int32_t act, float alpha, float limit,
+                                        const void* row_gates, int32_t* status, void* stream) {
   if (int rc = check_dtype("scatter2scatter_act", dtype)) return rc;
   SMOE_CHECK_ARG(R >= 0 && R < (int64_t(1) << 31), "scatter2scatter_act: R=%lld out of range", (long long)R);
   SMOE_CHECK_ARG(K >= 0 && N >= 0 && E >= 1 && fan_out >= 1, "scatter2scatter_act: bad sizes K=%d N=%d E=%d fan_out=%d",
@@ -157,6 +157,7 @@ extern "C" int smoe_scatter2scatter_act(const void* X, int64_t x_rows, int64_t s
             Y, stride_ym, stride_yn, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets,
             R, K, N, E, fan_out, x_grouped ? 1 : 0, 1, dtype, flags, status, static_cast<cudaStream_t>(stream)};
   a.H = H; a.shm = stride_hm; a.act_layout = act_layout; a.act = act; a.alpha = alpha; a.limit = limit;
+  a.row_gate = row_gates;
   if (Y == nullptr) { a.sym = 8; a.syn = 1; }
   const int rc = launch_s2s_tc(a);
   if (rc == SMOE_OK) set_last_path(1);
@@ -172,7 +173,8 @@ extern "C" int smoe_scatter2scatter_act_bwd(const void* DY, int64_t stride_dym, 
                                             int64_t stride_um, void* DU, int64_t stride_dum,
                                             const int64_t* expert_offsets, int64_t R, int32_t K, int32_t F, int32_t E,
                                             int32_t dtype, int32_t flags, int32_t act_layout, int32_t act, float alpha,
-                                            float limit, int32_t* status, void* stream) {
+                                            float limit, const void* row_gates, const int64_t* sorted_scattered_idxs,
+                                            float* gate_partials, int32_t* status, void* stream) {
   if (int rc = check_dtype("scatter2scatter_act_bwd", dtype)) return rc;
   SMOE_CHECK_ARG(R >= 0 && R < (int64_t(1) << 31), "scatter2scatter_act_bwd: R=%lld out of range", (long long)R);
   SMOE_CHECK_ARG(K >= 0 && F >= 0 && E >= 1, "scatter2scatter_act_bwd: bad sizes K=%d F=%d E=%d", K, F, E);
@@ -180,13 +182,21 @@ extern "C" int smoe_scatter2scatter_act_bwd(const void* DY, int64_t stride_dym, 
                  "scatter2scatter_act_bwd: layout %d / function %d", act_layout, act);
   if (R == 0 || F == 0) return SMOE_OK;
   SMOE_CHECK_ARG(DY && W && U && DU && expert_offsets, "scatter2scatter_act_bwd: null pointer");
+  SMOE_CHECK_ARG((row_gates == nullptr && gate_partials == nullptr) || (row_gates && gate_partials && sorted_scattered_idxs),
+                 "scatter2scatter_act_bwd: row_gates, sorted_scattered_idxs and gate_partials go together");
   if (flags & SMOE_FLAG_FORCE_SIMT) return SMOE_ERR_UNSUPPORTED;
-  // rows are in expert order on both sides: the index tensors are never read (the offsets stand in for them)
+  // rows are in expert order on both sides: without gates the index tensors are never read (the offsets stand in)
+  const int64_t* slots = sorted_scattered_idxs ? sorted_scattered_idxs : expert_offsets;
   S2SArgs a{DY, R, stride_dym, stride_dyk, W, stride_we, stride_wk, stride_wn, nullptr, 0, 0,
-            DU, stride_dum, 1, expert_offsets, expert_offsets, expert_offsets,
+            DU, stride_dum, 1, expert_offsets, slots, expert_offsets,
             R, K, F, E, 1, 1, 1, dtype, flags, status, static_cast<cudaStream_t>(stream)};
   a.U = U; a.sum = stride_um; a.act_layout = act_layout; a.act = act; a.alpha = alpha; a.limit = limit; a.act_bwd = 1;
+  a.row_gate = row_gates; a.dot_out = gate_partials;
   const int rc = launch_s2s_tc(a);
   if (rc == SMOE_OK) set_last_path(1);
   return rc;
 }
+
+// Lines of fp32 partial sums (each R long) that smoe_scatter2scatter_act_bwd writes per row when it is given gates:
+// two per 256-wide tile of hidden columns (one per group of epilogue warps).
+extern "C" int32_t smoe_act_bwd_partial_lines(int32_t F) { return F > 0 ? 2 * ((F + 255) / 256) : 0; }

@@ -68,6 +68,13 @@ struct S2SParams {
   // fused activation-gradient epilogue (EPI_BWD_*): U (rows, n_up) is the up-projection saved by forward; the GEMM's
   // result is the hidden gradient (N = F columns, never stored) and Y receives the (rows, n_up) gradient of U
   const uint8_t* U; int64_t u_row_bytes;
+  // per-row gate (nullable; 16-bit, indexed by the row's slot = sorted_idx[m]). Forward activation epilogues write
+  // hidden * gate (the gate weighting of the layer's output moves in front of the down-projection, which is linear);
+  // gradient epilogues take the UN-weighted output gradient as A, scale the hidden gradient by the gate and emit the
+  // gate gradient's partial dot products <dH_unweighted, hidden_unweighted> over their chunks of hidden columns:
+  // dot_out[(column tile * 2 + epilogue group) * dot_stride + m], fp32.
+  const uint8_t* row_gate;
+  float* dot_out; int64_t dot_stride;
   int group_m;         // m-tiles per raster group (see decode_tile)
   uint32_t idesc;
   int32_t* status;
@@ -224,7 +231,7 @@ __device__ __forceinline__ void flush_rows(uint8_t* slab, int lane, const uint4 
 template <int BN, int EPI>
 __device__ __forceinline__ void epilogue_rows(const S2SParams& p, int n0, uint32_t taddr, uint8_t* slab, int lane,
                                               bool valid, uint8_t* yrow, uint8_t* hrow, const uint8_t* brow,
-                                              int c_first = 0, int c_step = 1) {
+                                              int c_first = 0, int c_step = 1, float hscale = 1.0f) {
   constexpr int TN = (EPI == EPI_GLU_HALVES) ? BN / 2 : BN;
   const bool write_y = (EPI == EPI_NONE) || p.Y != nullptr;
   // 32-column chunks c_first, c_first + c_step, ...: with two groups of epilogue warps each takes every other chunk
@@ -250,7 +257,7 @@ __device__ __forceinline__ void epilogue_rows(const S2SParams& p, int n0, uint32
         add_bias8(brow, nn, p.is_bf16, p.bias_vec, a);
         add_bias8(brow, p.F + nn, p.is_bf16, p.bias_vec, b);
         SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj)
-          h[jj] = p.glu_first ? act_fwd<ACT_, true>(a[jj]) * b[jj] : act_fwd<ACT_, true>(b[jj]) * a[jj];)
+          h[jj] = hscale * (p.glu_first ? act_fwd<ACT_, true>(a[jj]) * b[jj] : act_fwd<ACT_, true>(b[jj]) * a[jj]);)
         pa[g] = pack8(a, p.is_bf16);
         pb[g] = pack8(b, p.is_bf16);
         ph[g] = pack8(h, p.is_bf16);
@@ -289,7 +296,7 @@ __device__ __forceinline__ void epilogue_rows(const S2SParams& p, int n0, uint32
             const float u0 = (jj < 4) ? v0[2 * jj + 1] : v1[2 * jj - 7];
             const float gc = fminf(g0, p.limit);
             const float uc = fminf(fmaxf(u0, -p.limit), p.limit);
-            h[jj] = (uc + 1.0f) * (gc * sigmoidf_<true>(p.alpha * gc));
+            h[jj] = hscale * (uc + 1.0f) * (gc * sigmoidf_<true>(p.alpha * gc));
           }
           py[2 * gg] = pack8(v0, p.is_bf16);
           py[2 * gg + 1] = pack8(v1, p.is_bf16);
@@ -309,7 +316,7 @@ __device__ __forceinline__ void epilogue_rows(const S2SParams& p, int n0, uint32
           py[g] = pack8(v, p.is_bf16);
           if (EPI == EPI_ACT) {
             float h[8];
-            SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj) h[jj] = act_fwd<ACT_, true>(v[jj]);)
+            SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj) h[jj] = hscale * act_fwd<ACT_, true>(v[jj]);)
             ph[g] = pack8(h, p.is_bf16);
           }
         }
@@ -349,7 +356,7 @@ __device__ __forceinline__ void cvt8(const uint4& raw, int is_bf16, float (&v)[8
 template <int BN, int EPI, typename WaitFn>
 __device__ __forceinline__ bool epilogue_act_bwd(const S2SParams& p, int n0, uint32_t taddr, uint8_t* slab, int lane,
                                                  bool valid, uint8_t* durow, const uint8_t* urow, int c_first, int c_step,
-                                                 WaitFn wait_acc) {
+                                                 WaitFn wait_acc, float rg, float& dot) {
   constexpr int NRAW = (EPI == EPI_BWD_PLAIN) ? 4 : 8;       // 16-byte pieces of U per 32 hidden columns
   const int F = p.N;
   const int lin_off = p.glu_first ? F : 0, gate_off = p.glu_first ? 0 : F;
@@ -388,8 +395,11 @@ __device__ __forceinline__ bool epilogue_act_bwd(const S2SParams& p, int n0, uin
       for (int g = 0; g < 4; ++g) {
         float u[8], d[8];
         cvt8(cur[g], p.is_bf16, u);
-        SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj)
-          d[jj] = __uint_as_float(acc[g * 8 + jj]) * act_bwd<ACT_, true>(u[jj]);)
+        SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj) {
+          const float a0 = __uint_as_float(acc[g * 8 + jj]);
+          if (p.dot_out) dot = fmaf(a0, act_fwd<ACT_, true>(u[jj]), dot);
+          d[jj] = rg * a0 * act_bwd<ACT_, true>(u[jj]);
+        })
         pd[g] = pack8(d, p.is_bf16);
       }
       flush_rows<4>(slab, lane, pd, durow, valid, n, F);
@@ -401,8 +411,11 @@ __device__ __forceinline__ bool epilogue_act_bwd(const S2SParams& p, int n0, uin
         cvt8(cur[g], p.is_bf16, lin);
         cvt8(cur[4 + g], p.is_bf16, gate);
         SMOE_ACT_SWITCH(p.act, _Pragma("unroll") for (int jj = 0; jj < 8; ++jj) {
-          const float dh = __uint_as_float(acc[g * 8 + jj]);
-          dl[jj] = dh * act_fwd<ACT_, true>(gate[jj]);
+          const float a0 = __uint_as_float(acc[g * 8 + jj]);
+          const float af = act_fwd<ACT_, true>(gate[jj]);
+          dot = fmaf(a0, lin[jj] * af, dot);
+          const float dh = rg * a0;
+          dl[jj] = dh * af;
           dg[jj] = dh * lin[jj] * act_bwd<ACT_, true>(gate[jj]);
         })
         pl[g] = pack8(dl, p.is_bf16);
@@ -423,10 +436,12 @@ __device__ __forceinline__ bool epilogue_act_bwd(const S2SParams& p, int n0, uin
           for (int jj = 0; jj < 8; ++jj) {
             const float g0 = (jj < 4) ? u0[2 * jj] : u1[2 * jj - 8];
             const float up0 = (jj < 4) ? u0[2 * jj + 1] : u1[2 * jj - 7];
-            const float dh = __uint_as_float(acc[hh * 16 + g * 8 + jj]);
+            const float a0 = __uint_as_float(acc[hh * 16 + g * 8 + jj]);
+            const float dh = rg * a0;
             const float gc = fminf(g0, p.limit);
             const float uc = fminf(fmaxf(up0, -p.limit), p.limit);
             const float sg = sigmoidf_<true>(p.alpha * gc);
+            dot = fmaf(a0, (uc + 1.0f) * (gc * sg), dot);
             const float d_u = (up0 >= -p.limit && up0 <= p.limit) ? dh * (gc * sg) : 0.f;
             const float d_g = (g0 <= p.limit) ? dh * (uc + 1.0f) * (sg + gc * p.alpha * sg * (1.0f - sg)) : 0.f;
             if (jj < 4) { o0[2 * jj] = d_g; o0[2 * jj + 1] = d_u; }
@@ -641,15 +656,29 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
       uint8_t* slab = epi_staging + (group * 4 + q) * (32 * C::STAGE_ROW_BYTES);
       auto wait_acc = [&]() { return mbar_wait_warp(tfull_bar(buf), tph, abort_flag, p.status, 5); };
+      float rg = 1.0f;                     // the row's gate, where the launch carries gates
+      if (EPI != EPI_NONE && p.row_gate != nullptr && valid) {
+        const int64_t slot = p.sorted_idx[tl.m0 + r];
+        if (slot >= 0 && slot < p.R) {
+          const uint16_t raw = __ldg(reinterpret_cast<const uint16_t*>(p.row_gate) + slot);
+          rg = p.is_bf16 ? __bfloat162float(__ushort_as_bfloat16(raw)) : __half2float(__ushort_as_half(raw));
+        }
+      }
       if constexpr (EPI >= EPI_BWD_PLAIN) {
         // (the first pieces of the saved up-projection are requested before the wait for the accumulator)
+        float dot = 0.f;
         if (!epilogue_act_bwd<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, p.U + out_row * p.u_row_bytes, group,
-                                       c_step, wait_acc)) { ok = false; break; }
+                                       c_step, wait_acc, rg, dot)) { ok = false; break; }
+        if (p.dot_out != nullptr && valid) {
+          float* line = p.dot_out + static_cast<int64_t>((tl.n0 / BN) * 2 + group) * p.dot_stride + (tl.m0 + r);
+          *line = dot;
+          if (c_step == 1) line[p.dot_stride] = 0.f;       // one epilogue group only: the other group's line is empty
+        }
       } else {
         if (!wait_acc()) { ok = false; break; }
         tc_fence_after_sync();
         uint8_t* hrow = (EPI != EPI_NONE) ? p.H + out_row * p.h_row_bytes : nullptr;
-        epilogue_rows<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, hrow, brow, group, c_step);
+        epilogue_rows<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, hrow, brow, group, c_step, rg);
       }
       tc_fence_before_sync();
       mbar_arrive(tempty_bar(buf));
@@ -1258,6 +1287,8 @@ int launch_s2s_tc(const S2SArgs& a) {
   p.H = static_cast<uint8_t*>(a.H); p.h_row_bytes = a.shm * 2;
   p.F = F; p.glu_first = a.act_layout == LAYOUT_GLU_FIRST ? 1 : 0; p.act = a.act; p.alpha = a.alpha; p.limit = a.limit;
   p.U = static_cast<const uint8_t*>(a.U); p.u_row_bytes = a.sum * 2;
+  p.row_gate = static_cast<const uint8_t*>(a.row_gate);
+  p.dot_out = a.dot_out; p.dot_stride = a.R;
   // Raster (see decode_tile). While one expert's A panel (its rows x K) fits comfortably in L2, every m-tile of the
   // expert runs beside each column tile, so each weight tile is fetched from HBM once and the A panel comes from L2.
   // When the panel does not fit, both operands stream from HBM for every wave of tiles in flight and the wave is

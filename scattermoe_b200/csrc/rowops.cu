@@ -130,6 +130,20 @@ gate_grad_kernel(const T* __restrict__ Yx, int64_t syxm, const T* __restrict__ g
   if (lane == 0) dg[t * sdgt + j * sdgk] = from_f32<T>(acc);
 }
 
+// ---- gate gradient from the partial sums of the fused gradient epilogue -------------------------------------
+// d_gates[slot(m)] = sum over lines l of partials[l * R + m]; one thread per sorted position m.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gate_grad_partials_kernel(const float* __restrict__ partials, int lines, int64_t R, const int64_t* __restrict__ sorted_idx,
+                          T* __restrict__ d_gates) {
+  const int64_t m = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (m >= R) return;
+  float acc = 0.f;
+  for (int l = 0; l < lines; ++l) acc += partials[static_cast<int64_t>(l) * R + m];
+  const int64_t slot = sorted_idx[m];
+  if (slot >= 0 && slot < R) d_gates[slot] = from_f32<T>(acc);
+}
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 template <typename T>
@@ -221,4 +235,22 @@ extern "C" int smoe_gate_grad(const void* Yx, int64_t stride_yxm, const void* gr
   SMOE_CHECK_ARG(Yx && grad_out && d_gates, "gate_grad: null pointer");
   SMOE_DISPATCH_DTYPE(dtype, gate_grad_typed, Yx, stride_yxm, grad_out, stride_gom, d_gates, stride_dgt, stride_dgk, T,
                       k, N, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int smoe_gate_grad_from_partials(const float* partials, int32_t lines, int64_t R,
+                                            const int64_t* sorted_scattered_idxs, void* d_gates, int32_t dtype,
+                                            void* stream) {
+  SMOE_CHECK_ARG(R >= 0 && lines >= 1, "gate_grad_from_partials: bad sizes R=%lld lines=%d", (long long)R, lines);
+  if (R == 0) return SMOE_OK;
+  SMOE_CHECK_ARG(partials && sorted_scattered_idxs && d_gates, "gate_grad_from_partials: null pointer");
+  const unsigned grid = static_cast<unsigned>(cdiv64(R, 256));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case SMOE_F32: gate_grad_partials_kernel<float><<<grid, 256, 0, st>>>(partials, lines, R, sorted_scattered_idxs, static_cast<float*>(d_gates)); break;
+    case SMOE_BF16: gate_grad_partials_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(partials, lines, R, sorted_scattered_idxs, static_cast<__nv_bfloat16*>(d_gates)); break;
+    case SMOE_F16: gate_grad_partials_kernel<__half><<<grid, 256, 0, st>>>(partials, lines, R, sorted_scattered_idxs, static_cast<__half*>(d_gates)); break;
+    default: set_error("gate_grad_from_partials: unknown dtype %d", dtype); return SMOE_ERR_BAD_ARG;
+  }
+  SMOE_LAUNCH_CHECK();
+  return SMOE_OK;
 }

@@ -78,6 +78,9 @@ struct S2SArgs {
   // fused activation-gradient epilogue: U = saved up-projection (rows, n_up); Y then receives dU, N is F
   const void* U = nullptr; int64_t sum = 0;
   int act_bwd = 0;
+  // per-slot gates for the fused epilogues (nullable) and the gate gradient's partial sums (act_bwd only, nullable)
+  const void* row_gate = nullptr;
+  float* dot_out = nullptr;
 };
 
 struct WGradArgs {

@@ -129,7 +129,7 @@ def scatter2scatter(X, W, sorted_expert_idxs, sorted_scattered_idxs, k, b=None, 
 
 
 def _scatter2scatter_act_impl(up, hidden, W, X, k, sorted_expert_idxs, sorted_scattered_idxs, b, x_grouped,
-                              expert_offsets, act_layout, act, alpha, limit) -> bool:
+                              expert_offsets, act_layout, act, alpha, limit, row_gates=None) -> bool:
     """One launch writing `hidden` (and `up` unless None). False: the request does not fit the tensor-core kernel and
     nothing was launched."""
     _lib.require_cuda(X, "X")
@@ -139,6 +139,7 @@ def _scatter2scatter_act_impl(up, hidden, W, X, k, sorted_expert_idxs, sorted_sc
     E, N = W.size(0), W.size(-1)
     off = _i64(expert_offsets if expert_offsets is not None else offsets_from_sorted(se, E))
     sb = (b.stride(0), b.stride(1)) if b is not None else (0, 0)
+    rg = _flat_gates(row_gates, X.dtype, se.numel())
     with torch.cuda.device(X.device):
         rc = _lib.load().smoe_scatter2scatter_act(
             X.data_ptr(), X.size(0), X.stride(0), X.stride(1),
@@ -147,7 +148,7 @@ def _scatter2scatter_act_impl(up, hidden, W, X, k, sorted_expert_idxs, sorted_sc
             _ptr(up), up.stride(0) if up is not None else 0, 1, hidden.data_ptr(), hidden.stride(0),
             se.data_ptr(), ss.data_ptr(), off.data_ptr(),
             se.numel(), X.size(1), N, E, k, int(x_grouped), _dtype_code(X), _flags(),
-            act_layout, act, float(alpha), float(limit),
+            act_layout, act, float(alpha), float(limit), _ptr(rg),
             _lib.status_word(X.device).data_ptr(), _lib.stream_ptr(X.device))
     if rc == _lib.SMOE_ERR_UNSUPPORTED:
         return False
@@ -155,29 +156,44 @@ def _scatter2scatter_act_impl(up, hidden, W, X, k, sorted_expert_idxs, sorted_sc
     return True
 
 
+def _flat_gates(row_gates, dtype, n):
+    """(T, k) gates -> contiguous flat tensor in the compute dtype, indexed by slot."""
+    if row_gates is None:
+        return None
+    g = row_gates.reshape(-1)
+    if g.numel() != n:
+        raise AssertionError("row_gates has %d entries, %d slots expected" % (g.numel(), n))
+    if g.dtype != dtype:
+        g = g.to(dtype)
+    return g if g.is_contiguous() else g.contiguous()
+
+
 @torch.library.custom_op("scattermoe_b200::scatter2scatter_act", mutates_args={"up", "hidden"})
 def scatter2scatter_act_compileable(up: torch.Tensor, hidden: torch.Tensor, W: torch.Tensor, X: torch.Tensor, k: int,
                                     sorted_expert_idxs: torch.Tensor, sorted_scattered_idxs: torch.Tensor,
                                     b: Optional[torch.Tensor], x_grouped: bool,
                                     expert_offsets: Optional[torch.Tensor], act_layout: int, act: int, alpha: float,
-                                    limit: float) -> None:
+                                    limit: float, row_gates: Optional[torch.Tensor] = None) -> None:
     """Traceable form: always fills both outputs, by the fused kernel when it applies, else by the grouped GEMM
     followed by the activation kernel (a traced graph cannot branch on what the library answers)."""
     if not _scatter2scatter_act_impl(up, hidden, W, X, k, sorted_expert_idxs, sorted_scattered_idxs, b, x_grouped,
-                                     expert_offsets, act_layout, act, alpha, limit):
+                                     expert_offsets, act_layout, act, alpha, limit, row_gates):
         from .. import activation as _act
         _scatter2scatter_impl(up, W, X, k, sorted_expert_idxs, sorted_scattered_idxs, b, x_grouped, True,
                               expert_offsets)
         _act._call(False, up, None, hidden, hidden.size(1), act_layout, act, alpha, limit)
+        if row_gates is not None:
+            hidden.mul_(row_gates.reshape(-1).to(hidden.dtype)[sorted_scattered_idxs].unsqueeze(1))
 
 
 def scatter2scatter_act(X, W, sorted_expert_idxs, sorted_scattered_idxs, k, act_layout, act, b=None, x_grouped=False,
-                        expert_offsets=None, alpha=1.702, limit=7.0, need_up=True):
+                        expert_offsets=None, alpha=1.702, limit=7.0, need_up=True, row_gates=None):
     """Up-projection into expert order with the activation fused into the kernel's epilogue (the first expert
     linear and the activation of scattermoe/mlp.py:35-41 / :76-87 in one launch). Returns (up, hidden), `up` None
     when `need_up` is False; returns None when the request does not fit the tensor-core kernel (the caller then
     uses `scatter2scatter` and the activation kernel; while torch.compile traces, that choice is made inside the
-    registered operator and the result is never None). Layout / function codes: scattermoe_b200.activation."""
+    registered operator and the result is never None). Layout / function codes: scattermoe_b200.activation.
+    `row_gates` ((T, k), optional): `hidden` rows are multiplied by the gate of their slot (`up` is not)."""
     assert sorted_scattered_idxs.size(0) == sorted_expert_idxs.size(0)
     assert sorted_scattered_idxs.size(0) == X.size(0) * k
     R, N = sorted_expert_idxs.size(0), W.size(-1)
@@ -186,37 +202,57 @@ def scatter2scatter_act(X, W, sorted_expert_idxs, sorted_scattered_idxs, k, act_
         up = torch.empty((R, N), device=X.device, dtype=X.dtype)
         hidden = torch.empty((R, F), device=X.device, dtype=X.dtype)
         scatter2scatter_act_compileable(up, hidden, W, X, k, sorted_expert_idxs, sorted_scattered_idxs, b, x_grouped,
-                                        expert_offsets, act_layout, act, float(alpha), float(limit))
+                                        expert_offsets, act_layout, act, float(alpha), float(limit), row_gates)
         return up, hidden
     up = torch.empty((R, N), device=X.device, dtype=X.dtype) if need_up else None
     hidden = torch.empty((R, F), device=X.device, dtype=X.dtype)
     if not _scatter2scatter_act_impl(up, hidden, W, X, k, sorted_expert_idxs, sorted_scattered_idxs, b, x_grouped,
-                                     expert_offsets, act_layout, act, alpha, limit):
+                                     expert_offsets, act_layout, act, alpha, limit, row_gates):
         return None
     return up, hidden
 
 
-def _scatter2scatter_act_bwd_impl(d_up, DY, W, up, expert_offsets, act_layout, act, alpha, limit) -> bool:
-    """One launch writing `d_up` = activation gradient of (DY @ W) with respect to the saved up-projection `up`.
-    False: the request does not fit the tensor-core kernel and nothing was launched."""
+def _scatter2scatter_act_bwd_impl(d_up, DY, W, up, expert_offsets, act_layout, act, alpha, limit, row_gates=None,
+                                  sorted_scattered_idxs=None, partials=None) -> bool:
+    """One launch writing `d_up` = activation gradient of (DY @ W) with respect to the saved up-projection `up`
+    (and, with gates, the gate gradient's partial sums into `partials`). False: the request does not fit the
+    tensor-core kernel and nothing was launched."""
     _lib.require_cuda(DY, "DY")
     if FORCE_PATH == "simt" or DY.dtype not in (torch.bfloat16, torch.float16) or W.dtype != DY.dtype:
         return False
     if up.dtype != DY.dtype or up.stride(1) != 1 or d_up.stride(1) != 1 or d_up.shape != up.shape:
         return False
     off = _i64(expert_offsets)
+    rg = _flat_gates(row_gates, DY.dtype, DY.size(0))
+    ss = _i64(sorted_scattered_idxs) if rg is not None else None
     with torch.cuda.device(DY.device):
         rc = _lib.load().smoe_scatter2scatter_act_bwd(
             DY.data_ptr(), DY.stride(0), DY.stride(1),
             W.data_ptr(), W.stride(0), W.stride(1), W.stride(2),
             up.data_ptr(), up.stride(0), d_up.data_ptr(), d_up.stride(0),
             off.data_ptr(), DY.size(0), DY.size(1), W.size(-1), W.size(0), _dtype_code(DY), _flags(),
-            act_layout, act, float(alpha), float(limit),
+            act_layout, act, float(alpha), float(limit), _ptr(rg), _ptr(ss), _ptr(partials if rg is not None else None),
             _lib.status_word(DY.device).data_ptr(), _lib.stream_ptr(DY.device))
     if rc == _lib.SMOE_ERR_UNSUPPORTED:
         return False
     _lib.check(rc, "smoe_scatter2scatter_act_bwd")
     return True
+
+
+def _partial_lines(F: int) -> int:
+    return 2 * ((F + 255) // 256)
+
+
+def _gate_grad_from_partials(partials, sorted_scattered_idxs, dtype):
+    R = partials.size(1)
+    d_gates = torch.empty(R, dtype=dtype, device=partials.device)
+    ss = _i64(sorted_scattered_idxs)
+    with torch.cuda.device(partials.device):
+        rc = _lib.load().smoe_gate_grad_from_partials(partials.data_ptr(), partials.size(0), R, ss.data_ptr(),
+                                                      d_gates.data_ptr(), _lib.DTYPE_CODE[dtype],
+                                                      _lib.stream_ptr(partials.device))
+    _lib.check(rc, "smoe_gate_grad_from_partials")
+    return d_gates
 
 
 @torch.library.custom_op("scattermoe_b200::scatter2scatter_act_bwd", mutates_args={"d_up"})
@@ -228,33 +264,74 @@ def scatter2scatter_act_bwd_compileable(d_up: torch.Tensor, DY: torch.Tensor, W:
     _scatter2scatter_act_bwd_fill(d_up, DY, W, up, expert_offsets, act_layout, act, alpha, limit)
 
 
-def _scatter2scatter_act_bwd_fill(d_up, DY, W, up, expert_offsets, act_layout, act, alpha, limit):
-    if _scatter2scatter_act_bwd_impl(d_up, DY, W, up, expert_offsets, act_layout, act, alpha, limit):
-        return
-    from .. import activation as _act
+@torch.library.custom_op("scattermoe_b200::scatter2scatter_act_bwd_gated", mutates_args={"d_up", "d_gates"})
+def scatter2scatter_act_bwd_gated_compileable(d_up: torch.Tensor, d_gates: torch.Tensor, DY: torch.Tensor, W: torch.Tensor,
+                                              up: torch.Tensor, expert_offsets: torch.Tensor, act_layout: int, act: int,
+                                              alpha: float, limit: float, row_gates: torch.Tensor,
+                                              sorted_scattered_idxs: torch.Tensor) -> None:
+    """Traceable form of the variant that takes the un-weighted output gradient and the gates: fills `d_up` and
+    `d_gates` (flat by slot)."""
+    _scatter2scatter_act_bwd_fill(d_up, DY, W, up, expert_offsets, act_layout, act, alpha, limit, row_gates,
+                                  sorted_scattered_idxs, d_gates)
+
+
+def _scatter2scatter_act_bwd_fill(d_up, DY, W, up, expert_offsets, act_layout, act, alpha, limit, row_gates=None,
+                                  sorted_scattered_idxs=None, d_gates=None):
+    F = W.size(-1)
     R = DY.size(0)
-    d_hidden = torch.empty((R, W.size(-1)), device=DY.device, dtype=DY.dtype)
+    partials = None
+    if row_gates is not None:
+        partials = torch.empty((_partial_lines(F), R), dtype=torch.float32, device=DY.device)
+    if _scatter2scatter_act_bwd_impl(d_up, DY, W, up, expert_offsets, act_layout, act, alpha, limit, row_gates,
+                                     sorted_scattered_idxs, partials):
+        if row_gates is not None:
+            d_gates.copy_(_gate_grad_from_partials(partials, sorted_scattered_idxs, d_gates.dtype))
+        return
+    # the two separate kernels (CUDA cores for fp32 / unaligned shapes)
+    from .. import activation as _act
+    d_hidden = torch.empty((R, F), device=DY.device, dtype=DY.dtype)
     # rows are in expert order on both sides; the CUDA-core kernel still reads each row's expert id
     rows = torch.arange(R, device=DY.device, dtype=torch.int64)
     sorted_e = torch.searchsorted(_i64(expert_offsets), rows, right=True)
     _scatter2scatter_impl(d_hidden, W, DY, 1, sorted_e, rows, None, True, True, expert_offsets)
-    _act._call(True, up, d_hidden, d_up, d_hidden.size(1), act_layout, act, alpha, limit)
+    if row_gates is not None:
+        # gate gradient <hidden (un-weighted), d_hidden (un-weighted)> per row, then the gate on the hidden gradient
+        hidden = torch.empty_like(d_hidden)
+        _act._call(False, up, None, hidden, F, act_layout, act, alpha, limit)
+        slots = _i64(sorted_scattered_idxs)
+        d_gates[slots] = (hidden.float() * d_hidden.float()).sum(-1).to(d_gates.dtype)
+        d_hidden = d_hidden * row_gates.reshape(-1).to(d_hidden.dtype)[slots].unsqueeze(1)
+    _act._call(True, up, d_hidden, d_up, F, act_layout, act, alpha, limit)
 
 
-def scatter2scatter_act_bwd(DY, W, up, expert_offsets, act_layout, act, alpha=1.702, limit=7.0):
+def scatter2scatter_act_bwd(DY, W, up, expert_offsets, act_layout, act, alpha=1.702, limit=7.0, row_gates=None,
+                            sorted_scattered_idxs=None):
     """Gradient of the up-projection `up` (rows, n_up) given the gradient `DY` (rows, K) of the down-projection's
     OUTPUT, rows in expert order: d_up = activation'(up) applied to DY @ W, with W the (E, K, F) transposed view of
     the down-projection weight. One tensor-core launch whose epilogue applies the activation gradient (the
     autograd of scattermoe/mlp.py:41 / :81-87 fused into the grouped GEMM of scattermoe/parallel_experts.py:110-116);
     the (rows, F) hidden gradient is not materialised. Falls back to the two separate kernels when the request does
-    not fit the tensor-core kernel."""
+    not fit the tensor-core kernel.
+
+    With `row_gates` ((T, k)) and `sorted_scattered_idxs`, DY is the UN-weighted output gradient: the hidden gradient
+    is scaled by each row's gate inside the epilogue, which also yields the gate gradient (the row dot product of
+    scattermoe/parallel_experts.py:79, taken on the hidden side of the down-projection). Returns (d_up, d_gates)
+    then, d_gates flat by slot in the dtype of DY."""
     d_up = torch.empty_like(up)
+    d_gates = None
+    if row_gates is not None:
+        d_gates = torch.empty(DY.size(0), dtype=DY.dtype, device=DY.device)
     if torch.compiler.is_compiling():
-        scatter2scatter_act_bwd_compileable(d_up, DY, W, up, expert_offsets, act_layout, act, float(alpha),
-                                            float(limit))
+        if row_gates is None:
+            scatter2scatter_act_bwd_compileable(d_up, DY, W, up, expert_offsets, act_layout, act, float(alpha),
+                                                float(limit))
+        else:
+            scatter2scatter_act_bwd_gated_compileable(d_up, d_gates, DY, W, up, expert_offsets, act_layout, act,
+                                                      float(alpha), float(limit), row_gates, sorted_scattered_idxs)
     else:
-        _scatter2scatter_act_bwd_fill(d_up, DY, W, up, expert_offsets, act_layout, act, alpha, limit)
-    return d_up
+        _scatter2scatter_act_bwd_fill(d_up, DY, W, up, expert_offsets, act_layout, act, alpha, limit, row_gates,
+                                      sorted_scattered_idxs, d_gates)
+    return d_up if row_gates is None else (d_up, d_gates)
 
 
 # --------------------------------------------------------------------------------------------------

@@ -72,6 +72,11 @@ def flatten_sort_count(expert_idxs: torch.Tensor, num_experts: int):
 # TMA-fed kernels run ~2x faster than the cp.async row gather for the weight gradient. False: gather in-kernel.
 GROUP_INPUT_COPY = True
 
+# `ExpertMLP` without a down-projection bias: apply the gates to the hidden rows inside the fused up-projection kernel
+# and take the gate gradient from the fused hidden-gradient kernel (no separate gate-weighting or gate-gradient pass).
+# False: gate-weighted top-k sum after the down-projection and a separate gate-gradient kernel, as the reference does.
+FUSE_GATES = True
+
 
 def _rowmajor(t: torch.Tensor) -> torch.Tensor:
     return t if t.stride(-1) == 1 else t.contiguous()
@@ -252,9 +257,17 @@ class ExpertMLP(torch.autograd.Function):
         # the up-projection itself is only kept for backward: without a gradient to compute (inference, torch.no_grad)
         # the fused kernel writes the hidden rows alone
         training = any(ctx.needs_input_grad[:6])
+        # Without a bias on the down-projection the gate weighting moves in front of it (the projection is linear): the
+        # fused up-projection kernel writes hidden * gate, the per-slot outputs come out weighted and the layer's
+        # output is their plain sum. Backward then gets the gate gradient from the same launch that computes the
+        # hidden gradient (kernels.ops.scatter2scatter_act_bwd).
+        want_gated = (FUSE_GATES and b_down is None and x.dtype in (torch.bfloat16, torch.float16)
+                      and kernels.ops.FORCE_PATH != "simt")
         res = kernels.ops.scatter2scatter_act(x_src, w_up, sorted_expert_idxs, sorted_scattered_idxs, kk, act_layout,
                                               act, b=b_up, x_grouped=grouped, expert_offsets=expert_offsets,
-                                              alpha=alpha, limit=limit, need_up=training)
+                                              alpha=alpha, limit=limit, need_up=training,
+                                              row_gates=gates if want_gated else None)
+        gated = want_gated and res is not None
         if res is None:     # not a tensor-core case: the two separate kernels
             up = kernels.ops.scatter2scatter(x_src, w_up, sorted_expert_idxs, sorted_scattered_idxs, kk, b=b_up,
                                              x_grouped=grouped, y_grouped=True, expert_offsets=expert_offsets)
@@ -265,35 +278,47 @@ class ExpertMLP(torch.autograd.Function):
             up, hidden = res
         per_slot = kernels.ops.scatter2scatter(hidden, w_down, sorted_expert_idxs, sorted_scattered_idxs, 1, b=b_down,
                                                x_grouped=True, y_grouped=False, expert_offsets=expert_offsets)
-        out = kernels.ops.topk_reduce(per_slot, gates, T, k)
+        out = kernels.ops.topk_reduce(per_slot, None if gated else gates, T, k)
         ctx.save_for_backward(x, w_up, b_up, w_down, b_down, gates, sorted_expert_idxs, sorted_scattered_idxs,
                               expert_offsets, up, hidden, per_slot, x_src if grouped else None)
-        ctx.cfg = (k, act_layout, act, alpha, limit)
+        ctx.cfg = (k, act_layout, act, alpha, limit, gated)
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
         (x, w_up, b_up, w_down, b_down, gates, sorted_expert_idxs, sorted_scattered_idxs, expert_offsets, up, hidden,
          per_slot, x_in_expert_order) = ctx.saved_tensors
-        k, act_layout, act, alpha, limit = ctx.cfg
+        k, act_layout, act, alpha, limit, gated = ctx.cfg
         T, E = x.size(0), w_up.size(0)
         need = ctx.needs_input_grad
         grad_out = _rowmajor(grad_out)
         if grad_out.dtype != x.dtype:
             grad_out = grad_out.to(x.dtype)
-        d_gates = kernels.ops.gate_grad(per_slot, grad_out, T, k).to(gates.dtype) if need[5] else None
+        d_gates = None
+        if need[5] and not gated:
+            d_gates = kernels.ops.gate_grad(per_slot, grad_out, T, k).to(gates.dtype)
         d_x = d_w_up = d_b_up = d_w_down = d_b_down = None
-        if need[0] or need[1] or need[2] or need[3] or need[4]:
-            # gate-scaled output gradient in expert order; written over the per-slot outputs, which nothing reads
-            # after the gate gradient (a traced backward must not write into a tensor saved by forward)
-            grouped_grad = kernels.ops.group(grad_out, sorted_scattered_idxs, fan_out=k, coeff=gates.flatten(),
+        need_up_grad = need[0] or need[1] or (b_up is not None and need[2]) or (gated and need[5])
+        if need_up_grad or need[3] or need[4]:
+            # the output gradient in expert order (gate-scaled unless the hidden rows carry the gate); written over the
+            # per-slot outputs, which nothing reads any more (a traced backward must not write into a tensor saved by
+            # forward)
+            grouped_grad = kernels.ops.group(grad_out, sorted_scattered_idxs, fan_out=k,
+                                             coeff=None if gated else gates.flatten(),
                                              out=None if torch.compiler.is_compiling() else per_slot)
             if need[3] or (b_down is not None and need[4]):
                 d_w_down, d_b_down = kernels.ops.group_bwd_W(DY=grouped_grad, X=hidden, expert_offsets=expert_offsets,
                                                              E=E, has_bias=b_down is not None)
-            if need[0] or need[1] or (b_up is not None and need[2]):
-                d_up = kernels.ops.scatter2scatter_act_bwd(grouped_grad, w_down.permute(0, 2, 1), up, expert_offsets,
-                                                           act_layout, act, alpha, limit)
+            if need_up_grad:
+                if gated:
+                    d_up, flat = kernels.ops.scatter2scatter_act_bwd(
+                        grouped_grad, w_down.permute(0, 2, 1), up, expert_offsets, act_layout, act, alpha, limit,
+                        row_gates=gates, sorted_scattered_idxs=sorted_scattered_idxs)
+                    if need[5]:
+                        d_gates = flat.view(T, k).to(gates.dtype)
+                else:
+                    d_up = kernels.ops.scatter2scatter_act_bwd(grouped_grad, w_down.permute(0, 2, 1), up, expert_offsets,
+                                                               act_layout, act, alpha, limit)
                 if need[1] or (b_up is not None and need[2]):
                     grouped = x_in_expert_order is not None
                     d_w_up, d_b_up = kernels.ops.group_bwd_W(

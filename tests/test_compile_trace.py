@@ -108,3 +108,5 @@ def test_patched_hugging_face_block_traces_as_one_graph(recorder, family):
     # and the input gradient of the up-projection
     assert recorder.calls.count("smoe_group_bwd_w") == 2 and recorder.calls.count("smoe_scatter2scatter") == 1
     assert recorder.calls.count("smoe_scatter2scatter_act_bwd") == 1 and "smoe_activation_backward" not in recorder.calls
+    if family == "qwen3_moe":       # no down-projection bias: the gate gradient comes out of the fused launch
+        assert "smoe_gate_grad" not in recorder.calls and "smoe_gate_grad_from_partials" in recorder.calls

@@ -486,3 +486,53 @@ def test_group_bwd_w_many_tiles_per_cta(T, E, k, K, N, zipf, gathered):
     scale = counts.sqrt().view(E, 1, 1)               # sums over the expert's rows of unit-variance products
     assert_close("DW", DW.float().cpu() / scale, wDW / scale, True)
     assert_close("Db", Db.float().cpu() / scale.view(E, 1), wDb / scale.view(E, 1), True)
+
+
+@pytest.mark.parametrize("path", ["tc", "simt"])
+@pytest.mark.parametrize("layout,act", [("plain", "gelu"), ("glu_second", "silu"), ("glu_first", "gelu"), ("gpt_oss", None)])
+@pytest.mark.parametrize("T,E,k,K,F", [(513, 8, 3, 320, 200), (1000, 8, 2, 256, 384), (16384, 8, 4, 128, 512)])
+def test_fused_epilogues_with_gates(T, E, k, K, F, layout, act, path):
+    """Gates inside the fused epilogues: the up-projection kernel writes hidden * gate (the up-projection itself
+    un-weighted); the gradient kernel takes the UN-weighted output gradient, scales the hidden gradient by the gate
+    and returns the gate gradient <hidden, d_hidden> (the reference's `output_expanded @ grad_out`,
+    parallel_experts.py:79, taken on the other side of the linear down-projection). The last shape makes every CTA
+    walk several tiles."""
+    from scattermoe_b200.kernels import ops
+    dtype = torch.bfloat16
+    n_up = F if layout == "plain" else 2 * F
+    gates, idx, g = _routing(T, E, k, seed=T + K + F + 9, skew=True)
+    gates = gates.to(dtype)
+    se, ss, off = oracle.flatten_sort_count(idx, E)
+    R = T * k
+    lay, code = _act_codes(layout, act)
+    X = torch.randn(T, K, generator=g).to(dtype)
+    W1 = (torch.randn(E, n_up, K, generator=g) * 0.1).to(dtype).permute(0, 2, 1)
+    row_g = gates.float().reshape(-1)[ss].unsqueeze(1)                  # gate of every expert-ordered row
+    # forward
+    ops.FORCE_PATH = None
+    res = ops.scatter2scatter_act(_dev(X), _dev(W1), _dev(se), _dev(ss), k, lay, code, expert_offsets=_dev(off),
+                                  row_gates=_dev(gates))
+    assert res is not None
+    up, hidden = res
+    want_up = oracle.scatter2scatter(X.float(), W1.float(), se, ss, k, y_grouped=True)
+    want_h = _act_reference(layout, act, want_up)
+    assert_close("up", up, want_up, True)
+    assert_close("hidden * gate", hidden, want_h * row_g, True, atol_scale=max(1.0, want_h.abs().max().item() / 4))
+    # backward
+    DY = torch.randn(R, K, generator=g).to(dtype)                        # un-weighted output gradient, expert order
+    W2t = (torch.randn(E, K, F, generator=g) * 0.1).to(dtype)
+    ops.FORCE_PATH = path if path == "simt" else None
+    d_up, d_gates = ops.scatter2scatter_act_bwd(_dev(DY), _dev(W2t), up, _dev(off), lay, code, row_gates=_dev(gates),
+                                                sorted_scattered_idxs=_dev(ss))
+    if path == "tc":
+        assert ops.last_path_was_tensor_core()
+    d_hidden0 = oracle.scatter2scatter(DY.float(), W2t.float(), se, ss, 1, x_grouped=True, y_grouped=True)
+    ref_in = up.float().cpu().requires_grad_()
+    h_ref = _act_reference(layout, act, ref_in)
+    (want_d_up,) = torch.autograd.grad(h_ref, ref_in, d_hidden0 * row_g)
+    want_dg = torch.empty(R)
+    want_dg[ss] = (h_ref.detach() * d_hidden0).sum(-1)
+    assert_close("d_up", d_up, want_d_up, True, atol_scale=max(1.0, want_d_up.abs().max().item() / 4))
+    assert d_gates.shape == (R,)
+    scale = max(1.0, float(want_dg.pow(2).mean().sqrt()))              # a dot product of F bf16-rounded products
+    assert_close("d_gates", d_gates.float().cpu() / scale, want_dg / scale, True)
