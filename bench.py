@@ -277,7 +277,7 @@ class LaunchCounter:
                "smoe_ep_return": 1, "smoe_ep_barrier": 1, "smoe_sort_count": 3, "smoe_sort_count_static": 3,
                "smoe_offsets_from_sorted": 1, "smoe_scatter2scatter": 1, "smoe_group_bwd_w": 1, "smoe_group": 1,
                "smoe_topk_reduce": 1, "smoe_gate_grad": 1, "smoe_activation_forward": 1, "smoe_activation_backward": 1,
-               "smoe_route_topk": 3, "smoe_status_poison": 1, "smoe_ep_plan_tokens": 1, "smoe_ep_dispatch_meta": 1,
+               "smoe_route_topk": 3, "smoe_status_poison": 1, "smoe_gate_grad_from_partials": 1, "smoe_ep_plan_tokens": 1, "smoe_ep_dispatch_meta": 1,
                "smoe_ep_expand": 1, "smoe_ep_combine": 1, "smoe_ep_sum_parts": 1}
 
     def __init__(self):
