@@ -707,7 +707,10 @@ def measure(name, c, device, rank, world, dist, steps, warmup, with_e2e=True, sa
                             dev_in["idx"])
 
     out_host = dict(y=torch.empty_like(host["x"]).pin_memory(), dx=torch.empty_like(host["x"]).pin_memory())
+    # two copy streams, one per direction: PCIe is full duplex, and a result travelling back must not queue behind the
+    # next step's inputs
     copy_stream = torch.cuda.Stream(device=device)
+    back_stream = torch.cuda.Stream(device=device)
     staged = {}
 
     def stage_inputs():
@@ -718,9 +721,9 @@ def measure(name, c, device, rank, world, dist, steps, warmup, with_e2e=True, sa
             staged["ready"].record(copy_stream)
 
     def e2e_step(prefetch):
-        # Every step copies its own inputs from pinned host memory and its results back. The copies run on a
-        # second stream: the next step's inputs are enqueued while this step computes, and this step's results
-        # travel back while the next step computes.
+        # Every step copies its own inputs from pinned host memory and its results back. The copies run on two
+        # streams of their own: the next step's inputs are enqueued while this step computes, and this step's
+        # results travel back while the next step computes.
         cur = torch.cuda.current_stream(device)
         cur.wait_event(staged["ready"])
         ins = staged.pop("in")
@@ -732,10 +735,10 @@ def measure(name, c, device, rank, world, dist, steps, warmup, with_e2e=True, sa
         dx = grads[0]
         done = torch.cuda.Event()
         done.record(cur)
-        with torch.cuda.stream(copy_stream):
-            copy_stream.wait_event(done)
-            y.record_stream(copy_stream)
-            dx.record_stream(copy_stream)
+        with torch.cuda.stream(back_stream):
+            back_stream.wait_event(done)
+            y.record_stream(back_stream)
+            dx.record_stream(back_stream)
             out_host["y"].copy_(y, non_blocking=True)
             out_host["dx"].copy_(dx, non_blocking=True)
 
@@ -747,6 +750,7 @@ def measure(name, c, device, rank, world, dist, steps, warmup, with_e2e=True, sa
         for i in range(n):
             e2e_step(prefetch=(i + 1 < n))
         torch.cuda.current_stream(device).wait_stream(copy_stream)
+        torch.cuda.current_stream(device).wait_stream(back_stream)
 
     def timed(fn, n):
         barrier()
