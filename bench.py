@@ -274,7 +274,7 @@ class LaunchCounter:
     """Counts the kernels this library launches: a proxy in front of the ctypes library that knows how many
     kernels each C entry point enqueues."""
     KERNELS = {"smoe_scatter2scatter_act": 1, "smoe_scatter2scatter_act_bwd": 1, "smoe_ep_dispatch": 1,
-               "smoe_ep_return": 1, "smoe_ep_barrier": 1, "smoe_sort_count": 3, "smoe_sort_count_static": 3,
+               "smoe_ep_return": 1, "smoe_scatter2scatter_to_peers": 1, "smoe_ep_barrier": 1, "smoe_sort_count": 3, "smoe_sort_count_static": 3,
                "smoe_offsets_from_sorted": 1, "smoe_scatter2scatter": 1, "smoe_group_bwd_w": 1, "smoe_group": 1,
                "smoe_topk_reduce": 1, "smoe_gate_grad": 1, "smoe_activation_forward": 1, "smoe_activation_backward": 1,
                "smoe_route_topk": 3, "smoe_status_poison": 1, "smoe_gate_grad_from_partials": 1, "smoe_ep_plan_tokens": 1, "smoe_ep_dispatch_meta": 1,
@@ -299,7 +299,10 @@ class LaunchCounter:
             s0.record()
             rc = fn(*a)
             s1.record()
-            self.events.append((name, s0, s1))
+            if rc == self._mod.SMOE_ERR_UNSUPPORTED:      # nothing was launched: the caller takes its two-call form
+                self.count -= n
+            else:
+                self.events.append((name, s0, s1))
             return rc
         return counted
 
@@ -916,6 +919,9 @@ def main():
     ap.add_argument("--once-per-rank", choices=("auto", "on", "off"), default="auto",
                     help="NVLink exchange: send each token once per owning rank instead of once per slot (auto: when "
                          "that saves at least 30 % of the rows)")
+    ap.add_argument("--separate-return", action="store_true",
+                    help="per-slot NVLink exchange: return rows with a push kernel after the GEMM instead of from the "
+                         "GEMM's own epilogue")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-triton-ref", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
@@ -960,6 +966,9 @@ def main():
         dist.init_process_group("nccl", device_id=device)
 
     once = {"auto": None, "on": True, "off": False}[args.once_per_rank]
+    if args.separate_return:
+        import scattermoe_b200.expert_parallel as _ep
+        _ep.FUSE_RETURN = False
     fields, st = measure(name, c, device, rank, world, dist, args.steps, args.warmup, with_e2e=True,
                          sampler_gpu=local_rank, exchange=args.exchange, chunks=args.chunks, keep=(world == 1),
                          once_per_rank=once)

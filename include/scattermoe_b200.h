@@ -23,7 +23,7 @@
 extern "C" {
 #endif
 
-#define SMOE_ABI_VERSION 3
+#define SMOE_ABI_VERSION 4
 
 enum smoe_status {
   SMOE_OK = 0,
@@ -253,6 +253,22 @@ int smoe_ep_dispatch(const void* X, int64_t x_rows, int64_t stride_xm, const int
 int smoe_ep_return(const void* Y, int64_t stride_ym, const int64_t* return_addr, const int64_t* live_rows,
                    int64_t capacity_rows, void* const* peer_slot_bufs, int64_t peer_stride_rows, int64_t peer_rows,
                    int32_t K, int32_t world, int32_t my_rank, int32_t local_experts, int32_t dtype, void* stream);
+/* smoe_scatter2scatter_to_peers: the grouped GEMM of the local experts and smoe_ep_return in ONE kernel. X is the
+ * owner's expert-grouped (x_rows, K) buffer (x_rows = its capacity; the live rows are those the offsets of the E
+ * LOCAL experts delimit), W is (E, K, N) in element strides; for every live row i
+ *     (r, s) = return_addr[i];  peer_slot_bufs[r][s, 0:N] = X[i, :] @ W[expert of row i]
+ * written by the epilogue of the tcgen05 kernel with plain peer stores, 64 bytes of a row per store instruction, as
+ * each 128 x 256 tile finishes: the rows cross NVLink while the tensor cores work on the next tile, and the local
+ * result buffer of the two-call form does not exist. Rank `my_rank` walks the row tiles of every expert starting
+ * my_rank / world of the way in (the same reason as the rotation of smoe_ep_return). Tensor-core kernel only:
+ * returns SMOE_ERR_UNSUPPORTED (nothing launched, no error text) when the request does not fit it (dtype, alignment);
+ * the caller then runs smoe_scatter2scatter and smoe_ep_return. */
+int smoe_scatter2scatter_to_peers(const void* X, int64_t x_rows, int64_t stride_xm, int64_t stride_xk,
+                                  const void* W, int64_t stride_we, int64_t stride_wk, int64_t stride_wn,
+                                  const int64_t* expert_offsets, const int64_t* return_addr,
+                                  void* const* peer_slot_bufs, int64_t peer_stride_rows, int64_t peer_rows,
+                                  int32_t world, int32_t my_rank, int32_t K, int32_t N, int32_t E, int32_t dtype,
+                                  int32_t flags, int32_t* status, void* stream);
 /* ---- the same exchange with every token row crossing NVLink once per owning rank (no counterpart in the reference) ----
  * A token whose k slots fall on n distinct ranks is sent n times instead of k times, and n rows come back. The caller
  * lists the distinct (token, rank) pairs in rank order (a counting sort of each token's first slot per rank) and

@@ -17,7 +17,7 @@ from . import build as _build
 _lock = threading.Lock()
 _lib = None
 
-ABI_VERSION = 3          # SMOE_ABI_VERSION of include/scattermoe_b200.h this binding was written against
+ABI_VERSION = 4          # SMOE_ABI_VERSION of include/scattermoe_b200.h this binding was written against
 
 SMOE_OK = 0
 SMOE_ERR_BAD_ARG = 1
@@ -77,6 +77,8 @@ SIGNATURES = {
     "smoe_ep_dispatch": ([_P, _I64, _I64, _P, _P, _P, _P, _P, _I32, _P, _I64, _I64, _P, _I32, _I64, _I32, _I32, _I32, _I32,
                           _P], c_int32),
     "smoe_ep_return": ([_P, _I64, _P, _P, _I64, _P, _I64, _I64, _I32, _I32, _I32, _I32, _I32, _P], c_int32),
+    "smoe_scatter2scatter_to_peers": ([_P, _I64, _I64, _I64, _P, _I64, _I64, _I64, _P, _P, _P, _I64, _I64, _I32, _I32,
+                                       _I32, _I32, _I32, _I32, _I32, _P, _P], c_int32),
     "smoe_ep_barrier": ([_P, _I32, _I32, _I32, _I64, _P, _P], c_int32),
     "smoe_ep_tokmeta_ints": ([_I32], c_int32),
     "smoe_ep_plan_tokens": ([_P, _P, _I64, _I32, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I32, _I32, _I32, _I32,

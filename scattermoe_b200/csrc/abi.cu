@@ -197,6 +197,36 @@ extern "C" int smoe_scatter2scatter_act_bwd(const void* DY, int64_t stride_dym, 
   return rc;
 }
 
+// Grouped GEMM whose epilogue returns the rows to their home ranks (the expert-parallel return direction, fused):
+// what smoe_scatter2scatter (grouped in, grouped out) followed by smoe_ep_return does, without the intermediate
+// result buffer and with the NVLink transfer overlapped tile by tile with the tensor-core work. Returns
+// SMOE_ERR_UNSUPPORTED (no error text) when the request does not fit the tensor-core kernel: the caller then runs
+// the two separate calls.
+extern "C" int smoe_scatter2scatter_to_peers(const void* X, int64_t x_rows, int64_t stride_xm, int64_t stride_xk,
+                                             const void* W, int64_t stride_we, int64_t stride_wk, int64_t stride_wn,
+                                             const int64_t* expert_offsets, const int64_t* return_addr,
+                                             void* const* peer_slot_bufs, int64_t peer_stride_rows, int64_t peer_rows,
+                                             int32_t world, int32_t my_rank, int32_t K, int32_t N, int32_t E,
+                                             int32_t dtype, int32_t flags, int32_t* status, void* stream) {
+  if (int rc = check_dtype("scatter2scatter_to_peers", dtype)) return rc;
+  SMOE_CHECK_ARG(x_rows >= 0 && x_rows < (int64_t(1) << 31), "scatter2scatter_to_peers: %lld rows out of range",
+                 (long long)x_rows);
+  SMOE_CHECK_ARG(K >= 0 && N >= 0 && E >= 1, "scatter2scatter_to_peers: bad sizes K=%d N=%d E=%d", K, N, E);
+  SMOE_CHECK_ARG(world >= 1 && my_rank >= 0 && my_rank < world, "scatter2scatter_to_peers: rank %d of %d", my_rank, world);
+  SMOE_CHECK_ARG(peer_rows >= 0 && peer_rows < (int64_t(1) << 40), "scatter2scatter_to_peers: peer buffer too large");
+  if (x_rows == 0 || N == 0) return SMOE_OK;
+  SMOE_CHECK_ARG(X && W && expert_offsets && return_addr && peer_slot_bufs, "scatter2scatter_to_peers: null pointer");
+  if (flags & SMOE_FLAG_FORCE_SIMT) return SMOE_ERR_UNSUPPORTED;
+  S2SArgs a{X, x_rows, stride_xm, stride_xk, W, stride_we, stride_wk, stride_wn, nullptr, 0, 0,
+            nullptr, 0, 1, expert_offsets, expert_offsets, expert_offsets,
+            x_rows, K, N, E, 1, 1, 1, dtype, flags, status, static_cast<cudaStream_t>(stream)};
+  a.out_addr = return_addr; a.out_peers = peer_slot_bufs; a.out_peer_stride = peer_stride_rows;
+  a.out_peer_rows = peer_rows; a.out_world = world; a.my_rank = my_rank;
+  const int rc = launch_s2s_tc(a);
+  if (rc == SMOE_OK) set_last_path(1);
+  return rc;
+}
+
 // Lines of fp32 partial sums (each R long) that smoe_scatter2scatter_act_bwd writes per row when it is given gates:
 // two per 256-wide tile of hidden columns (one per group of epilogue warps).
 extern "C" int32_t smoe_act_bwd_partial_lines(int32_t F) { return F > 0 ? 2 * ((F + 255) / 256) : 0; }

@@ -24,6 +24,7 @@
 
 #include "act_math.cuh"
 #include "ptx.cuh"
+#include "ep_common.cuh"
 #include "smoe_common.cuh"
 
 namespace smoe {
@@ -76,6 +77,14 @@ struct S2SParams {
   const uint8_t* row_gate;
   float* dot_out; int64_t dot_stride;
   int group_m;         // m-tiles per raster group (see decode_tile)
+  // Expert-parallel return fused into the epilogue (plain launches only; out_addr nullable). Output row m is not
+  // stored to Y but straight into another rank's memory over NVLink: out_addr[m] packs (rank, row) as in
+  // ep_common.cuh, the row lands in out_peer.p[rank] + row * out_peer_row_bytes. Each rank also starts the m-tiles
+  // of every expert m_rot_num / m_rot_den of the way in and wraps, so that the ranks address different receivers
+  // at any moment (the rows of an expert are ordered by the rank they return to).
+  const int64_t* out_addr; int64_t out_peer_row_bytes, out_peer_rows;
+  int out_world, m_rot_num, m_rot_den;
+  PeerPtrs out_peer;
   uint32_t idesc;
   int32_t* status;
 };
@@ -123,7 +132,7 @@ struct Tile { int e, m0, rows, n0; };
 // m-tiles x a few columns: with group_m chosen so that both footprints are alike, the operands a wave streams
 // from HBM (rows x K of A plus columns x K of W) are at their minimum for the number of tiles in flight.
 __device__ __forceinline__ Tile decode_tile(int t, const int32_t* tile_prefix, const int32_t* seg_start, int E, int BN,
-                                            int group_m) {
+                                            int group_m, int rot_num = 0, int rot_den = 1) {
   constexpr int mtile_rows = BM;
   int lo = 0, hi = E;
   while (hi - lo > 1) {
@@ -142,7 +151,11 @@ __device__ __forceinline__ Tile decode_tile(int t, const int32_t* tile_prefix, c
   const int in_grp = local - grp * per_group;
   const int gw = min(gm, m_tiles - grp * gm);
   const int n_tile = in_grp / gw;
-  const int m_tile = grp * gm + (in_grp - n_tile * gw);
+  int m_tile = grp * gm + (in_grp - n_tile * gw);
+  if (rot_num > 0) {          // rotated start (rot_num < rot_den): see S2SParams::out_addr
+    m_tile += static_cast<int>(static_cast<int64_t>(m_tiles) * rot_num / rot_den);
+    if (m_tile >= m_tiles) m_tile -= m_tiles;
+  }
   tl.m0 = seg_start[lo] + m_tile * mtile_rows;
   tl.rows = min(mtile_rows, seg_start[lo + 1] - tl.m0);
   tl.n0 = n_tile * BN;
@@ -516,7 +529,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, p.group_m);
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, p.group_m, p.m_rot_num, p.m_rot_den);
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         const int s = it % STAGES;
         const uint32_t ph = (it / STAGES) & 1;
@@ -592,7 +605,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     int it = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, p.group_m);
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, p.group_m, p.m_rot_num, p.m_rot_den);
       const uint8_t* rowptr[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -641,7 +654,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     int tile_iter = 0;
     bool ok = true;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
-      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, p.group_m);
+      const Tile tl = decode_tile(t, tile_prefix, seg_start, p.E, TN, p.group_m, p.m_rot_num, p.m_rot_den);
       const int buf = tile_iter & 1;
       const uint32_t tph = (tile_iter >> 1) & 1;
       bool valid = r < tl.rows;
@@ -652,6 +665,17 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         valid = out_row >= 0 && out_row < p.R;
       }
       uint8_t* yrow = p.Y + out_row * p.y_row_bytes;
+      if (EPI == EPI_NONE && p.out_addr != nullptr) {
+        // the row's home is on another rank (or this one): a malformed return address drops the row
+        yrow = nullptr;
+        if (valid) {
+          const int64_t d = p.out_addr[tl.m0 + r];
+          const int rk = dest_rank(d);
+          const int64_t s = dest_row(d);
+          valid = rk >= 0 && rk < p.out_world && s < p.out_peer_rows;
+          if (valid) yrow = p.out_peer.p[rk] + s * p.out_peer_row_bytes;
+        }
+      }
       const uint8_t* brow = p.bias ? p.bias + static_cast<int64_t>(tl.e) * p.bias_row_elems * 2 : nullptr;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
       uint8_t* slab = epi_staging + (group * 4 + q) * (32 * C::STAGE_ROW_BYTES);
@@ -1236,7 +1260,11 @@ int launch_s2s_tc(const S2SArgs& a) {
   if (a.dtype != SMOE_BF16 && a.dtype != SMOE_F16) return SMOE_ERR_UNSUPPORTED;
   if (a.K < 8 || a.K % 8 || a.N % 8 || a.E > MAX_E) return SMOE_ERR_UNSUPPORTED;
   if (a.sxk != 1 || a.sxm % 8 || !al16(a.X)) return SMOE_ERR_UNSUPPORTED;
-  if (a.syn != 1 || a.sym % 8 || !al16(a.Y)) return SMOE_ERR_UNSUPPORTED;
+  const bool to_peers = a.out_addr != nullptr;
+  if (!to_peers && (a.syn != 1 || a.sym % 8 || !al16(a.Y))) return SMOE_ERR_UNSUPPORTED;
+  if (to_peers && (a.act_layout >= 0 || a.act_bwd || a.bias || a.out_peers == nullptr || a.out_peer_stride % 8 ||
+                   a.out_peer_stride < a.N || a.out_world < 1 || a.out_world > EP_MAX_WORLD))
+    return SMOE_ERR_UNSUPPORTED;
   if (a.bias && a.sbn != 1) return SMOE_ERR_UNSUPPORTED;
   if (!al16(a.W) || a.swe % 8 || a.swe < 0) return SMOE_ERR_UNSUPPORTED;
   const bool k_major = (a.swk == 1 && a.swn % 8 == 0 && a.swn >= a.K);
@@ -1289,6 +1317,17 @@ int launch_s2s_tc(const S2SArgs& a) {
   p.U = static_cast<const uint8_t*>(a.U); p.u_row_bytes = a.sum * 2;
   p.row_gate = static_cast<const uint8_t*>(a.row_gate);
   p.dot_out = a.dot_out; p.dot_stride = a.R;
+  p.out_addr = a.out_addr; p.out_peer_row_bytes = a.out_peer_stride * 2; p.out_peer_rows = a.out_peer_rows;
+  p.out_world = a.out_world; p.m_rot_num = 0; p.m_rot_den = 1;
+  for (int i = 0; i < EP_MAX_WORLD; ++i) p.out_peer.p[i] = nullptr;
+  if (to_peers) {
+    for (int i = 0; i < a.out_world; ++i) {
+      p.out_peer.p[i] = static_cast<uint8_t*>(a.out_peers[i]);
+      if (p.out_peer.p[i] == nullptr || !al16(p.out_peer.p[i])) return SMOE_ERR_UNSUPPORTED;
+    }
+    p.Y = nullptr; p.y_row_bytes = 0;
+    if (a.my_rank > 0 && a.my_rank < a.out_world) { p.m_rot_num = a.my_rank; p.m_rot_den = a.out_world; }
+  }
   // Raster (see decode_tile). While one expert's A panel (its rows x K) fits comfortably in L2, every m-tile of the
   // expert runs beside each column tile, so each weight tile is fetched from HBM once and the A panel comes from L2.
   // When the panel does not fit, both operands stream from HBM for every wave of tiles in flight and the wave is

@@ -81,6 +81,12 @@ struct S2SArgs {
   // per-slot gates for the fused epilogues (nullable) and the gate gradient's partial sums (act_bwd only, nullable)
   const void* row_gate = nullptr;
   float* dot_out = nullptr;
+  // expert-parallel return fused into the epilogue (tensor-core kernel, plain launches only): output row m goes to
+  // out_peers[rank] at the row packed in out_addr[m] instead of Y
+  const int64_t* out_addr = nullptr;
+  void* const* out_peers = nullptr;
+  int64_t out_peer_stride = 0, out_peer_rows = 0;
+  int out_world = 0, my_rank = 0;
 };
 
 struct WGradArgs {

@@ -301,6 +301,11 @@ class PeerTokenBuffers(PeerBuffers):
 # their step then yields NaNs and sets the status word, it does not hang and it does not return plausible numbers.
 BARRIER_LIMIT_CYCLES = 0
 
+# Per-slot exchange: the two GEMMs whose results travel home (down-projection in forward, input gradient of the
+# up-projection in backward) store them into the home ranks' buffers from their own epilogues. False: separate push
+# kernels after the GEMMs (the two forms give bit-identical results).
+FUSE_RETURN = True
+
 
 def _ep_call(name, *args):
     from . import _lib
@@ -359,13 +364,18 @@ class _PeerExchangeMLP(torch.autograd.Function):
                        rows_dev)
         else:
             up, hidden = fused
-        y_rows = ops.scatter2scatter(hidden, w_down.permute(0, 2, 1), dummy, dummy, 1, x_grouped=True, y_grouped=True,
-                                     expert_offsets=local_offsets)
-        # 5. results go home: one row per (token, slot) into the token owner's slot-ordered buffer
-        with torch.cuda.device(dev):
-            _ep_call("smoe_ep_return", y_rows.data_ptr(), y_rows.stride(0), bufs.local["ret"].data_ptr(),
-                     rows_dev.data_ptr(), cap, bufs.ptrs["yslot"], bufs.width, bufs.slot_rows, d, W, rank, e_local, code,
-                     stream)
+        # 5. down-projection; results go home, one row per (token, slot) into the token owner's slot-ordered buffer:
+        # stored there by the GEMM's own epilogue as each tile finishes (the rows cross NVLink under the tensor-core
+        # work on the next tiles) or, where the tensor-core kernel does not apply, by a push kernel after the GEMM
+        if not (FUSE_RETURN and ops.scatter2scatter_to_peers(hidden, w_down.permute(0, 2, 1), local_offsets,
+                                                             bufs.local["ret"], bufs.ptrs["yslot"], bufs.width,
+                                                             bufs.slot_rows, rank, W)):
+            y_rows = ops.scatter2scatter(hidden, w_down.permute(0, 2, 1), dummy, dummy, 1, x_grouped=True,
+                                         y_grouped=True, expert_offsets=local_offsets)
+            with torch.cuda.device(dev):
+                _ep_call("smoe_ep_return", y_rows.data_ptr(), y_rows.stride(0), bufs.local["ret"].data_ptr(),
+                         rows_dev.data_ptr(), cap, bufs.ptrs["yslot"], bufs.width, bufs.slot_rows, d, W, rank, e_local,
+                         code, stream)
         bufs.barrier()
         out = ops.topk_reduce(bufs.local["yslot"], gates, T, k)
         bufs.poison_if_a_wait_expired(out)
@@ -404,12 +414,14 @@ class _PeerExchangeMLP(torch.autograd.Function):
         # (input gradient of the down-projection and the activation gradient in one launch where the tensor-core
         # kernel applies; only the live rows, which the expert offsets delimit, are read or written)
         d_up = ops.scatter2scatter_act_bwd(gb, w_down, up, local_offsets, _act.LAYOUT_GLU_SECOND, layer.act_code)
-        dx_rows = ops.scatter2scatter(d_up, w_up, dummy, dummy, 1, x_grouped=True, y_grouped=True,
-                                      expert_offsets=local_offsets)
-        with torch.cuda.device(dev):
-            _ep_call("smoe_ep_return", dx_rows.data_ptr(), dx_rows.stride(0), bufs.local["ret"].data_ptr(),
-                     rows_dev.data_ptr(), cap, bufs.ptrs["dxslot"], bufs.width, bufs.slot_rows, d, W, rank, e_local, code,
-                     stream)
+        if not (FUSE_RETURN and ops.scatter2scatter_to_peers(d_up, w_up, local_offsets, bufs.local["ret"],
+                                                             bufs.ptrs["dxslot"], bufs.width, bufs.slot_rows, rank, W)):
+            dx_rows = ops.scatter2scatter(d_up, w_up, dummy, dummy, 1, x_grouped=True, y_grouped=True,
+                                          expert_offsets=local_offsets)
+            with torch.cuda.device(dev):
+                _ep_call("smoe_ep_return", dx_rows.data_ptr(), dx_rows.stride(0), bufs.local["ret"].data_ptr(),
+                         rows_dev.data_ptr(), cap, bufs.ptrs["dxslot"], bufs.width, bufs.slot_rows, d, W, rank, e_local,
+                         code, stream)
         # ... while the two weight gradients run: the barrier that follows them finds the peers' rows already here
         d_w_down, _ = ops.group_bwd_W(gb, hidden, local_offsets, e_local)
         d_w_up, _ = ops.group_bwd_W(d_up, xb, local_offsets, e_local)

@@ -334,6 +334,33 @@ def scatter2scatter_act_bwd(DY, W, up, expert_offsets, act_layout, act, alpha=1.
     return d_up if row_gates is None else (d_up, d_gates)
 
 
+def scatter2scatter_to_peers(X, W, expert_offsets, return_addr, peer_ptrs, peer_stride_rows, peer_rows, rank,
+                             world) -> bool:
+    """Grouped GEMM of the local experts whose epilogue stores every result row straight into its home rank's buffer
+    over NVLink (expert parallelism, the return direction): `scatter2scatter(X, W, ..., x_grouped=True,
+    y_grouped=True)` followed by `smoe_ep_return`, as one tensor-core launch without the local result buffer. X is the
+    owner's expert-grouped (capacity, K) buffer, W (E_local, K, N), `return_addr` the (capacity,) int64 (rank, row)
+    records written by `smoe_ep_dispatch`, `peer_ptrs` the ctypes table of the ranks' (peer_rows, peer_stride_rows)
+    buffers. False: the request does not fit the tensor-core kernel and nothing was launched (the caller runs the two
+    separate calls). No counterpart in the reference, which has no multi-GPU code."""
+    _lib.require_cuda(X, "X")
+    if FORCE_PATH == "simt" or X.dtype not in (torch.bfloat16, torch.float16) or W.dtype != X.dtype:
+        return False
+    off, ret = _i64(expert_offsets), _i64(return_addr)
+    if ret.numel() < X.size(0):
+        raise AssertionError("return_addr has %d entries for %d rows" % (ret.numel(), X.size(0)))
+    with torch.cuda.device(X.device):
+        rc = _lib.load().smoe_scatter2scatter_to_peers(
+            X.data_ptr(), X.size(0), X.stride(0), X.stride(1), W.data_ptr(), W.stride(0), W.stride(1), W.stride(2),
+            off.data_ptr(), ret.data_ptr(), peer_ptrs, int(peer_stride_rows), int(peer_rows), int(world), int(rank),
+            X.size(1), W.size(-1), W.size(0), _dtype_code(X), _flags(), _lib.status_word(X.device).data_ptr(),
+            _lib.stream_ptr(X.device))
+    if rc == _lib.SMOE_ERR_UNSUPPORTED:
+        return False
+    _lib.check(rc, "smoe_scatter2scatter_to_peers")
+    return True
+
+
 # --------------------------------------------------------------------------------------------------
 # group_bwd_W
 # --------------------------------------------------------------------------------------------------

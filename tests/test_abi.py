@@ -30,7 +30,7 @@ def test_header_symbols_are_exported_and_bound():
 
 
 def test_version_and_library_location():
-    assert _lib.load().smoe_version() == _lib.ABI_VERSION == 3
+    assert _lib.load().smoe_version() == _lib.ABI_VERSION == 4
     path = scattermoe_b200.library_path()
     assert os.path.dirname(path) == os.path.join(ROOT, "scattermoe_b200"), "the library must live in-tree"
 

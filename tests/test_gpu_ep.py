@@ -156,3 +156,54 @@ def test_barrier_that_nobody_answers_gives_up_and_is_loud():
     with torch.cuda.device(dev):
         assert lib.smoe_ep_barrier(one, 0, 1, 2, 0, status.data_ptr(), _lib.stream_ptr(dev)) == 0
     sm.check_device_status(dev)
+
+
+@pytest.mark.parametrize("rank", [0, 2])
+@pytest.mark.parametrize("K,N", [(128, 256), (256, 512), (64, 136)])
+def test_gemm_that_returns_its_rows_equals_gemm_then_push(rank, K, N):
+    """`smoe_scatter2scatter_to_peers` against `smoe_scatter2scatter` + `smoe_ep_return` on the same inputs, bit for
+    bit. One GPU plays the owner; the four "ranks" its rows return to are four buffers of this GPU (a peer pointer is
+    just an address). Ragged local experts (one empty, one larger than a tile), a buffer larger than its live rows,
+    and two malformed return addresses, whose rows must be dropped by both forms."""
+    import ctypes
+    from scattermoe_b200 import _lib
+    from scattermoe_b200.kernels import ops
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(100 + K + rank)
+    world, slot_rows, cap = 4, 700, 1024
+    counts = torch.tensor([130, 0, 301, 57, 200])
+    live, E = int(counts.sum()), counts.numel()
+    offsets = counts.cumsum(0).to(dev)
+    X = torch.randn(cap, K, generator=g).to(torch.bfloat16).to(dev)
+    W = (torch.randn(E, K, N, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+    # every live row has its own (rank, slot) home
+    homes = torch.randperm(world * slot_rows, generator=g)[:live]
+    ret = torch.full((cap,), -1, dtype=torch.int64)
+    ret[:live] = ((homes // slot_rows) << 40) | (homes % slot_rows)
+    ret[5] = (7 << 40) | 3                      # rank outside the world
+    ret[140] = (1 << 40) | (slot_rows + 9)      # row outside the peer buffer
+    ret = ret.to(dev)
+    dummy = torch.zeros(cap, dtype=torch.int64, device=dev)
+
+    def buffers():
+        b = [torch.full((slot_rows, N), -7.0, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+        return b, (ctypes.c_void_p * world)(*[t.data_ptr() for t in b])
+
+    two, two_ptrs = buffers()
+    y = ops.scatter2scatter(X, W, dummy, dummy, 1, x_grouped=True, y_grouped=True, expert_offsets=offsets)
+    rows_dev = offsets[-1:].contiguous()
+    with torch.cuda.device(dev):
+        rc = _lib.load().smoe_ep_return(y.data_ptr(), y.stride(0), ret.data_ptr(), rows_dev.data_ptr(), cap, two_ptrs, N,
+                                        slot_rows, N, world, rank, E, _lib.DTYPE_CODE[torch.bfloat16], _lib.stream_ptr(dev))
+    assert rc == 0, _lib.last_error()
+    one, one_ptrs = buffers()
+    fits = K % 8 == 0 and N % 8 == 0
+    assert ops.scatter2scatter_to_peers(X, W, offsets, ret, one_ptrs, N, slot_rows, rank, world) == fits
+    torch.cuda.synchronize()
+    import scattermoe_b200 as sm
+    sm.check_device_status(dev)
+    written = 0
+    for a, b in zip(one, two):
+        assert torch.equal(a, b)
+        written += int((b != -7.0).any(1).sum())
+    assert written == live - 2
