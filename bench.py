@@ -723,11 +723,17 @@ def measure(name, c, device, rank, world, dist, steps, warmup, with_e2e=True, sa
             staged["ready"] = torch.cuda.Event()
             staged["ready"].record(copy_stream)
 
+    pending = []      # (y, dx, copied event) of the steps whose results may still be travelling to the host
+
     def e2e_step(prefetch):
         # Every step copies its own inputs from pinned host memory and its results back. The copies run on two
         # streams of their own: the next step's inputs are enqueued while this step computes, and this step's
         # results travel back while the next step computes.
         cur = torch.cuda.current_stream(device)
+        # results older than the previous step's: their copies ended long ago; after this wait their memory may be
+        # reused by what this step enqueues (the tensors are allocated on `cur`, only read on `back_stream`)
+        while len(pending) > 1:
+            cur.wait_event(pending.pop(0)[2])
         cur.wait_event(staged["ready"])
         ins = staged.pop("in")
         for t in ins.values():
@@ -738,12 +744,13 @@ def measure(name, c, device, rank, world, dist, steps, warmup, with_e2e=True, sa
         dx = grads[0]
         done = torch.cuda.Event()
         done.record(cur)
+        copied = torch.cuda.Event()
         with torch.cuda.stream(back_stream):
             back_stream.wait_event(done)
-            y.record_stream(back_stream)
-            dx.record_stream(back_stream)
             out_host["y"].copy_(y, non_blocking=True)
             out_host["dx"].copy_(dx, non_blocking=True)
+            copied.record(back_stream)
+        pending.append((y, dx, copied))
 
     def e2e_loop(n):
         # Nothing is staged before the loop starts (the first step's host->device copy is not hidden) and the
@@ -754,6 +761,7 @@ def measure(name, c, device, rank, world, dist, steps, warmup, with_e2e=True, sa
             e2e_step(prefetch=(i + 1 < n))
         torch.cuda.current_stream(device).wait_stream(copy_stream)
         torch.cuda.current_stream(device).wait_stream(back_stream)
+        pending.clear()
 
     def timed(fn, n):
         barrier()
@@ -840,7 +848,7 @@ def measure(name, c, device, rank, world, dist, steps, warmup, with_e2e=True, sa
 
     ms_e2e = None
     if with_e2e:
-        e2e_loop(2)
+        e2e_loop(4)          # the caching allocator reaches its steady state (no cudaMalloc inside the timed loop)
         ms_e2e = timed(e2e_loop, steps)
     sm.check_device_status(device)
 
