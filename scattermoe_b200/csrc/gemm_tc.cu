@@ -84,6 +84,7 @@ struct S2SParams {
   // at any moment (the rows of an expert are ordered by the rank they return to).
   const int64_t* out_addr; int64_t out_peer_row_bytes, out_peer_rows;
   int out_world, m_rot_num, m_rot_den;
+  int out_pieces;      // 16-byte pieces of a row per store instruction of that epilogue: 8, 16, or 4 (the plain epilogue)
   PeerPtrs out_peer;
   uint32_t idesc;
   int32_t* status;
@@ -167,8 +168,9 @@ __device__ __forceinline__ Tile decode_tile(int t, const int32_t* tile_prefix, c
 // EPI_BWD_*: the GEMM's result is the gradient of the hidden activations (N = F columns); the epilogue turns it into
 // the gradient of the saved up-projection U and stores that, (rows, n_up), instead: the hidden gradient never
 // reaches memory (4 plain, 5 gated halves, 6 gpt-oss interleaved).
+// EPI_PEERS: plain linear whose rows are stored into other ranks' memory (S2SParams::out_addr).
 enum { EPI_NONE = 0, EPI_ACT = 1, EPI_GLU_HALVES = 2, EPI_GPT_OSS = 3, EPI_BWD_PLAIN = 4, EPI_BWD_GLU = 5,
-       EPI_BWD_GPT_OSS = 6 };
+       EPI_BWD_GPT_OSS = 6, EPI_PEERS = 7 };
 
 __device__ __forceinline__ void add_bias8(const uint8_t* brow, int col, int is_bf16, int bias_vec, float (&v)[8]) {
   if (!brow) return;
@@ -235,6 +237,69 @@ __device__ __forceinline__ void flush_rows(uint8_t* slab, int lane, const uint4 
     if (ok && col < col_limit) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(ptr) + col * 2) = v;
   }
   __syncwarp();
+}
+
+// flush_rows for rows that leave this GPU: lane l holds NP 16-byte pieces (NP * 8 columns from `col0`) of ITS row.
+// The rows pass through the same slab RP at a time (RP rows x (NP * 16 + 16) bytes fit the warp's 32 x 80 bytes), so that
+// every store instruction writes 32 / NP rows x NP * 16 CONTIGUOUS bytes: whole 128-byte lines per row instead of the
+// half lines of flush_rows<4>. Local stores do not care (L2 merges them); over NVLink a partial line costs a packet of
+// its own.
+template <int NP>
+__device__ __forceinline__ void flush_rows_wide(uint8_t* slab, int lane, const uint4 (&mine)[NP], uint8_t* rowptr,
+                                                bool valid, int col0, int col_limit) {
+  constexpr int ROW = NP * 16 + 16;
+  constexpr int RP = (NP == 8) ? 16 : 8;                 // rows per pass
+  static_assert(RP * ROW <= 32 * 80, "the pass does not fit the warp's staging slab");
+  constexpr int ROWS_PER_STORE = 32 / NP;
+  const unsigned long long mine_ptr = reinterpret_cast<unsigned long long>(rowptr);
+#pragma unroll
+  for (int pass = 0; pass < 32 / RP; ++pass) {
+    if (lane / RP == pass) {
+#pragma unroll
+      for (int g = 0; g < NP; ++g) *reinterpret_cast<uint4*>(slab + (lane % RP) * ROW + g * 16) = mine[g];
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < RP / ROWS_PER_STORE; ++i) {
+      const int row = i * ROWS_PER_STORE + lane / NP;      // row of this pass
+      const int ck = lane % NP;
+      const uint4 v = *reinterpret_cast<const uint4*>(slab + row * ROW + ck * 16);
+      const unsigned long long ptr = __shfl_sync(0xffffffffu, mine_ptr, pass * RP + row);
+      const int ok = __shfl_sync(0xffffffffu, valid ? 1 : 0, pass * RP + row);
+      const int col = col0 + ck * 8;
+      if (ok && col < col_limit) *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(ptr) + col * 2) = v;
+    }
+    __syncwarp();
+  }
+}
+
+// Plain epilogue of a launch whose rows return to their home ranks (S2SParams::out_addr): NP * 8 accumulator columns
+// at a time (64: each row travels in whole 128-byte lines; 128: in pairs of lines). The two groups of epilogue warps
+// take every other unit.
+template <int BN, int NP>
+__device__ __forceinline__ void epilogue_rows_to_peers(const S2SParams& p, int n0, uint32_t taddr, uint8_t* slab, int lane,
+                                                       bool valid, uint8_t* yrow, int u_first, int u_step) {
+  constexpr int UNIT = NP * 8;
+#pragma unroll 1
+  for (int u = u_first; u < BN / UNIT; u += u_step) {
+    const int n = n0 + u * UNIT;
+    if (n >= p.N) break;
+    uint4 py[NP];
+#pragma unroll
+    for (int h = 0; h < NP / 4; ++h) {
+      uint32_t acc[32];
+      tmem_ld_32x32b_x32(taddr + u * UNIT + h * 32, acc);
+      tmem_ld_wait();
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        float v[8];
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) v[jj] = __uint_as_float(acc[g * 8 + jj]);
+        py[h * 4 + g] = pack8(v, p.is_bf16);
+      }
+    }
+    flush_rows_wide<NP>(slab, lane, py, yrow, valid, n, p.N);
+  }
 }
 
 // Epilogue of one tile for one warp: lane l owns accumulator row (TMEM lane) l of the warp's quarter. Reads the BN
@@ -665,7 +730,7 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         valid = out_row >= 0 && out_row < p.R;
       }
       uint8_t* yrow = p.Y + out_row * p.y_row_bytes;
-      if (EPI == EPI_NONE && p.out_addr != nullptr) {
+      if (EPI == EPI_PEERS) {
         // the row's home is on another rank (or this one): a malformed return address drops the row
         yrow = nullptr;
         if (valid) {
@@ -681,14 +746,14 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
       uint8_t* slab = epi_staging + (group * 4 + q) * (32 * C::STAGE_ROW_BYTES);
       auto wait_acc = [&]() { return mbar_wait_warp(tfull_bar(buf), tph, abort_flag, p.status, 5); };
       float rg = 1.0f;                     // the row's gate, where the launch carries gates
-      if (EPI != EPI_NONE && p.row_gate != nullptr && valid) {
+      if (EPI != EPI_NONE && EPI != EPI_PEERS && p.row_gate != nullptr && valid) {
         const int64_t slot = p.sorted_idx[tl.m0 + r];
         if (slot >= 0 && slot < p.R) {
           const uint16_t raw = __ldg(reinterpret_cast<const uint16_t*>(p.row_gate) + slot);
           rg = p.is_bf16 ? __bfloat162float(__ushort_as_bfloat16(raw)) : __half2float(__ushort_as_half(raw));
         }
       }
-      if constexpr (EPI >= EPI_BWD_PLAIN) {
+      if constexpr (EPI >= EPI_BWD_PLAIN && EPI <= EPI_BWD_GPT_OSS) {
         // (the first pieces of the saved up-projection are requested before the wait for the accumulator)
         float dot = 0.f;
         if (!epilogue_act_bwd<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, p.U + out_row * p.u_row_bytes, group,
@@ -701,8 +766,17 @@ s2s_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
       } else {
         if (!wait_acc()) { ok = false; break; }
         tc_fence_after_sync();
-        uint8_t* hrow = (EPI != EPI_NONE) ? p.H + out_row * p.h_row_bytes : nullptr;
-        epilogue_rows<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, hrow, brow, group, c_step, rg);
+        if constexpr (EPI == EPI_PEERS) {
+          if (p.out_pieces == 16)
+            epilogue_rows_to_peers<BN, 16>(p, tl.n0, taddr, slab, lane, valid, yrow, group, c_step);
+          else if (p.out_pieces == 8)
+            epilogue_rows_to_peers<BN, 8>(p, tl.n0, taddr, slab, lane, valid, yrow, group, c_step);
+          else
+            epilogue_rows<BN, EPI_NONE>(p, tl.n0, taddr, slab, lane, valid, yrow, nullptr, nullptr, group, c_step, 1.0f);
+        } else {
+          uint8_t* hrow = (EPI != EPI_NONE) ? p.H + out_row * p.h_row_bytes : nullptr;
+          epilogue_rows<BN, EPI>(p, tl.n0, taddr, slab, lane, valid, yrow, hrow, brow, group, c_step, rg);
+        }
       }
       tc_fence_before_sync();
       mbar_arrive(tempty_bar(buf));
@@ -1262,7 +1336,7 @@ int launch_s2s_tc(const S2SArgs& a) {
   if (a.sxk != 1 || a.sxm % 8 || !al16(a.X)) return SMOE_ERR_UNSUPPORTED;
   const bool to_peers = a.out_addr != nullptr;
   if (!to_peers && (a.syn != 1 || a.sym % 8 || !al16(a.Y))) return SMOE_ERR_UNSUPPORTED;
-  if (to_peers && (a.act_layout >= 0 || a.act_bwd || a.bias || a.out_peers == nullptr || a.out_peer_stride % 8 ||
+  if (to_peers && (a.act_layout >= 0 || a.act_bwd || a.bias || a.N <= 128 || a.out_peers == nullptr || a.out_peer_stride % 8 ||
                    a.out_peer_stride < a.N || a.out_world < 1 || a.out_world > EP_MAX_WORLD))
     return SMOE_ERR_UNSUPPORTED;
   if (a.bias && a.sbn != 1) return SMOE_ERR_UNSUPPORTED;
@@ -1291,6 +1365,7 @@ int launch_s2s_tc(const S2SArgs& a) {
     epi = a.act_layout == LAYOUT_PLAIN ? EPI_BWD_PLAIN : (a.act_layout == LAYOUT_GPT_OSS ? EPI_BWD_GPT_OSS : EPI_BWD_GLU);
     F = a.N;
   }
+  if (to_peers) epi = EPI_PEERS;
   const int BN = a.N > 128 ? 256 : 128;
   CUtensorMap map;
   const uint64_t e_stride = (a.E > 1 ? static_cast<uint64_t>(a.swe) : static_cast<uint64_t>(a.K) * a.N) * 2;
@@ -1319,6 +1394,8 @@ int launch_s2s_tc(const S2SArgs& a) {
   p.dot_out = a.dot_out; p.dot_stride = a.R;
   p.out_addr = a.out_addr; p.out_peer_row_bytes = a.out_peer_stride * 2; p.out_peer_rows = a.out_peer_rows;
   p.out_world = a.out_world; p.m_rot_num = 0; p.m_rot_den = 1;
+  const int peer_store_bytes = to_peers ? env_int("SMOE_PEER_STORE_BYTES", 128) : 0;    // read per launch: a test hook
+  p.out_pieces = peer_store_bytes >= 256 ? 16 : (peer_store_bytes >= 128 ? 8 : 4);
   for (int i = 0; i < EP_MAX_WORLD; ++i) p.out_peer.p[i] = nullptr;
   if (to_peers) {
     for (int i = 0; i < a.out_world; ++i) {
@@ -1363,6 +1440,9 @@ int launch_s2s_tc(const S2SArgs& a) {
     case EPI_BWD_GPT_OSS:
       return k_major ? launch_s2s_cfg<256, true, EPI_BWD_GPT_OSS>(map, map_x, p, grid, a.stream)
                      : launch_s2s_cfg<256, false, EPI_BWD_GPT_OSS>(map, map_x, p, grid, a.stream);
+    case EPI_PEERS:
+      return k_major ? launch_s2s_cfg<256, true, EPI_PEERS>(map, map_x, p, grid, a.stream)
+                     : launch_s2s_cfg<256, false, EPI_PEERS>(map, map_x, p, grid, a.stream);
     default: break;
   }
   if (BN == 256)

@@ -158,16 +158,20 @@ def test_barrier_that_nobody_answers_gives_up_and_is_loud():
     sm.check_device_status(dev)
 
 
+@pytest.mark.parametrize("store_bytes", [64, 128, 256])
 @pytest.mark.parametrize("rank", [0, 2])
 @pytest.mark.parametrize("K,N", [(128, 256), (256, 512), (64, 136)])
-def test_gemm_that_returns_its_rows_equals_gemm_then_push(rank, K, N):
+def test_gemm_that_returns_its_rows_equals_gemm_then_push(rank, K, N, store_bytes, monkeypatch):
     """`smoe_scatter2scatter_to_peers` against `smoe_scatter2scatter` + `smoe_ep_return` on the same inputs, bit for
     bit. One GPU plays the owner; the four "ranks" its rows return to are four buffers of this GPU (a peer pointer is
     just an address). Ragged local experts (one empty, one larger than a tile), a buffer larger than its live rows,
-    and two malformed return addresses, whose rows must be dropped by both forms."""
+    and two malformed return addresses, whose rows must be dropped by both forms. All three store widths of the
+    epilogue."""
     import ctypes
     from scattermoe_b200 import _lib
     from scattermoe_b200.kernels import ops
+    # contiguous bytes of a row per store instruction of the epilogue (the library reads this at every launch)
+    monkeypatch.setenv("SMOE_PEER_STORE_BYTES", str(store_bytes))
     dev = torch.device("cuda", 0)
     g = torch.Generator().manual_seed(100 + K + rank)
     world, slot_rows, cap = 4, 700, 1024
