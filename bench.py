@@ -926,7 +926,7 @@ def main():
                     help="pipeline chunks of the NVLink exchange (each chunk's transfers overlap the other's GEMMs)")
     ap.add_argument("--once-per-rank", choices=("auto", "on", "off"), default="auto",
                     help="NVLink exchange: send each token once per owning rank instead of once per slot (auto: when "
-                         "that saves at least 30 % of the rows)")
+                         "that saves at least 70 % of the rows)")
     ap.add_argument("--separate-return", action="store_true",
                     help="per-slot NVLink exchange: return rows with a push kernel after the GEMM instead of from the "
                          "GEMM's own epilogue")

@@ -654,13 +654,15 @@ class PeerExpertParallelGLUMLP(ExpertParallelGLUMLP):
                  capacity_rows=None, global_tokens=None, chunks=1, once_per_rank=None):
         super().__init__(input_size, hidden_size, num_experts, top_k, group=group, activation=activation)
         # once_per_rank: send every token row once per owning rank (csrc/ep_dedup.cu) instead of once per slot.
-        # Default: when that saves at least 30 % of the rows (below that, the extra passes over local HBM cost what the
-        # smaller transfers save). With uniform routing a token's top_k slots fall on about
+        # Default: when that saves at least 70 % of the rows. The per-slot exchange returns its rows from the epilogue
+        # of the GEMM that makes them (hidden under the tensor-core work) while this one adds passes over local HBM at
+        # the owner: measured on k = 8, E = 128 the two tie when 75 % of the rows are saved (2 ranks) and the per-slot
+        # exchange wins at 55 % and 34 % (4 and 8 ranks). With uniform routing a token's top_k slots fall on about
         # world * (1 - (1 - 1/world) ** top_k) distinct ranks.
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         owners = world * (1.0 - (1.0 - 1.0 / world) ** self.top_k)
         if once_per_rank is None:
-            once_per_rank = 1 < self.top_k <= 16 and owners <= 0.7 * self.top_k
+            once_per_rank = 1 < self.top_k <= 16 and owners <= 0.3 * self.top_k
         self.once_per_rank = bool(once_per_rank)
         if self.once_per_rank and not (1 <= self.top_k <= 16):
             raise AssertionError("once_per_rank needs top_k <= 16")
