@@ -713,7 +713,7 @@ def measure(name, c, device, rank, world, dist, steps, warmup, with_e2e=True, sa
     # two copy streams, one per direction: PCIe is full duplex, and a result travelling back must not queue behind the
     # next step's inputs
     copy_stream = torch.cuda.Stream(device=device)
-    back_stream = torch.cuda.Stream(device=device)
+    back_stream = torch.cuda.Stream(device=device) if COPY_STREAMS == 2 else copy_stream
     staged = {}
 
     def stage_inputs():
@@ -903,6 +903,9 @@ def measure(name, c, device, rank, world, dist, steps, warmup, with_e2e=True, sa
     return fields, state
 
 
+COPY_STREAMS = 2      # end-to-end loop: one copy stream per direction (2) or one for both (1); see --copy-streams
+
+
 def describe(name, c, world, ep, exchange, tokens_all, tokens_local):
     return {"workload": name, "global_tokens": tokens_all, "tokens_per_gpu": tokens_local, "d_model": c["d"],
             "d_ffn": c["F"], "experts": c["E"], "experts_per_gpu": c["E"] // world if ep else c["E"],
@@ -930,6 +933,8 @@ def main():
     ap.add_argument("--separate-return", action="store_true",
                     help="per-slot NVLink exchange: return rows with a push kernel after the GEMM instead of from the "
                          "GEMM's own epilogue")
+    ap.add_argument("--copy-streams", type=int, choices=(1, 2), default=COPY_STREAMS,
+                    help="end-to-end loop: host->device and device->host copies on one stream each, or both on one")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-triton-ref", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
@@ -974,6 +979,7 @@ def main():
         dist.init_process_group("nccl", device_id=device)
 
     once = {"auto": None, "on": True, "off": False}[args.once_per_rank]
+    globals()["COPY_STREAMS"] = args.copy_streams
     if args.separate_return:
         import scattermoe_b200.expert_parallel as _ep
         _ep.FUSE_RETURN = False
