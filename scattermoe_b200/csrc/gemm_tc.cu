@@ -77,6 +77,7 @@ struct S2SParams {
   const uint8_t* row_gate;
   float* dot_out; int64_t dot_stride;
   int group_m;         // m-tiles per raster group (see decode_tile)
+  int wide_rows;       // gradient epilogues: rows of U and of the result are read and written 32 bytes per lane (put_rows)
   // Expert-parallel return fused into the epilogue (plain launches only; out_addr nullable). Output row m is not
   // stored to Y but straight into another rank's memory over NVLink: out_addr[m] packs (rank, row) as in
   // ep_common.cuh, the row lands in out_peer.p[rank] + row * out_peer_row_bytes. Each rank also starts the m-tiles
@@ -273,6 +274,25 @@ __device__ __forceinline__ void flush_rows_wide(uint8_t* slab, int lane, const u
   }
 }
 
+// NCH consecutive 16-byte pieces (NCH * 8 columns from `col0`) of every lane's own row. `direct`: two pieces at a time
+// straight from registers as 32-byte stores, one full sector per lane (needs 32-byte aligned rows and col0, and a
+// col_limit that is a multiple of 16); else through the staging slab (flush_rows). The direct form costs more
+// store transactions but no shared-memory traffic, and shared-memory bandwidth is what the MMAs of the next tile are
+// short of while an epilogue with twice the usual output (the activation gradients) runs.
+template <int NCH>
+__device__ __forceinline__ void put_rows(bool direct, uint8_t* slab, int lane, const uint4 (&mine)[NCH], uint8_t* rowptr,
+                                         bool valid, int col0, int col_limit) {
+  if (direct) {
+#pragma unroll
+    for (int g = 0; g < NCH; g += 2) {
+      const int col = col0 + g * 8;
+      if (valid && col < col_limit) st_global_256(rowptr + static_cast<int64_t>(col) * 2, mine[g], mine[g + 1]);
+    }
+  } else {
+    flush_rows<NCH>(slab, lane, mine, rowptr, valid, col0, col_limit);
+  }
+}
+
 // Plain epilogue of a launch whose rows return to their home ranks (S2SParams::out_addr): NP * 8 accumulator columns
 // at a time (64: each row travels in whole 128-byte lines; 128: in pairs of lines). The two groups of epilogue warps
 // take every other unit.
@@ -440,18 +460,28 @@ __device__ __forceinline__ bool epilogue_act_bwd(const S2SParams& p, int n0, uin
   const int lin_off = p.glu_first ? F : 0, gate_off = p.glu_first ? 0 : F;
   // byte offset inside the row of piece q of the chunk that starts at hidden column n (clamped to stay inside
   // the row: the flush masks what lies beyond it)
+  const bool wide = p.wide_rows != 0;      // 32-byte loads and stores, two pieces at a time (host-checked alignment)
+  const int last = F - (wide ? 16 : 8);    // last column a (pair of) piece(s) may start at
   auto piece_offset = [&](int n, int q) -> int64_t {
-    if (EPI == EPI_BWD_PLAIN) return static_cast<int64_t>(min(n + q * 8, F - 8)) * 2;
-    if (EPI == EPI_BWD_GLU) return static_cast<int64_t>((q < 4 ? lin_off : gate_off) + min(n + (q & 3) * 8, F - 8)) * 2;
+    if (EPI == EPI_BWD_PLAIN) return static_cast<int64_t>(min(n + q * 8, last)) * 2;
+    if (EPI == EPI_BWD_GLU) return static_cast<int64_t>((q < 4 ? lin_off : gate_off) + min(n + (q & 3) * 8, last)) * 2;
     return static_cast<int64_t>(2 * min(n + (q >> 1) * 8, F - 8) + (q & 1) * 8) * 2;
   };
   uint4 nxt[NRAW];
   auto request = [&](int c) {
     const int n = n0 + c * 32;
     const bool live = valid && c < BN / 32 && n < F;
+    if (wide) {
 #pragma unroll
-    for (int q = 0; q < NRAW; ++q)
-      nxt[q] = live ? __ldg(reinterpret_cast<const uint4*>(urow + piece_offset(n, q))) : make_uint4(0u, 0u, 0u, 0u);
+      for (int q = 0; q < NRAW; q += 2) {
+        if (live) ld_global_nc_256(urow + piece_offset(n, q), nxt[q], nxt[q + 1]);
+        else nxt[q] = nxt[q + 1] = make_uint4(0u, 0u, 0u, 0u);
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < NRAW; ++q)
+        nxt[q] = live ? __ldg(reinterpret_cast<const uint4*>(urow + piece_offset(n, q))) : make_uint4(0u, 0u, 0u, 0u);
+    }
   };
   request(c_first);
   if (!wait_acc()) return false;
@@ -480,7 +510,7 @@ __device__ __forceinline__ bool epilogue_act_bwd(const S2SParams& p, int n0, uin
         })
         pd[g] = pack8(d, p.is_bf16);
       }
-      flush_rows<4>(slab, lane, pd, durow, valid, n, F);
+      put_rows<4>(wide, slab, lane, pd, durow, valid, n, F);
     } else if (EPI == EPI_BWD_GLU) {
       uint4 pl[4], pg[4];
 #pragma unroll
@@ -499,8 +529,8 @@ __device__ __forceinline__ bool epilogue_act_bwd(const S2SParams& p, int n0, uin
         pl[g] = pack8(dl, p.is_bf16);
         pg[g] = pack8(dg, p.is_bf16);
       }
-      flush_rows<4>(slab, lane, pl, durow + static_cast<int64_t>(lin_off) * 2, valid, n, F);
-      flush_rows<4>(slab, lane, pg, durow + static_cast<int64_t>(gate_off) * 2, valid, n, F);
+      put_rows<4>(wide, slab, lane, pl, durow + static_cast<int64_t>(lin_off) * 2, valid, n, F);
+      put_rows<4>(wide, slab, lane, pg, durow + static_cast<int64_t>(gate_off) * 2, valid, n, F);
     } else {
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {               // 16 hidden columns -> 32 columns of U
@@ -528,7 +558,7 @@ __device__ __forceinline__ bool epilogue_act_bwd(const S2SParams& p, int n0, uin
           po[2 * g] = pack8(o0, p.is_bf16);
           po[2 * g + 1] = pack8(o1, p.is_bf16);
         }
-        flush_rows<4>(slab, lane, po, durow, valid, 2 * (n + hh * 16), 2 * F);
+        put_rows<4>(wide, slab, lane, po, durow, valid, 2 * (n + hh * 16), 2 * F);
       }
     }
   }
@@ -1392,6 +1422,12 @@ int launch_s2s_tc(const S2SArgs& a) {
   p.U = static_cast<const uint8_t*>(a.U); p.u_row_bytes = a.sum * 2;
   p.row_gate = static_cast<const uint8_t*>(a.row_gate);
   p.dot_out = a.dot_out; p.dot_stride = a.R;
+  {
+    // SMOE_EPI_DIRECT=2 keeps the staged stores (a measurement hook)
+    auto al32 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 31) == 0; };
+    p.wide_rows = (a.act_bwd && a.N % 16 == 0 && a.sum % 16 == 0 && a.sym % 16 == 0 && al32(a.U) && al32(a.Y) &&
+                   env_int("SMOE_EPI_DIRECT", 1) == 1) ? 1 : 0;
+  }
   p.out_addr = a.out_addr; p.out_peer_row_bytes = a.out_peer_stride * 2; p.out_peer_rows = a.out_peer_rows;
   p.out_world = a.out_world; p.m_rot_num = 0; p.m_rot_den = 1;
   const int peer_store_bytes = to_peers ? env_int("SMOE_PEER_STORE_BYTES", 128) : 0;    // read per launch: a test hook

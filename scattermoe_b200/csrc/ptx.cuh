@@ -195,4 +195,16 @@ inline uint32_t make_idesc_f16(bool bf16, bool a_mn_major, bool b_mn_major, int 
   return d;
 }
 
+// 256-bit global accesses (sm_100): one full 32-byte sector per lane. The address must be 32-byte aligned.
+__device__ __forceinline__ void ld_global_nc_256(const void* ptr, uint4& lo, uint4& hi) {
+  asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+               : "l"(ptr));
+}
+__device__ __forceinline__ void st_global_256(void* ptr, const uint4& lo, const uint4& hi) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(lo.x), "r"(lo.y), "r"(lo.z),
+               "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+               : "memory");
+}
+
 }  // namespace smoe

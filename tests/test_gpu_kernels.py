@@ -347,7 +347,7 @@ def _act_codes(layout, act):
 
 @pytest.mark.parametrize("w_layout", ["k_contig", "n_contig"])
 @pytest.mark.parametrize("layout,act", [("plain", "gelu"), ("glu_second", "silu"), ("glu_first", "gelu"), ("gpt_oss", None)])
-@pytest.mark.parametrize("T,E,k,K,F", [(300, 4, 2, 64, 136), (513, 8, 3, 320, 200), (1000, 8, 2, 256, 384),
+@pytest.mark.parametrize("T,E,k,K,F", [(300, 4, 2, 64, 136), (300, 4, 2, 64, 144), (513, 8, 3, 320, 200), (1000, 8, 2, 256, 384),
                                        (2048, 4, 2, 128, 1024)])
 def test_fused_input_gradient_and_activation_gradient(T, E, k, K, F, layout, act, w_layout):
     """The activation gradient fused into the epilogue of the down-projection's input-gradient GEMM (one launch,
