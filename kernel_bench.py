@@ -5,7 +5,8 @@
 times, with CUDA events around back-to-back launches on torch's current stream, the launches one layer step makes
 through `kernels.ops` (rows already in expert order, as `parallel_linear` feeds them): the up-projection with and
 without the fused activation, the down-projection, the two input gradients (the down-projection's also with the
-fused activation gradient) and the two weight gradients. One JSON line per measurement. `--tokens` shrinks the problem (for profiler captures); the weights keep the workload's shape.
+fused activation gradient) and the two weight gradients, plus the down-projection in the form that stores its rows
+into peer buffers (`gemm2_to_peers`, with this GPU as the only peer). One JSON line per measurement. `--tokens` shrinks the problem (for profiler captures); the weights keep the workload's shape.
 """
 from __future__ import annotations
 
@@ -23,7 +24,7 @@ WORKLOADS = {   # tokens, d_model, d_ffn, experts, top_k
     "gpt_oss_20b": (8192, 2880, 2880, 32, 4),
     "qwen3_moe": (8192, 2048, 768, 128, 8),
 }
-LAUNCHES = ("gemm1", "gemm1_act", "gemm2", "dgrad2", "dgrad2_act", "dgrad1", "wgrad1", "wgrad2")
+LAUNCHES = ("gemm1", "gemm1_act", "gemm2", "gemm2_to_peers", "dgrad2", "dgrad2_act", "dgrad1", "wgrad1", "wgrad2")
 
 
 def main(argv=None):
@@ -51,7 +52,14 @@ def main(argv=None):
     w1 = torch.randn(E, 2 * F, d, device=dev, dtype=dt) * 0.02     # nn.Linear storage (E, out, in)
     w2 = torch.randn(E, d, F, device=dev, dtype=dt) * 0.02
     s2s = lambda X, W, yg: ops.scatter2scatter(X, W, se, ss, 1, x_grouped=True, y_grouped=yg, expert_offsets=off)
+    # the down-projection whose epilogue returns its rows "home" (expert parallelism): here a world of one whose only
+    # peer buffer is local, every row returning to the slot its index names
+    import ctypes
+    home = torch.empty(R, d, device=dev, dtype=dt)
+    home_ptrs = (ctypes.c_void_p * 1)(home.data_ptr())
     calls = {
+        "gemm2_to_peers": (lambda: ops.scatter2scatter_to_peers(h, w2.permute(0, 2, 1), off, ss, home_ptrs, d, R, 0, 1),
+                           2 * R * d * F),
         "gemm1": (lambda: s2s(x, w1.permute(0, 2, 1), True), 2 * R * d * 2 * F),
         "gemm1_act": (lambda: ops.scatter2scatter_act(x, w1.permute(0, 2, 1), se, ss, 1, act.LAYOUT_GLU_SECOND,
                                                       act.ACT_SILU, x_grouped=True, expert_offsets=off),
