@@ -257,7 +257,7 @@ int smoe_ep_return(const void* Y, int64_t stride_ym, const int64_t* return_addr,
  * owner's expert-grouped (x_rows, K) buffer (x_rows = its capacity; the live rows are those the offsets of the E
  * LOCAL experts delimit), W is (E, K, N) in element strides; for every live row i
  *     (r, s) = return_addr[i];  peer_slot_bufs[r][s, 0:N] = X[i, :] @ W[expert of row i]
- * written by the epilogue of the tcgen05 kernel with plain peer stores, 64 bytes of a row per store instruction, as
+ * written by the epilogue of the tcgen05 kernel with plain peer stores, whole 128-byte lines of a row per store instruction, as
  * each 128 x 256 tile finishes: the rows cross NVLink while the tensor cores work on the next tile, and the local
  * result buffer of the two-call form does not exist. Rank `my_rank` walks the row tiles of every expert starting
  * my_rank / world of the way in (the same reason as the rotation of smoe_ep_return). Tensor-core kernel only:
