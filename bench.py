@@ -23,6 +23,7 @@ reference's own test uses as ground truth) on the host cores, every step on a bo
 from __future__ import annotations
 
 import argparse
+import gc
 import importlib
 import importlib.util
 import json
@@ -274,7 +275,7 @@ class LaunchCounter:
     """Counts the kernels this library launches: a proxy in front of the ctypes library that knows how many
     kernels each C entry point enqueues."""
     KERNELS = {"smoe_scatter2scatter_act": 1, "smoe_scatter2scatter_act_bwd": 1, "smoe_ep_dispatch": 1,
-               "smoe_ep_return": 1, "smoe_scatter2scatter_to_peers": 1, "smoe_ep_barrier": 1, "smoe_sort_count": 3, "smoe_sort_count_static": 3,
+               "smoe_ep_return": 1, "smoe_ep_plan_rows": 1, "smoe_scatter2scatter_to_peers": 1, "smoe_ep_barrier": 1, "smoe_sort_count": 3, "smoe_sort_count_static": 3,
                "smoe_offsets_from_sorted": 1, "smoe_scatter2scatter": 1, "smoe_group_bwd_w": 1, "smoe_group": 1,
                "smoe_topk_reduce": 1, "smoe_gate_grad": 1, "smoe_activation_forward": 1, "smoe_activation_backward": 1,
                "smoe_route_topk": 3, "smoe_status_poison": 1, "smoe_gate_grad_from_partials": 1, "smoe_ep_plan_tokens": 1, "smoe_ep_dispatch_meta": 1,
@@ -764,12 +765,20 @@ def measure(name, c, device, rank, world, dist, steps, warmup, with_e2e=True, sa
         pending.clear()
 
     def timed(fn, n):
-        barrier()
-        a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        fn(n)
-        z.record()
-        barrier()
+        # No cyclic garbage collection inside a timed region: a collection that happens to free an earlier
+        # workload's peer-mapped buffers unmaps them on every rank and stalls this one for hundreds of milliseconds
+        # (seen as a 50 ms/step outlier in a 6-step end-to-end loop).
+        gc.collect()
+        gc.disable()
+        try:
+            barrier()
+            a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn(n)
+            z.record()
+            barrier()
+        finally:
+            gc.enable()
         ms = a.elapsed_time(z)
         if dist is not None:
             t = torch.tensor([ms], device=device)

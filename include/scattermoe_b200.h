@@ -250,6 +250,12 @@ int smoe_ep_dispatch(const void* X, int64_t x_rows, int64_t stride_xm, const int
                      const void* coeff, int32_t fan_out, void* const* peer_bufs, int64_t peer_stride_rows,
                      int64_t capacity_rows, void* const* peer_return_addr, int32_t my_rank, int64_t R, int32_t K,
                      int32_t E, int32_t world, int32_t dtype, void* stream);
+/* smoe_ep_plan_rows: the placement arithmetic between the all-gather of every rank's expert offsets and
+ * smoe_ep_dispatch, as one small kernel. all_offsets is (world, E) int64, row s = sender s's inclusive per-expert ends
+ * (its smoe_sort_count offsets). Writes dst_offsets (E,) for smoe_ep_dispatch (every owner's buffer ordered (local
+ * expert, sender)) and local_offsets (E / world,), the inclusive ends of this rank's own experts in its buffer. */
+int smoe_ep_plan_rows(const int64_t* all_offsets, int32_t my_rank, int32_t world, int32_t E, int64_t* dst_offsets,
+                      int64_t* local_offsets, void* stream);
 int smoe_ep_return(const void* Y, int64_t stride_ym, const int64_t* return_addr, const int64_t* live_rows,
                    int64_t capacity_rows, void* const* peer_slot_bufs, int64_t peer_stride_rows, int64_t peer_rows,
                    int32_t K, int32_t world, int32_t my_rank, int32_t local_experts, int32_t dtype, void* stream);

@@ -76,6 +76,7 @@ SIGNATURES = {
                             c_int32),
     "smoe_ep_dispatch": ([_P, _I64, _I64, _P, _P, _P, _P, _P, _I32, _P, _I64, _I64, _P, _I32, _I64, _I32, _I32, _I32, _I32,
                           _P], c_int32),
+    "smoe_ep_plan_rows": ([_P, _I32, _I32, _I32, _P, _P, _P], c_int32),
     "smoe_ep_return": ([_P, _I64, _P, _P, _I64, _P, _I64, _I64, _I32, _I32, _I32, _I32, _I32, _P], c_int32),
     "smoe_scatter2scatter_to_peers": ([_P, _I64, _I64, _I64, _P, _I64, _I64, _I64, _P, _P, _P, _I64, _I64, _I32, _I32,
                                        _I32, _I32, _I32, _I32, _I32, _P, _P], c_int32),

@@ -142,6 +142,38 @@ ep_barrier_kernel(PeerPtrs flags, int my_rank, int world, int epoch, long long l
   }
 }
 
+// Where this rank's rows go and what it will hold, from every rank's expert offsets (one block; replaces a dozen
+// small tensor operations between the counts all-gather and the dispatch). all_offsets is (world, E): row s = the
+// inclusive per-expert ends of sender s's expert-sorted slot list. With count[s][e] the differences:
+//   dst_off[e]       = (slots of all senders for the experts before e on e's owner) + (slots of senders < rank for e)
+//   local_offsets[j] = inclusive ends of this rank's own experts over all senders' slots
+// i.e. every owner's buffer is ordered (local expert, sender), which is what ep_dispatch_kernel fills.
+__global__ void __launch_bounds__(256)
+ep_plan_rows_kernel(const int64_t* __restrict__ all_offsets, int my_rank, int world, int E, int e_local,
+                    int64_t* __restrict__ dst_off, int64_t* __restrict__ local_offsets) {
+  extern __shared__ int64_t plan_tot[];          // E totals over the senders
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int64_t tot = 0, before = 0;
+    for (int s = 0; s < world; ++s) {
+      const int64_t* row = all_offsets + static_cast<int64_t>(s) * E;
+      int64_t c = row[e] - (e ? row[e - 1] : 0);
+      c = c < 0 ? 0 : c;
+      tot += c;
+      if (s < my_rank) before += c;
+    }
+    plan_tot[e] = tot;
+    dst_off[e] = before;                         // completed below, once every total is known
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int first = (e / e_local) * e_local;
+    int64_t base = 0;
+    for (int j = first; j < e; ++j) base += plan_tot[j];
+    dst_off[e] += base;
+    if (e / e_local == my_rank) local_offsets[e - first] = base + plan_tot[e];
+  }
+}
+
 template <typename T>
 static int dispatch_typed(const void* X, int64_t x_rows, int64_t sxm, const int64_t* sorted_e, const int64_t* sorted_idx,
                           const int64_t* offsets, const int64_t* dst_off, const void* coeff, int fan_out,
@@ -216,6 +248,18 @@ extern "C" int smoe_ep_dispatch(const void* X, int64_t x_rows, int64_t stride_xm
   }
   set_error("ep_dispatch: unknown dtype %d", dtype);
   return SMOE_ERR_BAD_ARG;
+}
+
+extern "C" int smoe_ep_plan_rows(const int64_t* all_offsets, int32_t my_rank, int32_t world, int32_t E,
+                                 int64_t* dst_offsets, int64_t* local_offsets, void* stream) {
+  SMOE_CHECK_ARG(world >= 1 && world <= EP_MAX_WORLD && E >= 1 && E <= 4096 && E % world == 0,
+                 "ep_plan_rows: E=%d (<= 4096), world=%d", E, world);
+  SMOE_CHECK_ARG(my_rank >= 0 && my_rank < world, "ep_plan_rows: rank %d of %d", my_rank, world);
+  SMOE_CHECK_ARG(all_offsets && dst_offsets && local_offsets, "ep_plan_rows: null pointer");
+  ep_plan_rows_kernel<<<1, 256, static_cast<size_t>(E) * sizeof(int64_t), static_cast<cudaStream_t>(stream)>>>(
+      all_offsets, my_rank, world, E, E / world, dst_offsets, local_offsets);
+  SMOE_LAUNCH_CHECK();
+  return SMOE_OK;
 }
 
 extern "C" int smoe_ep_return(const void* Y, int64_t stride_ym, const int64_t* return_addr, const int64_t* live_rows,

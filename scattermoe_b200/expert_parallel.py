@@ -313,6 +313,21 @@ def _ep_call(name, *args):
     _lib.check(rc, name)
 
 
+def row_exchange_placement(offsets_all: torch.Tensor, num_experts: int, world: int, rank: int):
+    """What `smoe_ep_plan_rows` computes, in tensor operations (the statement the kernel is tested against, and what
+    the multi-process CPU tests replay). `offsets_all[s]` = sender s's inclusive per-expert ends. Returns
+      dst_off (E,)          first position of this rank's slots of expert e in the owner's expert-grouped buffer
+                            (expert-major, then sender)
+      local_offsets (E/W,)  inclusive ends of this rank's own experts in its buffer (all senders' slots)"""
+    e_local = num_experts // world
+    counts_all = torch.diff(offsets_all, dim=1, prepend=offsets_all.new_zeros((world, 1))).clamp_min(0)
+    tot = counts_all.sum(0).view(world, e_local)
+    ebase = (tot.cumsum(1) - tot).flatten()
+    dst_off = (ebase + (counts_all.cumsum(0) - counts_all)[rank]).contiguous()
+    local_offsets = tot[rank].cumsum(0).contiguous()
+    return dst_off, local_offsets
+
+
 class _PeerExchangeMLP(torch.autograd.Function):
     """dispatch -> local expert GLU-MLP -> return, forward and backward, on peer row buffers.
 
@@ -333,16 +348,17 @@ class _PeerExchangeMLP(torch.autograd.Function):
         x = x.contiguous()
         gates = gates.to(x.dtype).contiguous()
 
-        # 1. local routing sort; every rank learns every rank's per-expert counts (tiny all-gather)
+        # 1. local routing sort; every rank learns every rank's per-expert offsets (tiny all-gather)
         sorted_e, sorted_idx, offsets = flatten_sort_count(expert_idxs, E)
-        counts = torch.diff(offsets, prepend=offsets.new_zeros(1))
-        counts_all = torch.empty((W, E), dtype=counts.dtype, device=dev)
-        dist.all_gather_into_tensor(counts_all, counts, group=bufs.group)
-        # 2. where my rows of expert e start in the owner's buffer; my own experts' inclusive offsets
-        tot = counts_all.sum(0).view(W, e_local)
-        ebase = (tot.cumsum(1) - tot).flatten()
-        dst_off = (ebase + (counts_all.cumsum(0) - counts_all)[rank]).contiguous()
-        local_offsets = tot[rank].cumsum(0).contiguous()
+        offsets_all = torch.empty((W, E), dtype=offsets.dtype, device=dev)
+        dist.all_gather_into_tensor(offsets_all, offsets.contiguous(), group=bufs.group)
+        # 2. where my rows of expert e start in the owner's buffer; my own experts' inclusive offsets (one small
+        # kernel; `row_exchange_placement` below states the arithmetic)
+        dst_off = torch.empty(E, dtype=torch.int64, device=dev)
+        local_offsets = torch.empty(e_local, dtype=torch.int64, device=dev)
+        with torch.cuda.device(dev):
+            _ep_call("smoe_ep_plan_rows", offsets_all.data_ptr(), rank, W, E, dst_off.data_ptr(),
+                     local_offsets.data_ptr(), stream)
         rows_dev = local_offsets[-1:]
         # 3. dispatch: rows go straight to their final, expert-grouped position on the owning rank
         with torch.cuda.device(dev):

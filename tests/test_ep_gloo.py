@@ -132,6 +132,36 @@ def test_plan_on_a_single_process_is_the_plain_routing_sort():
     assert torch.equal(rows, x[plan.sorted_scattered_idxs // idx.size(1)])
 
 
+@pytest.mark.parametrize("world,E,k", [(1, 8, 2), (2, 8, 2), (4, 16, 8), (8, 128, 8)])
+def test_per_slot_exchange_placement_fills_every_owner_buffer_exactly(world, E, k):
+    """`row_exchange_placement` (the arithmetic `smoe_ep_plan_rows` runs on the device) for every rank of a world,
+    with the dispatch stores played on the host: every owner's buffer must end up holding each of its slots exactly
+    once, grouped by local expert and, inside an expert, ordered by sending rank; `local_offsets` must delimit the
+    experts."""
+    from scattermoe_b200 import expert_parallel as ep
+    g = torch.Generator().manual_seed(world * 100 + E)
+    T, e_local = 96, E // world
+    ids = [torch.topk(torch.rand(T, E, generator=g), k).indices for _ in range(world)]
+    if world > 1:
+        ids[1] = ids[1] % e_local                                  # one sender routes everything to rank 0
+    sorts = [TorchRowOps.sort(i, E) for i in ids]                  # (sorted ids, sorted slots, inclusive offsets)
+    offsets_all = torch.stack([s[2] for s in sorts])
+    received = [[] for _ in range(world)]                          # per owner: (position, expert, sender)
+    placements = [ep.row_exchange_placement(offsets_all, E, world, r) for r in range(world)]
+    for sender, (sorted_e, _, offsets) in enumerate(sorts):
+        dst_off = placements[sender][0]
+        starts = offsets - torch.diff(offsets, prepend=offsets.new_zeros(1))
+        for m, e in enumerate(sorted_e.tolist()):
+            received[e // e_local].append((int(dst_off[e]) + m - int(starts[e]), e, sender))
+    for owner in range(world):
+        rows = sorted(received[owner])
+        assert [r[0] for r in rows] == list(range(len(rows)))      # a permutation of 0..n-1: no gap, no collision
+        assert [(r[1], r[2]) for r in rows] == sorted((r[1], r[2]) for r in rows)      # (expert, sender) order
+        local_offsets = placements[owner][1]
+        per_expert = [sum(1 for r in rows if r[1] == owner * e_local + j) for j in range(e_local)]
+        assert local_offsets.tolist() == torch.tensor(per_expert).cumsum(0).tolist()
+
+
 # ---- the once-per-owning-rank exchange: its plan and placement arithmetic, with the peer stores played on the host ----
 
 class SkippingSort:

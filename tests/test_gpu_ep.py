@@ -211,3 +211,24 @@ def test_gemm_that_returns_its_rows_equals_gemm_then_push(rank, K, N, store_byte
         assert torch.equal(a, b)
         written += int((b != -7.0).any(1).sum())
     assert written == live - 2
+
+
+@pytest.mark.parametrize("world,E", [(1, 8), (2, 8), (8, 128), (4, 1024)])
+def test_row_placement_kernel_equals_its_statement(world, E):
+    """`smoe_ep_plan_rows` against `row_exchange_placement` (tensor operations), bit for bit, for every rank."""
+    from scattermoe_b200 import _lib
+    from scattermoe_b200 import expert_parallel as ep
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(E + world)
+    counts = torch.randint(0, 50, (world, E), generator=g)
+    counts[0, : E // 2] = 0                                           # experts nobody on rank 0 routes to
+    offsets_all = counts.cumsum(1).to(dev)
+    for rank in range(world):
+        want_dst, want_loc = ep.row_exchange_placement(offsets_all, E, world, rank)
+        dst = torch.full((E,), -1, dtype=torch.int64, device=dev)
+        loc = torch.full((E // world,), -1, dtype=torch.int64, device=dev)
+        with torch.cuda.device(dev):
+            rc = _lib.load().smoe_ep_plan_rows(offsets_all.data_ptr(), rank, world, E, dst.data_ptr(), loc.data_ptr(),
+                                               _lib.stream_ptr(dev))
+        assert rc == 0, _lib.last_error()
+        assert torch.equal(dst, want_dst) and torch.equal(loc, want_loc)
