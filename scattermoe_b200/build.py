@@ -14,7 +14,6 @@ import hashlib
 import os
 import shutil
 import subprocess
-import sys
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")

@@ -21,7 +21,7 @@ the tests; the defaults are the CUDA kernels of this package and there is no oth
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Callable, List, Optional
+from typing import List, Optional
 
 import torch
 import torch.distributed as dist
@@ -29,7 +29,7 @@ from torch import nn
 
 from . import activation as _act
 from .kernels import ops
-from .parallel_experts import flatten_sort_count, parallel_linear
+from .parallel_experts import flatten_sort_count
 
 
 class RowOps:

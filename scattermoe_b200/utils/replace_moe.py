@@ -17,7 +17,6 @@ import inspect
 import logging
 
 import torch
-from torch.nn import functional as F
 
 from .. import _lib
 from .. import activation as _act
