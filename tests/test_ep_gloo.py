@@ -297,3 +297,20 @@ def test_once_per_owning_rank_exchange_plan_on_gloo_ranks(world):
                 q.terminate()
                 raise AssertionError("a rank did not finish")
         assert {r: ret.get(r) for r in range(world)} == {r: "ok" for r in range(world)}
+
+
+@pytest.mark.parametrize("world,k,expect", [(2, 8, True), (4, 8, False), (8, 8, False), (2, 2, False), (8, 2, False),
+                                            (1, 8, True), (2, 1, False)])
+def test_default_exchange_of_the_peer_layer(world, k, expect, monkeypatch):
+    """Which NVLink exchange the layer picks by itself: once per owning rank only where it saves at least 70 % of the
+    rows (expected distinct owners of a token's k slots <= 0.3 k), else per slot with the return fused into the GEMM;
+    an explicit argument always wins."""
+    from scattermoe_b200 import expert_parallel as ep
+    monkeypatch.setattr(ep.dist, "is_initialized", lambda: True)
+    monkeypatch.setattr(ep.dist, "get_world_size", lambda group=None: world)
+    monkeypatch.setattr(ep.dist, "get_rank", lambda group=None: 0)
+    E = 16 * world
+    layer = ep.PeerExpertParallelGLUMLP(64, 32, E, k)
+    assert layer.once_per_rank is expect
+    assert ep.PeerExpertParallelGLUMLP(64, 32, E, k, once_per_rank=not expect).once_per_rank is (not expect and k > 0)
+    assert ep.FUSE_RETURN is True
